@@ -1,0 +1,148 @@
+/*
+ * wkv_b200 -- C ABI of the B200 (sm_100a) implementation of the RWKV WKV
+ * time-mix recurrence: forward and backward, recurrent state and its gradient
+ * carried across BPTT segments, for the v4, v5 and v6 variants.
+ *
+ * Every entry point takes raw device pointers and sizes, launches on the
+ * stream it is given (a cudaStream_t passed as void*), allocates nothing,
+ * never synchronises and keeps no global state.  The caller makes the device
+ * that owns the pointers current before the call.  Return value: WKV_OK or
+ * one of the WKV_ERR_* codes (wkv_error_string() gives the text); on error
+ * nothing was launched.  Nothing ever aborts the process or traps the device.
+ *
+ * file:line citations name the interface of RWKV-infctx-trainer that each
+ * entry point replaces (paths inside that project).
+ */
+#ifndef WKV_B200_H
+#define WKV_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element type of the activation tensors (r,k,v,u,y,gy,gr,gk,gv,gw). */
+enum { WKV_F32 = 0, WKV_BF16 = 1, WKV_F16 = 2 };
+
+enum {
+    WKV_OK = 0,
+    WKV_ERR_NULL = 1,       /* a required pointer is NULL */
+    WKV_ERR_SHAPE = 2,      /* negative size, head size other than 64, C != H*N ... */
+    WKV_ERR_DTYPE = 3,      /* unknown element type / decay encoding / state layout */
+    WKV_ERR_ALIGN = 4,      /* a pointer is not 16-byte aligned */
+    WKV_ERR_WORKSPACE = 5,  /* workspace missing or smaller than *_workspace() says */
+    WKV_ERR_LAUNCH = 6,     /* the CUDA runtime refused the launch (cudaGetLastError) */
+    WKV_ERR_UNSUPPORTED = 7 /* combination not built (e.g. fast path asked for fp32) */
+};
+
+/* How the decay tensor `w` is encoded. */
+enum {
+    WKV_W_RAW = 0, /* the module parameter/activation x; decay = exp(-exp(x)).
+                      v6: [B,T,C] in the activation dtype.  v5: [H,N] fp32. */
+    WKV_W_NEGEXP = 1 /* ew = -exp(x), fp32 (what the project's Python wrappers
+                        precompute: RWKV-v6/src/module/TimeMix.py:49-51,
+                        RWKV-v5/src/module/TimeMix.py:57-60).  Same shapes. */
+};
+
+/* Memory layout of the v5/v6 per-head N x N state. */
+enum {
+    WKV_STATE_KV = 0, /* [B,H,key,value]: rwkv_inner's kv_state
+                         (RWKV-v6/src/module/rwkv_inner.py:22) */
+    WKV_STATE_VK = 1  /* [B,H,value,key]: the project's CUDA kernels
+                         (RWKV-v5/src/module/cuda/wkv5_cuda.cu:142-149) */
+};
+
+/* Which implementation runs a v5/v6 call. */
+enum {
+    WKV_PATH_AUTO = 0,   /* tensor-core chunked kernels when dtype is bf16, else scalar */
+    WKV_PATH_SCALAR = 1, /* token-serial fp32 CUDA-core kernels (any dtype, any T) */
+    WKV_PATH_CHUNKED = 2 /* tcgen05 chunked kernels (bf16 only) */
+};
+
+const char *wkv_error_string(int code);
+
+/* ------------------------------------------------------------------ v4 --
+ * Replaces cuda_forward / cuda_backward of RWKV-v4neo/cuda/wkv_cuda_bf16.cu:160-172
+ * (called from WKVFunction, RWKV-v4neo/cuda/wkv_op_bf16.cpp:53-56, 76-83).
+ *   w          fp32 [C]      = -exp(time_decay)                (wkv_op_bf16.cpp:34)
+ *   u,k,v,y    dtype [C] / [B,T,C]   (the project supports bf16 only; fp32 and
+ *                                     fp16 are additions)
+ *   state_*    fp32 [B,C,3] = (p,q,o); NULL state_in means (0,0,-1e38)
+ *   gw,gu      fp32 [B,C] per-batch partials (the caller sums over B as
+ *              wkv_op_bf16.cpp:85 does); gw is d/d(time_decay), i.e. already
+ *              multiplied by w (wkv_cuda_bf16.cu:156)
+ *   gstate_*   fp32 [B,C,3] = (gp,gq,go) in the exponent-scaled convention of
+ *              wkv_cuda_bf16.cu:116-152; gstate_out may be NULL (= none)
+ * No compile-time limit on T (the project needs T <= Tmax).
+ */
+int wkv4_forward(int B, int T, int C, int dtype, const float *w, const void *u,
+                 const void *k, const void *v, const float *state_in, void *y,
+                 float *state_out, void *stream);
+
+size_t wkv4_backward_workspace(int B, int T, int C);
+
+int wkv4_backward(int B, int T, int C, int dtype, const float *w, const void *u,
+                  const void *k, const void *v, const float *state_in,
+                  const void *gy, const float *gstate_out, float *gw, float *gu,
+                  void *gk, void *gv, float *gstate_in, void *workspace,
+                  size_t workspace_bytes, void *stream);
+
+/* -------------------------------------------------------------- v5 / v6 --
+ * One argument block serves forward and backward of both variants.
+ * C = H*N, N must be 64 (RWKV-v6/src/model.py:313 fixes the head size).
+ */
+typedef struct wkv_args {
+    int B, T, H, N;
+    int dtype;        /* WKV_F32 / WKV_BF16 / WKV_F16 */
+    int w_kind;       /* WKV_W_RAW / WKV_W_NEGEXP */
+    int state_layout; /* WKV_STATE_KV / WKV_STATE_VK (applies to state_* and gstate_*) */
+    int path;         /* WKV_PATH_* */
+    /* forward inputs */
+    const void *r, *k, *v; /* [B,T,C] dtype */
+    const void *w;         /* see w_kind */
+    const void *u;         /* [H,N] dtype */
+    const float *state_in; /* [B,H,N,N] fp32, NULL = zeros */
+    /* forward outputs */
+    void *y;          /* [B,T,C] dtype */
+    float *state_out; /* [B,H,N,N] fp32; may be NULL; may alias state_in */
+    /* backward inputs */
+    const void *gy;          /* [B,T,C] dtype */
+    const float *gstate_out; /* [B,H,N,N] fp32, NULL = zeros */
+    /* backward outputs */
+    void *gr, *gk, *gv; /* [B,T,C] dtype */
+    void *gw;           /* v6: [B,T,C] dtype, gradient w.r.t. x (both w_kinds:
+                           the project's kernels multiply by ew too,
+                           wkv6state_cuda_v1.cu:290).  v5: [B,C] fp32 per-batch
+                           partials of the gradient w.r.t. time_decay */
+    float *gu;          /* [B,C] fp32 per-batch partials */
+    float *gstate_in;   /* [B,H,N,N] fp32; may be NULL */
+    /* scratch */
+    void *workspace;
+    size_t workspace_bytes;
+} wkv_args_t;
+
+/* v5: replaces cuda_forward_{bf16,fp16,fp32} / cuda_backward_* of
+ * RWKV-v5/src/module/cuda/wkv5_cuda.cu:348-383 (bound in wkv5_op.cpp:88-116),
+ * with per-batch state, a state output and the state gradient those lack. */
+size_t wkv5_forward_workspace(const wkv_args_t *a);
+size_t wkv5_backward_workspace(const wkv_args_t *a);
+int wkv5_forward(const wkv_args_t *a, void *stream);
+int wkv5_backward(const wkv_args_t *a, void *stream);
+
+/* v6: replaces cuda_forward / cuda_backward of
+ * RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:295-308 (bound in
+ * wkv6state_op.cpp:8-22) and of the stateless wkv6_cuda.cu:229-242, with fp32
+ * per-batch state, a state output, and the full state gradient. */
+size_t wkv6_forward_workspace(const wkv_args_t *a);
+size_t wkv6_backward_workspace(const wkv_args_t *a);
+int wkv6_forward(const wkv_args_t *a, void *stream);
+int wkv6_backward(const wkv_args_t *a, void *stream);
+
+/* Library build identification: "wkv_b200 <n> sm_100a". */
+const char *wkv_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WKV_B200_H */

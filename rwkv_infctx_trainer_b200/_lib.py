@@ -1,0 +1,110 @@
+"""ctypes binding of libwkv_b200.so (declared in include/wkv_b200.h).
+
+The library is the product: if it cannot be loaded this module raises, there is
+no PyTorch or CPU fallback behind any op of this package.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+WKV_F32, WKV_BF16, WKV_F16 = 0, 1, 2
+WKV_W_RAW, WKV_W_NEGEXP = 0, 1
+WKV_STATE_KV, WKV_STATE_VK = 0, 1
+WKV_PATH_AUTO, WKV_PATH_SCALAR, WKV_PATH_CHUNKED = 0, 1, 2
+
+DTYPE_CODE = {torch.float32: WKV_F32, torch.bfloat16: WKV_BF16, torch.float16: WKV_F16}
+
+_vp = ctypes.c_void_p
+
+
+class WkvArgs(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int), ("T", ctypes.c_int), ("H", ctypes.c_int), ("N", ctypes.c_int),
+        ("dtype", ctypes.c_int), ("w_kind", ctypes.c_int), ("state_layout", ctypes.c_int),
+        ("path", ctypes.c_int),
+        ("r", _vp), ("k", _vp), ("v", _vp), ("w", _vp), ("u", _vp), ("state_in", _vp),
+        ("y", _vp), ("state_out", _vp),
+        ("gy", _vp), ("gstate_out", _vp),
+        ("gr", _vp), ("gk", _vp), ("gv", _vp), ("gw", _vp), ("gu", _vp), ("gstate_in", _vp),
+        ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+EXPORTS = [
+    "wkv_error_string", "wkv_version",
+    "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
+    "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
+    "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
+]
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first if the in-tree library is missing or stale and nvcc exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if not os.path.exists(path):
+        path = _build.build()
+    lib = ctypes.CDLL(path)
+    if any(not hasattr(lib, name) for name in EXPORTS):
+        # a library from older sources: rebuild once (raises if nvcc is absent)
+        path = _build.build(force=True)
+        lib = ctypes.CDLL(path)
+        missing = [name for name in EXPORTS if not hasattr(lib, name)]
+        if missing:
+            raise ImportError(f"{path} lacks symbols {missing}")
+    lib.wkv_error_string.restype = ctypes.c_char_p
+    lib.wkv_error_string.argtypes = [ctypes.c_int]
+    lib.wkv_version.restype = ctypes.c_char_p
+    i, f = ctypes.c_int, _vp
+    lib.wkv4_forward.restype = i
+    lib.wkv4_forward.argtypes = [i, i, i, i, f, f, f, f, f, f, f, _vp]
+    lib.wkv4_backward_workspace.restype = ctypes.c_size_t
+    lib.wkv4_backward_workspace.argtypes = [i, i, i]
+    lib.wkv4_backward.restype = i
+    lib.wkv4_backward.argtypes = [i, i, i, i] + [f] * 12 + [_vp, ctypes.c_size_t, _vp]
+    for v in ("wkv5", "wkv6"):
+        for d in ("forward", "backward"):
+            fn = getattr(lib, f"{v}_{d}")
+            fn.restype = i
+            fn.argtypes = [ctypes.POINTER(WkvArgs), _vp]
+            ws = getattr(lib, f"{v}_{d}_workspace")
+            ws.restype = ctypes.c_size_t
+            ws.argtypes = [ctypes.POINTER(WkvArgs)]
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: {load().wkv_error_string(code).decode()} (code {code})")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_handle(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("wkv_b200 ops run on CUDA tensors only (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("all tensors of one WKV call must live on the same device")
+    return dev
