@@ -33,7 +33,8 @@ enum {
     WKV_ERR_ALIGN = 4,      /* a pointer is not 16-byte aligned */
     WKV_ERR_WORKSPACE = 5,  /* workspace missing or smaller than *_workspace() says */
     WKV_ERR_LAUNCH = 6,     /* the CUDA runtime refused the launch (cudaGetLastError) */
-    WKV_ERR_UNSUPPORTED = 7 /* combination not built (e.g. fast path asked for fp32) */
+    WKV_ERR_UNSUPPORTED = 7, /* combination not built (e.g. fast path asked for fp32) */
+    WKV_ERR_TOO_LARGE = 8    /* needs more scratch than the built-in array holds */
 };
 
 /* How the decay tensor `w` is encoded. */
@@ -87,6 +88,35 @@ int wkv4_backward(int B, int T, int C, int dtype, const float *w, const void *u,
                   const void *gy, const float *gstate_out, float *gw, float *gu,
                   void *gk, void *gv, float *gstate_in, void *workspace,
                   size_t workspace_bytes, void *stream);
+
+/* wkv4_backward for callers that cannot supply a workspace.  (No counterpart in
+ * RWKV-infctx-trainer: its kernels keep their scratch in per-thread arrays.)
+ *
+ * Who needs it: a host that binds only this C ABI and was handed its tensors
+ * by someone else, so it has no device allocator to ask; or a training loop
+ * whose device memory is laid out in advance and which may not call cudaMalloc
+ * (which also synchronises the device) between steps.
+ *
+ * Same arguments and results as wkv4_backward minus workspace/workspace_bytes.
+ * The tile-start states go to a 32 MiB array that is part of the library image
+ * (wkv4_backward_static_limit() returns its size); every GPU that loads the
+ * library carries those 32 MiB until the process ends.  The call allocates and
+ * frees nothing.  If wkv4_backward_workspace(B,T,C) exceeds the limit it
+ * returns WKV_ERR_TOO_LARGE and launches nothing -- split T into shorter
+ * segments (the state chains) or use wkv4_backward.
+ *
+ * The first call on each device looks up the array's device address (one
+ * cudaGetSymbolAddress with that device current); make that first call outside
+ * any stream capture.  All calls on a device share the one array, which keeps
+ * whatever the previous call left there: the kernel needs none of it zeroed,
+ * but two calls whose kernels may run at the same time on one GPU (different
+ * streams, or different host threads) overwrite each other's states and give
+ * wrong gradients.  Issue them on one stream, or order them with events. */
+size_t wkv4_backward_static_limit(void);
+int wkv4_backward_static(int B, int T, int C, int dtype, const float *w, const void *u,
+                         const void *k, const void *v, const float *state_in,
+                         const void *gy, const float *gstate_out, float *gw, float *gu,
+                         void *gk, void *gv, float *gstate_in, void *stream);
 
 /* -------------------------------------------------------------- v5 / v6 --
  * One argument block serves forward and backward of both variants.

@@ -38,6 +38,7 @@ class WkvArgs(ctypes.Structure):
 EXPORTS = [
     "wkv_error_string", "wkv_version",
     "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
+    "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
 ]
@@ -71,6 +72,10 @@ def load() -> ctypes.CDLL:
     lib.wkv4_backward_workspace.argtypes = [i, i, i]
     lib.wkv4_backward.restype = i
     lib.wkv4_backward.argtypes = [i, i, i, i] + [f] * 12 + [_vp, ctypes.c_size_t, _vp]
+    lib.wkv4_backward_static_limit.restype = ctypes.c_size_t
+    lib.wkv4_backward_static_limit.argtypes = []
+    lib.wkv4_backward_static.restype = i
+    lib.wkv4_backward_static.argtypes = [i, i, i, i] + [f] * 12 + [_vp]
     for v in ("wkv5", "wkv6"):
         for d in ("forward", "backward"):
             fn = getattr(lib, f"{v}_{d}")

@@ -203,3 +203,72 @@ extern "C" int wkv4_backward(int B, int T, int C, int dtype, const float *w, con
     }
     return WKV_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// Backward without a caller-provided workspace.
+//
+// Some hosts of this library cannot hand it scratch memory: a foreign-language
+// binding that was given its tensors by another framework and owns no device
+// allocator, or a training loop whose device memory is planned up front and
+// which must not call cudaMalloc in the middle of a step (cudaMalloc also
+// synchronises the device).  For them the tile-start states that
+// wkv4_backward keeps in its workspace live here, in a fixed array inside the
+// library image.  Every GPU that loads the library holds these bytes until the
+// process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char g_v4_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_scratch_addr[kMaxDevices];  // device address of the array, per device ordinal
+bool g_scratch_known[kMaxDevices];
+
+// In host code `g_v4_static_scratch` names a host-side shadow, not device
+// memory; the device address has to be asked for, on the device in question.
+int static_scratch_address(void **out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return WKV_ERR_LAUNCH;
+    if (!g_scratch_known[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_v4_static_scratch) != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return WKV_ERR_LAUNCH;
+        }
+        g_scratch_addr[dev] = p;
+        __atomic_store_n(&g_scratch_known[dev], true, __ATOMIC_RELEASE);
+    }
+    *out = g_scratch_addr[dev];
+    return WKV_OK;
+}
+
+}  // namespace
+
+extern "C" size_t wkv4_backward_static_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int wkv4_backward_static(int B, int T, int C, int dtype, const float *w, const void *u,
+                                    const void *k, const void *v, const float *state_in,
+                                    const void *gy, const float *gstate_out, float *gw, float *gu,
+                                    void *gk, void *gv, float *gstate_in, void *stream) {
+    if (B < 0 || T < 0 || C < 0) return WKV_ERR_SHAPE;
+    if (B == 0 || C == 0) return WKV_OK;
+    if (!w || !u || !gw || !gu) return WKV_ERR_NULL;
+    if (T > 0 && (!k || !v || !gy || !gk || !gv)) return WKV_ERR_NULL;
+    if (dtype != WKV_F32 && dtype != WKV_BF16 && dtype != WKV_F16) return WKV_ERR_DTYPE;
+    if (wkv4_backward_workspace(B, T, C) > kStaticScratchBytes) return WKV_ERR_TOO_LARGE;
+    void *scratch = nullptr;
+    const int err = static_scratch_address(&scratch);
+    if (err != WKV_OK) return err;
+    cudaStream_t s = (cudaStream_t)stream;
+    float *ws = (float *)scratch;
+    // Nothing in the scratch has to start at zero: the kernel's forward sweep
+    // writes every tile-start state before its reverse sweep reads it.
+    switch (dtype) {
+        case WKV_F32:
+            return bwd<float>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
+        case WKV_BF16:
+            return bwd<__nv_bfloat16>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
+        default:
+            return bwd<__half>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
+    }
+}

@@ -93,6 +93,7 @@ const char *wkv_error_string(int code) {
         case WKV_ERR_WORKSPACE: return "workspace missing or too small";
         case WKV_ERR_LAUNCH: return "CUDA launch failed";
         case WKV_ERR_UNSUPPORTED: return "the chunked tensor-core path does not take these arguments";
+        case WKV_ERR_TOO_LARGE: return "needs more scratch than the library's built-in array holds";
     }
     return "unknown error code";
 }
