@@ -128,6 +128,7 @@ class Runner:
         B, H, N = wl["B"], wl["H"], wl["N"]
         self.state0 = torch.zeros((B, H, N, N), device=device)
         self.bwd_events = []
+        self.fwd_events = []
         self.launches = 0
 
     def seg(self, name, t0, t1):
@@ -137,9 +138,15 @@ class Runner:
         W, d = self.W, self.d
         states = [self.state0]
         for t0, t1 in self.bounds:
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
             y, s = self.wkv56.forward("wkv6", self.seg("r", t0, t1), self.seg("k", t0, t1),
                                       self.seg("v", t0, t1), self.seg("w", t0, t1), d["u"],
                                       states[-1], w_kind=W.WKV_W_RAW)
+            if record:
+                e1.record()
+                self.fwd_events.append((e0, e1))
             states.append(s)
             self.launches += 1
         gs = None
@@ -211,6 +218,7 @@ def run_ours(args):
     ms = t_start.elapsed_time(t_end)
     launches = runner.launches
     bwd_ms = [a.elapsed_time(b) for a, b in runner.bwd_events]
+    fwd_ms = [a.elapsed_time(b) for a, b in runner.fwd_events]
 
     # ---- end to end through the public autograd op, host buffers in pinned memory
     import rwkv_infctx_trainer_b200 as W
@@ -280,6 +288,10 @@ def run_ours(args):
                          "frac": achieved / hbm, "peak_source": which,
                          "algorithmic_bytes_per_launch": bwd_bytes,
                          "avg_launch_ms": avg_bwd_ms, "traffic": None},
+            "forward_launch": {"avg_launch_ms": sum(fwd_ms) / len(fwd_ms),
+                               "achieved_gbs": (FWD_ELEMS * 2 * B * seg_tokens * C
+                                                + 2 * B * H * 64 * 64 * 4)
+                               / (sum(fwd_ms) / len(fwd_ms) * 1e-3) / 1e9},
             "whole_step_roofline_frac": (
                 (FWD_ELEMS + BWD_ELEMS) * 2 * B * T * C / (ms / args.steps * 1e-3) / 1e9 / hbm),
         }

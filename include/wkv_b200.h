@@ -169,6 +169,12 @@ size_t wkv6_backward_workspace(const wkv_args_t *a);
 int wkv6_forward(const wkv_args_t *a, void *stream);
 int wkv6_backward(const wkv_args_t *a, void *stream);
 
+/* 1 if a v5 (per_token_w = 0) / v6 (per_token_w = 1) call with these arguments runs on the
+ * chunked tensor-core kernels, 0 if on the token-serial ones.  When it does, the first 4
+ * bytes of the workspace hold a status word after the call has completed on the stream:
+ * 0 = ok, non-zero = a bounded device-side wait ran out and the results are invalid. */
+int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
+
 /* Library build identification: "wkv_b200 <n> sm_100a". */
 const char *wkv_version(void);
 

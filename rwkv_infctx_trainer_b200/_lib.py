@@ -36,7 +36,7 @@ class WkvArgs(ctypes.Structure):
 
 
 EXPORTS = [
-    "wkv_error_string", "wkv_version",
+    "wkv_error_string", "wkv_version", "wkv56_uses_chunked",
     "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
     "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
@@ -76,6 +76,8 @@ def load() -> ctypes.CDLL:
     lib.wkv4_backward_static_limit.argtypes = []
     lib.wkv4_backward_static.restype = i
     lib.wkv4_backward_static.argtypes = [i, i, i, i] + [f] * 12 + [_vp]
+    lib.wkv56_uses_chunked.restype = i
+    lib.wkv56_uses_chunked.argtypes = [ctypes.POINTER(WkvArgs), i]
     for v in ("wkv5", "wkv6"):
         for d in ("forward", "backward"):
             fn = getattr(lib, f"{v}_{d}")

@@ -1,9 +1,460 @@
-// Chunked tensor-core v5/v6 kernels (placeholder until the tcgen05 path lands).
+// Chunked tensor-core kernels for the v5/v6 WKV recurrence (bf16 I/O, fp32 state).
+//
+// Time is cut into chunks of 64 tokens, each chunk into two blocks of 32.  With
+// c_t the inclusive running sum of the log-decay inside a chunk and cp_t = c_{t-1}:
+//   scores  A[t,s] = sum_k r_t[k] k_s[k] e^{cp_t[k]-c_s[k]}  (s<t),  A[t,t] = sum_k r_t u k_t
+//   y       = A V + (r e^{cp}) S_in
+//   S_out   = diag(e^{c_63}) S_in + (k e^{c_63-c})^T V
+// (the chunked form of RWKV-v6/src/module/rwkv_inner.py:48-113).  Every factor that
+// multiplies an MMA operand is kept inside the bf16/fp32 exponent range: pairs inside
+// a 32-token block are factored around the block's midpoint (as rwkv_inner.py:88-90
+// does for its 128-token chunks in fp64), pairs across the two blocks around the end
+// of the first block (both factors <= 1).  For that to hold for any input the decay
+// is floored at 0.005 -- the floor rwkv_inner.py:40-45 applies.
+//
+// All contractions run on tcgen05.mma (M=64, bf16 operands in 128-byte-swizzled
+// shared-memory tiles, fp32 accumulators in tensor memory); input tiles arrive by
+// TMA; the fp32 state lives in tensor memory for the whole segment.
+#include "sm100_primitives.cuh"
+#include "tma_host.cuh"
 #include "wkv_common.cuh"
+
 namespace wkv {
-bool chunked_supported(const wkv_args_t *, bool) { return false; }
-size_t chunked_forward_workspace(const wkv_args_t *, bool) { return 0; }
-size_t chunked_backward_workspace(const wkv_args_t *, bool) { return 0; }
-int chunked_forward(const wkv_args_t *, bool, cudaStream_t) { return WKV_ERR_UNSUPPORTED; }
-int chunked_backward(const wkv_args_t *, bool, cudaStream_t) { return WKV_ERR_UNSUPPORTED; }
+namespace {
+
+using namespace sm100;
+
+constexpr int CH = 64;            // tokens per chunk
+constexpr int HB = 32;            // tokens per block
+constexpr float LW_FLOOR = -5.298317367f;  // log(0.005)
+
+struct __align__(16) Tile { unsigned char b[TILE_BYTES]; };
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void unpack8(const uint4 &q, float *f) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float *f) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+}
+__device__ __forceinline__ uint4 ld_tile(const Tile &t, int row, int chunk) {
+    return *reinterpret_cast<const uint4 *>(t.b + tile_off(row, chunk));
+}
+__device__ __forceinline__ void st_tile(Tile &t, int row, int chunk, const uint4 &v) {
+    *reinterpret_cast<uint4 *>(t.b + tile_off(row, chunk)) = v;
+}
+
+// ---------------------------------------------------------------------------
+// Per-chunk operand preparation.  Thread layout (128 threads): 16-byte column
+// `cc` = 2*warp + (lane>>4) (8 channels), token group tg = lane & 15 (4 tokens).
+// Everything a thread computes concerns tokens 4*tg..4*tg+3 of channels 8*cc..+7.
+struct Prep {
+    float c[4][8];    // inclusive cumulative log-decay
+    float lw[4][8];   // per-token log-decay (floored), 0 for tokens past the segment end
+    float m0[8], m1[8], e0[8], e1[8];
+};
+
+// lw filled by the caller; computes the chunk-wide cumulative sums by a local scan
+// plus a 16-lane segmented warp scan, then the four reference values.
+__device__ __forceinline__ void prep_scan(Prep &p, int lane) {
+    const int tg = lane & 15;
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        p.c[0][ch] = p.lw[0][ch];
+#pragma unroll
+        for (int i = 1; i < 4; i++) p.c[i][ch] = p.c[i - 1][ch] + p.lw[i][ch];
+        float tot = p.c[3][ch];
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
+            if (tg >= off) tot += o;
+        }
+        const float excl = tot - p.c[3][ch];
+#pragma unroll
+        for (int i = 0; i < 4; i++) p.c[i][ch] += excl;
+        // inclusive sums at tokens 15, 31, 47, 63 live in lanes tg = 3, 7, 11, 15
+        p.m0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 3, 16);
+        p.e0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 7, 16);
+        p.m1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 11, 16);
+        p.e1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 15, 16);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Forward: one CTA per (batch, head), serial over the chunks of the segment.
+struct FwdSmem {
+    Tile in[2][4];     // per stage: r, k, v, w  (r,k,w are overwritten in place by
+                       // r*fr, k*fk, r*e^{cp})
+    Tile x, khat, atil, sbf;
+    float dpart[8][CH];
+    float dvec[CH];
+    uint64_t load_bar[2];
+    uint64_t mma_bar;
+    uint32_t tmem_base;
+};
+
+struct FwdParams {
+    int T, H, nchunk, layout, w_kind;
+    const __nv_bfloat16 *u;
+    const float *wvec;        // v5: per-channel decay parameter [H*64]
+    const float *state_in;
+    float *state_out;
+    __nv_bfloat16 *y;
+    __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
+    int *status;
+};
+
+enum { COL_S = 0, COL_A1 = 64, COL_A2 = 128, COL_Y = 160, FWD_TMEM_COLS = 256 };
+
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(128, 2)
+k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
+            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
+            const FwdParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, C = P.H * 64;
+    const bool active = (lane & 16) == 0;          // owns an accumulator row
+    const int row = warp * 16 + (lane & 15);       // that row
+    const uint32_t lane_base = (uint32_t)(warp * 32);
+    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+
+    if (tid == 0) {
+        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 1);
+        fence_mbar_init();
+        prefetch_tmap(&map_r); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
+        if (PER_TOKEN) prefetch_tmap(&map_w);
+    }
+    if (warp == 0) { tmem_alloc(&s.tmem_base, FWD_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s.tmem_base;
+
+    auto issue_load = [&](int j) {
+        const int st = j & 1;
+        const uint32_t bytes = (PER_TOKEN ? 4 : 3) * TILE_BYTES;
+        mbar_expect_tx(&s.load_bar[st], bytes);
+        tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
+        tma_load_3d(&s.in[st][1], &map_k, &s.load_bar[st], h * 64, j * CH, b);
+        tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, j * CH, b);
+        if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+    };
+    if (tid == 0 && P.nchunk > 0) issue_load(0);
+
+    // state -> tensor memory (row = key channel, column = value channel)
+    const size_t sbase = (size_t)bh * 64 * 64;
+    {
+        float v[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) {
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
+            v[j] = P.state_in ? P.state_in[sbase + idx] : 0.f;
+        }
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+    }
+    tmem_st_wait();
+
+    // per-thread constants of the 8 channels this thread prepares
+    float uu[8], lwc[8];
+    {
+        const uint4 q = *reinterpret_cast<const uint4 *>(P.u + h * 64 + cc * 8);
+        unpack8(q, uu);
+        if (!PER_TOKEN) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const float x = P.wvec[h * 64 + cc * 8 + ch];
+                lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+            }
+        }
+    }
+
+    uint32_t mma_phase = 0;
+    int fail = 0;        // a bounded wait ran out (carried through the next barrier)
+    int aborted = 0;
+    int issued = P.nchunk > 0 ? 0 : -1, landed = -1;   // TMA loads issued / seen complete
+    tc_fence_before();
+    __syncthreads();
+
+    for (int j = 0; j < P.nchunk; j++) {
+        const int st = j & 1;
+        Tile *in = s.in[st];
+        if (j + 1 < P.nchunk) {
+            if (tid == 0) issue_load(j + 1);
+            issued = j + 1;
+        }
+        if (mbar_wait(&s.load_bar[st], (uint32_t)((j >> 1) & 1))) landed = j; else fail = 1;
+
+        // ------------------------------------------------------------ prep
+        {
+            Prep p;
+            float rr[4][8], kk[4][8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int t = 4 * tg + i;
+                unpack8(ld_tile(in[0], t, cc), rr[i]);
+                unpack8(ld_tile(in[1], t, cc), kk[i]);
+                const bool valid = j * CH + t < P.T;
+                if (PER_TOKEN) {
+                    float x[8];
+                    unpack8(ld_tile(in[3], t, cc), x);
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++)
+                        p.lw[i][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+                }
+            }
+            prep_scan(p, lane);
+            const bool blk1 = tg >= 8;
+            float ee0[8], ee10[8];
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                ee0[ch] = __expf(p.e0[ch]);
+                ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
+            }
+            if (tg == 0) {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int t = 4 * tg + i;
+                float rt[8], kt[8], xx[8], rh[8], kh[8];
+                float dsum = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) {
+                    const float c = p.c[i][ch], cp = c - p.lw[i][ch];
+                    const float mb = blk1 ? p.m1[ch] : p.m0[ch];
+                    const float fr = __expf(cp - mb), fk = __expf(mb - c);
+                    const float g = blk1 ? __expf(cp - p.e0[ch]) : __expf(p.e0[ch] - c);
+                    const float frh = blk1 ? g * ee0[ch] : __expf(cp);
+                    const float fkh = blk1 ? __expf(p.e1[ch] - c) : g * ee10[ch];
+                    const float r = rr[i][ch], k = kk[i][ch];
+                    rt[ch] = r * fr; kt[ch] = k * fk;
+                    xx[ch] = (blk1 ? r : k) * g;
+                    rh[ch] = r * frh; kh[ch] = k * fkh;
+                    dsum += r * uu[ch] * k;
+                }
+                st_tile(in[0], t, cc, pack8(rt));
+                st_tile(in[1], t, cc, pack8(kt));
+                st_tile(in[3], t, cc, pack8(rh));
+                st_tile(s.x, t, cc, pack8(xx));
+                st_tile(s.khat, t, cc, pack8(kh));
+                s.dpart[cc][t] = dsum;
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(fail)) { aborted = 1; break; }
+
+        // ------------------------------------------- scores: A1 = Rt Kt^T, A2 = X X[0:32]^T
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm + COL_A1, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id64, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm + COL_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+            mma_commit(&s.mma_bar);
+        }
+        // ---- meanwhile: snapshot the state as bf16 (operand of r*S, checkpoint) and decay it.
+        // tcgen05.ld/st are warp-wide: every lane runs them, lanes 16..31 of a warp touch the
+        // unused upper half of the 32 tensor-memory lanes and store nothing.
+        {
+            float v[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+            tmem_ld_wait();
+            const float d = s.dvec[row];
+            if (active) {
+                uint4 q[8];
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) {
+                    q[c8] = pack8(v + 8 * c8);
+                    st_tile(s.sbf, row, c8, q[c8]);
+                }
+                if (P.ckpt) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (P.nchunk + 1) + j) * 64 + row) * 64);
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; c8++) dst[c8] = q[c8];
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 64; c++) v[c] *= d;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+        }
+        tmem_st_wait();
+        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
+        mma_phase ^= 1;
+        tc_fence_after();
+
+        // ------------------------------------------------------- mask pass
+        {
+            const int t = row;
+            float a[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_A1 + c0), a + c0);
+            float a2[32];
+            tmem_ld16(tmem_addr(tm, lane_base, COL_A2), a2);
+            tmem_ld16(tmem_addr(tm, lane_base, COL_A2 + 16), a2 + 16);
+            tmem_ld_wait();
+            float diag = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; q++) diag += s.dpart[q][t];
+#pragma unroll
+            for (int sx = 0; sx < 64; sx++) {
+                float val;
+                if (sx == t) val = diag;
+                else if (sx > t) val = 0.f;
+                else if (t >= HB && sx < HB) val = a2[sx & 31];
+                else val = a[sx];
+                a[sx] = val;
+            }
+            if (active) {
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) st_tile(s.atil, t, c8, pack8(a + 8 * c8));
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(fail)) { aborted = 1; break; }
+
+        // --------------------------- y = Atil V + Rhat Sbf ;  S = d*S + Khat^T V
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t id_km = make_idesc(64, 64, false, true), id_mm = make_idesc(64, 64, true, true);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm + COL_Y, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k), id_km, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm + COL_Y, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k), id_km, true);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm + COL_S, desc_mnmajor(&s.khat, 0, k), desc_mnmajor(&in[2], 0, k), id_mm, true);
+            mma_commit(&s.mma_bar);
+        }
+        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
+        mma_phase ^= 1;
+        tc_fence_after();
+
+        // -------------------------------------------------------- epilogue
+        {
+            const int t = j * CH + row;
+            float yv[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_Y + c0), yv + c0);
+            tmem_ld_wait();
+            if (active && t < P.T) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64);
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(yv + 8 * c8);
+            }
+        }
+        tc_fence_before();
+        if (__syncthreads_or(fail)) { aborted = 1; break; }
+    }
+
+    // after a failed wait: let TMA loads that were issued land (bounded), so that the CTA
+    // never exits under one
+    if (aborted) {
+        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
+    }
+    tc_fence_after();
+    {
+        float v[64];
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+        tmem_ld_wait();
+        const bool wr = active && !aborted;
+        if (wr && P.state_out) {
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
+                P.state_out[sbase + idx] = v[j];
+            }
+        }
+        if (wr && P.ckpt) {
+            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (P.nchunk + 1) + P.nchunk) * 64 + row) * 64);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(v + 8 * c8);
+        }
+    }
+    if (aborted && P.status && tid == 0) atomicOr(P.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tm, FWD_TMEM_COLS);
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// host side
+
+bool chunked_supported(const wkv_args_t *a, bool per_token_w) {
+    if (a->dtype != WKV_BF16 || a->N != 64 || a->T <= 0) return false;
+    if (per_token_w && a->w_kind != WKV_W_RAW) return false;  // fp32 ew tensor: scalar path
+    return true;
+}
+
+// workspace layout: [0,256) status words ; then what the call needs
+size_t chunked_forward_workspace(const wkv_args_t *, bool) { return 256; }
+size_t chunked_backward_workspace(const wkv_args_t *a, bool) {
+    return 256 + scalar_backward_workspace(a);
+}
+
+int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
+    const int B = a->B, T = a->T, H = a->H, C = H * 64;
+    CUtensorMap mr, mk, mv, mw;
+    if (!make_btc_map(&mr, a->r, B, T, C) || !make_btc_map(&mk, a->k, B, T, C) ||
+        !make_btc_map(&mv, a->v, B, T, C))
+        return WKV_ERR_LAUNCH;
+    if (per_token_w) {
+        if (!make_btc_map(&mw, a->w, B, T, C)) return WKV_ERR_LAUNCH;
+    } else {
+        mw = mr;
+    }
+    FwdParams p;
+    p.T = T; p.H = H; p.nchunk = (T + CH - 1) / CH; p.layout = a->state_layout; p.w_kind = a->w_kind;
+    p.u = (const __nv_bfloat16 *)a->u;
+    p.wvec = per_token_w ? nullptr : (const float *)a->w;
+    p.state_in = a->state_in; p.state_out = a->state_out;
+    p.y = (__nv_bfloat16 *)a->y;
+    p.ckpt = nullptr;
+    p.status = (int *)a->workspace;
+    if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
+    const size_t smem = sizeof(FwdSmem) + 1024;
+    auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return WKV_ERR_LAUNCH;
+    kern<<<B * H, 128, smem, stream>>>(mr, mk, mv, mw, p);
+    return launch_status();
+}
+
+int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
+    // until the tensor-core backward lands the gradient runs on the token-serial kernel
+    if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
+    wkv_args_t b = *a;
+    b.workspace = (char *)a->workspace + 256;
+    b.workspace_bytes = a->workspace_bytes - 256;
+    return scalar_backward(&b, per_token_w, stream);
+}
+
 }  // namespace wkv

@@ -100,6 +100,12 @@ const char *wkv_error_string(int code) {
 
 const char *wkv_version(void) { return "wkv_b200 1 sm_100a"; }
 
+int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w) {
+    if (!a || a->B <= 0 || a->H <= 0 || a->T <= 0 || a->N != HEAD) return 0;
+    int err;
+    return use_chunked(a, per_token_w != 0, &err) ? 1 : 0;
+}
+
 size_t wkv5_forward_workspace(const wkv_args_t *a) { return fwd_ws(a, false); }
 size_t wkv5_backward_workspace(const wkv_args_t *a) { return bwd_ws(a, false); }
 int wkv5_forward(const wkv_args_t *a, void *stream) { return forward(a, false, stream); }

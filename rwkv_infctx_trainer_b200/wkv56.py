@@ -9,6 +9,20 @@ from . import _lib as L
 
 HEAD_SIZE = 64
 
+# Debug aid: when True every call synchronises and checks the status word the chunked
+# kernels keep at the start of their workspace (non-zero = a bounded device-side wait ran
+# out and the kernel gave up).  Off by default: the ops never synchronise on their own.
+CHECK_STATUS = False
+
+
+def _check_status(lib, a, variant, ws, what):
+    if (CHECK_STATUS and ws is not None and ws.numel() >= 4
+            and lib.wkv56_uses_chunked(ctypes.byref(a), int(variant == "wkv6"))):
+        torch.cuda.synchronize(ws.device)
+        code = int(ws[:4].view(torch.int32).item())
+        if code != 0:
+            raise RuntimeError(f"{what}: device-side wait timed out (status {code})")
+
 
 def _args(variant, B, T, H, dtype, w_kind, layout, path, **t) -> L.WkvArgs:
     a = L.WkvArgs()
@@ -43,6 +57,7 @@ def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE
         ws = _with_workspace(lib, variant, "forward", a, dev)
         L.check(getattr(lib, f"{variant}_forward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_forward")
+        _check_status(lib, a, variant, ws, f"{variant}_forward")
         del ws
     return y, state_out
 
@@ -70,5 +85,6 @@ def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
         ws = _with_workspace(lib, variant, "backward", a, dev)
         L.check(getattr(lib, f"{variant}_backward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_backward")
+        _check_status(lib, a, variant, ws, f"{variant}_backward")
         del ws
     return gr, gk, gv, gw, gu, gsi
