@@ -15,78 +15,13 @@
 // All contractions run on tcgen05.mma (M=64, bf16 operands in 128-byte-swizzled
 // shared-memory tiles, fp32 accumulators in tensor memory); input tiles arrive by
 // TMA; the fp32 state lives in tensor memory for the whole segment.
-#include "sm100_primitives.cuh"
-#include "tma_host.cuh"
-#include "wkv_common.cuh"
+#include "wkv56_chunked.cuh"
 
 namespace wkv {
 namespace {
 
 using namespace sm100;
-
-constexpr int CH = 64;            // tokens per chunk
-constexpr int HB = 32;            // tokens per block
-constexpr float LW_FLOOR = -5.298317367f;  // log(0.005)
-
-struct __align__(16) Tile { unsigned char b[TILE_BYTES]; };
-
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-__device__ __forceinline__ void unpack8(const uint4 &q, float *f) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-}
-__device__ __forceinline__ uint4 pack8(const float *f) {
-    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
-}
-__device__ __forceinline__ uint4 ld_tile(const Tile &t, int row, int chunk) {
-    return *reinterpret_cast<const uint4 *>(t.b + tile_off(row, chunk));
-}
-__device__ __forceinline__ void st_tile(Tile &t, int row, int chunk, const uint4 &v) {
-    *reinterpret_cast<uint4 *>(t.b + tile_off(row, chunk)) = v;
-}
-
-// ---------------------------------------------------------------------------
-// Per-chunk operand preparation.  Thread layout (128 threads): 16-byte column
-// `cc` = 2*warp + (lane>>4) (8 channels), token group tg = lane & 15 (4 tokens).
-// Everything a thread computes concerns tokens 4*tg..4*tg+3 of channels 8*cc..+7.
-struct Prep {
-    float c[4][8];    // inclusive cumulative log-decay
-    float lw[4][8];   // per-token log-decay (floored), 0 for tokens past the segment end
-    float m0[8], m1[8], e0[8], e1[8];
-};
-
-// lw filled by the caller; computes the chunk-wide cumulative sums by a local scan
-// plus a 16-lane segmented warp scan, then the four reference values.
-__device__ __forceinline__ void prep_scan(Prep &p, int lane) {
-    const int tg = lane & 15;
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        p.c[0][ch] = p.lw[0][ch];
-#pragma unroll
-        for (int i = 1; i < 4; i++) p.c[i][ch] = p.c[i - 1][ch] + p.lw[i][ch];
-        float tot = p.c[3][ch];
-#pragma unroll
-        for (int off = 1; off < 16; off <<= 1) {
-            const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
-            if (tg >= off) tot += o;
-        }
-        const float excl = tot - p.c[3][ch];
-#pragma unroll
-        for (int i = 0; i < 4; i++) p.c[i][ch] += excl;
-        // inclusive sums at tokens 15, 31, 47, 63 live in lanes tg = 3, 7, 11, 15
-        p.m0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 3, 16);
-        p.e0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 7, 16);
-        p.m1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 11, 16);
-        p.e1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 15, 16);
-    }
-}
+using namespace chunked;
 
 // ---------------------------------------------------------------------------
 // Forward: one CTA per (batch, head), serial over the chunks of the segment.
@@ -102,7 +37,7 @@ struct FwdSmem {
 };
 
 struct FwdParams {
-    int T, H, nchunk, layout, w_kind;
+    int T, H, nchunk, layout, w_kind, state_only;
     const __nv_bfloat16 *u;
     const float *wvec;        // v5: per-channel decay parameter [H*64]
     const float *state_in;
@@ -179,6 +114,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
     }
 
+    const bool full = P.state_only == 0;
     uint32_t mma_phase = 0;
     int fail = 0;        // a bounded wait ran out (carried through the next barrier)
     int aborted = 0;
@@ -247,12 +183,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     rh[ch] = r * frh; kh[ch] = k * fkh;
                     dsum += r * uu[ch] * k;
                 }
-                st_tile(in[0], t, cc, pack8(rt));
-                st_tile(in[1], t, cc, pack8(kt));
-                st_tile(in[3], t, cc, pack8(rh));
-                st_tile(s.x, t, cc, pack8(xx));
+                if (full) {
+                    st_tile(in[0], t, cc, pack8(rt));
+                    st_tile(in[1], t, cc, pack8(kt));
+                    st_tile(in[3], t, cc, pack8(rh));
+                    st_tile(s.x, t, cc, pack8(xx));
+                    s.dpart[cc][t] = dsum;
+                }
                 st_tile(s.khat, t, cc, pack8(kh));
-                s.dpart[cc][t] = dsum;
             }
         }
         fence_async_smem();
@@ -260,7 +198,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (__syncthreads_or(fail)) { aborted = 1; break; }
 
         // ------------------------------------------- scores: A1 = Rt Kt^T, A2 = X X[0:32]^T
-        if (tid == 0) {
+        if (tid == 0 && full) {
             tc_fence_after();
             const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
 #pragma unroll
@@ -299,12 +237,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
         }
         tmem_st_wait();
-        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
-        mma_phase ^= 1;
-        tc_fence_after();
+        if (full) {
+            if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
+            mma_phase ^= 1;
+            tc_fence_after();
+        }
 
         // ------------------------------------------------------- mask pass
-        {
+        if (full) {
             const int t = row;
             float a[64];
 #pragma unroll
@@ -338,12 +278,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (tid == 0) {
             tc_fence_after();
             const uint32_t id_km = make_idesc(64, 64, false, true), id_mm = make_idesc(64, 64, true, true);
+            if (full) {
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_Y, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k), id_km, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm + COL_Y, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k), id_km, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_Y, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k), id_km, true);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm + COL_Y, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k), id_km, true);
+            }
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm + COL_S, desc_mnmajor(&s.khat, 0, k), desc_mnmajor(&in[2], 0, k), id_mm, true);
@@ -354,7 +296,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tc_fence_after();
 
         // -------------------------------------------------------- epilogue
-        {
+        if (full) {
             const int t = j * CH + row;
             float yv[64];
 #pragma unroll
@@ -416,11 +358,8 @@ bool chunked_supported(const wkv_args_t *a, bool per_token_w) {
 
 // workspace layout: [0,256) status words ; then what the call needs
 size_t chunked_forward_workspace(const wkv_args_t *, bool) { return 256; }
-size_t chunked_backward_workspace(const wkv_args_t *a, bool) {
-    return 256 + scalar_backward_workspace(a);
-}
 
-int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
+int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, cudaStream_t stream) {
     const int B = a->B, T = a->T, H = a->H, C = H * 64;
     CUtensorMap mr, mk, mv, mw;
     if (!make_btc_map(&mr, a->r, B, T, C) || !make_btc_map(&mk, a->k, B, T, C) ||
@@ -433,13 +372,13 @@ int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) 
     }
     FwdParams p;
     p.T = T; p.H = H; p.nchunk = (T + CH - 1) / CH; p.layout = a->state_layout; p.w_kind = a->w_kind;
+    p.state_only = a->y == nullptr;
     p.u = (const __nv_bfloat16 *)a->u;
     p.wvec = per_token_w ? nullptr : (const float *)a->w;
     p.state_in = a->state_in; p.state_out = a->state_out;
     p.y = (__nv_bfloat16 *)a->y;
-    p.ckpt = nullptr;
+    p.ckpt = (__nv_bfloat16 *)state_ckpt;
     p.status = (int *)a->workspace;
-    if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
     const size_t smem = sizeof(FwdSmem) + 1024;
     auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -448,13 +387,9 @@ int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) 
     return launch_status();
 }
 
-int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
-    // until the tensor-core backward lands the gradient runs on the token-serial kernel
+int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
     if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
-    wkv_args_t b = *a;
-    b.workspace = (char *)a->workspace + 256;
-    b.workspace_bytes = a->workspace_bytes - 256;
-    return scalar_backward(&b, per_token_w, stream);
+    return chunked_forward_impl(a, per_token_w, nullptr, stream);
 }
 
 }  // namespace wkv

@@ -1,0 +1,703 @@
+// Chunked tensor-core backward of the v5/v6 WKV recurrence (bf16 I/O, fp32 state).
+//
+// Three kernels per BPTT segment:
+//   1. the forward kernel in state-only mode writes S_j, the state at the start of
+//      every 64-token chunk (bf16);
+//   2. k_chunk_dscan runs the reverse recurrence  D_j = diag(e^{c_63}) D_{j+1} +
+//      (r e^{cp})^T gy  with D in tensor memory, writes every D_{j+1} (bf16) and
+//      the state gradient D_0;
+//   3. k_chunk_bwd handles every (batch, head, chunk) independently from S_j and
+//      D_{j+1}: recomputes the masked scores A, P = gy v^T, and from them
+//         gv = A^T gy + khat D
+//         gr = fr*(P~ Kt) + g*(P~ X) + e^{cp}*(gy S^T) + p_tt u k
+//         gk = fk*(P~^T Rt) + g*(P~^T X) + e^{c_63-c}*(v D^T) + p_tt u r
+//      (P~ = strictly lower part of P; Rt, Kt, X, khat the scaled operands of the
+//      forward kernel) with every product on tcgen05.mma, accumulators laid out
+//      [channel, token] so that one thread owns one channel over all 64 tokens.
+//
+// Decay gradient.  dL/d(log w_t)[k] = w_t sum_v S_t[k,v] D_{t+1}[k,v] expands into
+//   d sum_v S_j D_{j+1}  +  sum_{t'>t} qrS_t'  +  sum_{s<t} qkD_s  +  C_t,
+//   C_{t+1} = C_t + qkI_t - qrI_{t+1},
+// where qrS/qkD are the state parts of r*gr and k*gk and qrI/qkI their intra-chunk
+// parts.  C is a difference of large sums; it is exact only because qrI and qkI
+// are built from the SAME bf16-rounded factors (Rt * (P~ Kt) and Kt * (P~^T Rt)),
+// so the common terms cancel to fp32 rounding instead of to bf16 rounding.
+//
+// Math reference: RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:70-293 (what the
+// gradients are), RWKV-v6/src/module/rwkv_inner.py:48-113 (the chunked form).
+#include "wkv56_chunked.cuh"
+
+namespace wkv {
+namespace {
+
+using namespace sm100;
+using namespace chunked;
+
+// ----------------------------------------------------------------------------
+// dS scan
+
+struct DscanSmem {
+    Tile in[2][3];  // r (overwritten by r e^{cp}), gy, w
+    float dvec[CH];
+    uint64_t load_bar[2];
+    uint64_t mma_bar;
+    uint32_t tmem_base;
+};
+
+struct DscanParams {
+    int T, H, nchunk, layout, w_kind;
+    const float *wvec;
+    const float *gstate_out;
+    float *gstate_in;
+    __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
+    int *status;
+};
+
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(128)
+k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_gy,
+              const __grid_constant__ CUtensorMap map_w, const DscanParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H;
+    const bool active = (lane & 16) == 0;
+    const int row = warp * 16 + (lane & 15);
+    const uint32_t lane_base = (uint32_t)(warp * 32);
+    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+    const int n = P.nchunk;
+
+    if (tid == 0) {
+        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) { tmem_alloc(&s.tmem_base, 64); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s.tmem_base;
+
+    // step i = 0..n-1 handles chunk j = n-1-i
+    auto issue_load = [&](int i) {
+        const int st = i & 1, j = n - 1 - i;
+        mbar_expect_tx(&s.load_bar[st], (PER_TOKEN ? 3 : 2) * TILE_BYTES);
+        tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
+        tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
+        if (PER_TOKEN) tma_load_3d(&s.in[st][2], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+    };
+    if (tid == 0 && n > 0) issue_load(0);
+
+    const size_t sbase = (size_t)bh * 64 * 64;
+    {
+        float v[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) {
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
+            v[j] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
+        }
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, c0), v + c0);
+    }
+    tmem_st_wait();
+
+    float lwc[8];
+    if (!PER_TOKEN) {
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            const float x = P.wvec[h * 64 + cc * 8 + ch];
+            lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+        }
+    }
+
+    uint32_t mma_phase = 0;
+    int fail = 0, aborted = 0, issued = n > 0 ? 0 : -1, landed = -1;
+    tc_fence_before();
+    __syncthreads();
+
+    for (int i = 0; i < n; i++) {
+        const int st = i & 1, j = n - 1 - i;
+        Tile *in = s.in[st];
+        if (i + 1 < n) {
+            if (tid == 0) issue_load(i + 1);
+            issued = i + 1;
+        }
+        if (mbar_wait(&s.load_bar[st], (uint32_t)((i >> 1) & 1))) landed = i; else fail = 1;
+
+        {   // r e^{cp}, chunk decay
+            Prep p;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int t = 4 * tg + q;
+                const bool valid = j * CH + t < P.T;
+                if (PER_TOKEN) {
+                    float x[8];
+                    unpack8(ld_tile(in[2], t, cc), x);
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++)
+                        p.lw[q][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) p.lw[q][ch] = valid ? lwc[ch] : 0.f;
+                }
+            }
+            prep_scan(p, lane);
+            if (tg == 0) {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int t = 4 * tg + q;
+                float rr[8];
+                unpack8(ld_tile(in[0], t, cc), rr);
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) rr[ch] *= __expf(p.c[q][ch] - p.lw[q][ch]);
+                st_tile(in[0], t, cc, pack8(rr));
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(fail)) { aborted = 1; break; }
+        tc_fence_after();
+
+        {   // checkpoint D_{j+1}, decay it
+            float v[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, c0), v + c0);
+            tmem_ld_wait();
+            const float d = s.dvec[row];
+            if (active) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64);
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(v + 8 * c8);
+            }
+#pragma unroll
+            for (int c = 0; c < 64; c++) v[c] *= d;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, c0), v + c0);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t id = make_idesc(64, 64, true, true);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k), id, true);
+            mma_commit(&s.mma_bar);
+        }
+        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
+        mma_phase ^= 1;
+        tc_fence_after();
+        tc_fence_before();
+        if (__syncthreads_or(fail)) { aborted = 1; break; }
+    }
+    if (aborted) {
+        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
+    }
+    tc_fence_after();
+    {
+        float v[64];
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, c0), v + c0);
+        tmem_ld_wait();
+        if (active && !aborted && P.gstate_in) {
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
+                P.gstate_in[sbase + idx] = v[j];
+            }
+        }
+    }
+    if (aborted && P.status && tid == 0) atomicOr(P.status, 2);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tm, 64);
+}
+
+// ----------------------------------------------------------------------------
+// per-chunk gradients
+
+enum { T_R = 0, T_K, T_V, T_W, T_GY, T_S, T_D, N_IN };
+
+struct BwdSmem {
+    Tile in[N_IN];                       // raw r, k, v, w, gy; S_j, D_{j+1}
+    Tile rt, kt, x, rhat, khat;          // scaled operands
+    Tile f_r, f_k, f_g, f_rh, f_kh;      // the scale factors themselves (bf16)
+    Tile atil, ptil;                     // masked scores A (with diagonal), P~
+    float dpart[8][CH];
+    float ptt[CH];
+    float dvec[CH];
+    uint64_t load_bar;
+    uint64_t mma_bar;
+    uint32_t tmem_base;
+};
+
+struct BwdParams {
+    int T, H, nchunk, w_kind;
+    const __nv_bfloat16 *u;
+    const float *wvec;
+    float *gu_part;   // [B*H, nchunk, 64]
+    float *gw_part;   // v5 only: [B*H, nchunk, 64]
+    int *status;
+};
+
+// tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31
+enum { C_A1 = 0, C_A2 = 64, C_P = 0,                                  // phase 1 (P in hi)
+       C_G1 = 0, C_G2 = 64, C_GS = 96, C_GV = 160, BWD_TMEM_COLS = 256 };  // phase 2
+
+__device__ __forceinline__ float ld_bf(const Tile &t, int row, int col) {
+    const unsigned short h =
+        *reinterpret_cast<const unsigned short *>(t.b + tile_off(row, col >> 3) + ((col & 7) << 1));
+    return __uint_as_float((uint32_t)h << 16);
+}
+__device__ __forceinline__ void st_bf(Tile &t, int row, int col, float v) {
+    *reinterpret_cast<__nv_bfloat16 *>(t.b + tile_off(row, col >> 3) + ((col & 7) << 1)) = __float2bfloat16_rn(v);
+}
+
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(128)
+k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
+            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
+            const __grid_constant__ CUtensorMap map_gy, const __grid_constant__ CUtensorMap map_s,
+            const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_gr,
+            const __grid_constant__ CUtensorMap map_gk, const __grid_constant__ CUtensorMap map_gv,
+            const __grid_constant__ CUtensorMap map_gw, const BwdParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    BwdSmem &s = *reinterpret_cast<BwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n = P.nchunk;
+    const int bh = blockIdx.x / n, j = blockIdx.x % n, b = bh / P.H, h = bh % P.H;
+    const bool lo = (lane & 16) == 0;
+    const int row = warp * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
+    const uint32_t lane_base = (uint32_t)(warp * 32);
+    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+
+    if (tid == 0) {
+        mbar_init(&s.load_bar, 1); mbar_init(&s.mma_bar, 1);
+        fence_mbar_init();
+        mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
+        tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
+        tma_load_3d(&s.in[T_K], &map_k, &s.load_bar, h * 64, j * CH, b);
+        tma_load_3d(&s.in[T_V], &map_v, &s.load_bar, h * 64, j * CH, b);
+        if (PER_TOKEN) tma_load_3d(&s.in[T_W], &map_w, &s.load_bar, h * 64, j * CH, b);
+        tma_load_3d(&s.in[T_GY], &map_gy, &s.load_bar, h * 64, j * CH, b);
+        tma_load_3d(&s.in[T_S], &map_s, &s.load_bar, 0, 0, bh * (n + 1) + j);
+        tma_load_3d(&s.in[T_D], &map_d, &s.load_bar, 0, 0, bh * (n + 1) + j + 1);
+    }
+    if (warp == 0) { tmem_alloc(&s.tmem_base, BWD_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s.tmem_base;
+    const uint32_t tm_lo = tm, tm_hi = tm + (16u << 16);
+
+    float uu[8], lwc[8];
+    unpack8(*reinterpret_cast<const uint4 *>(P.u + h * 64 + cc * 8), uu);
+    if (!PER_TOKEN) {
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            const float x = P.wvec[h * 64 + cc * 8 + ch];
+            lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+        }
+    }
+    int fail = 0;
+    if (!mbar_wait(&s.load_bar, 0)) fail = 1;
+
+    // ---------------------------------------------------------------- prep
+    {
+        Prep p;
+        float rr[4][8], kk[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int t = 4 * tg + i;
+            unpack8(ld_tile(s.in[T_R], t, cc), rr[i]);
+            unpack8(ld_tile(s.in[T_K], t, cc), kk[i]);
+            const bool valid = j * CH + t < P.T;
+            if (PER_TOKEN) {
+                float x[8];
+                unpack8(ld_tile(s.in[T_W], t, cc), x);
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++)
+                    p.lw[i][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+            }
+        }
+        prep_scan(p, lane);
+        const bool blk1 = tg >= 8;
+        float ee0[8], ee10[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            ee0[ch] = __expf(p.e0[ch]);
+            ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
+        }
+        if (tg == 0) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int t = 4 * tg + i;
+            float rt[8], kt[8], xx[8], rh[8], kh[8], vfr[8], vfk[8], vg[8], vrh[8], vkh[8];
+            float dsum = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const float c = p.c[i][ch], cp = c - p.lw[i][ch];
+                const float mb = blk1 ? p.m1[ch] : p.m0[ch];
+                const float fr = __expf(cp - mb), fk = __expf(mb - c);
+                const float g = blk1 ? __expf(cp - p.e0[ch]) : __expf(p.e0[ch] - c);
+                const float frh = blk1 ? g * ee0[ch] : __expf(cp);
+                const float fkh = blk1 ? __expf(p.e1[ch] - c) : g * ee10[ch];
+                const float r = rr[i][ch], k = kk[i][ch];
+                rt[ch] = r * fr; kt[ch] = k * fk;
+                xx[ch] = (blk1 ? r : k) * g;
+                rh[ch] = r * frh; kh[ch] = k * fkh;
+                vfr[ch] = fr; vfk[ch] = fk; vg[ch] = g; vrh[ch] = frh; vkh[ch] = fkh;
+                dsum += r * uu[ch] * k;
+            }
+            st_tile(s.rt, t, cc, pack8(rt));
+            st_tile(s.kt, t, cc, pack8(kt));
+            st_tile(s.x, t, cc, pack8(xx));
+            st_tile(s.rhat, t, cc, pack8(rh));
+            st_tile(s.khat, t, cc, pack8(kh));
+            st_tile(s.f_r, t, cc, pack8(vfr));
+            st_tile(s.f_k, t, cc, pack8(vfk));
+            st_tile(s.f_g, t, cc, pack8(vg));
+            st_tile(s.f_rh, t, cc, pack8(vrh));
+            st_tile(s.f_kh, t, cc, pack8(vkh));
+            s.dpart[cc][t] = dsum;
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    const int abort1 = __syncthreads_or(fail);
+
+    // ------------------------------------------------- phase 1: A1, A2, P
+    if (!abort1 && tid == 0) {
+        tc_fence_after();
+        const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            mma_ss(tm_lo + C_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
+        mma_commit(&s.mma_bar);
+    }
+    if (!abort1 && !mbar_wait(&s.mma_bar, 0)) fail = 1;
+    tc_fence_after();
+
+    // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t)
+    {
+        const int t = row;
+        float a[64], a2[32];
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_A1 + c0), a + c0);
+        tmem_ld16(tmem_addr(tm, lane_base, C_A2), a2);
+        tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
+        tmem_ld_wait();
+        if (lo) {
+            float diag = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; q++) diag += s.dpart[q][t];
+#pragma unroll
+            for (int sx = 0; sx < 64; sx++) {
+                float val;
+                if (sx == t) val = diag;
+                else if (sx > t) val = 0.f;
+                else if (t >= HB && sx < HB) val = a2[sx & 31];
+                else val = a[sx];
+                a[sx] = val;
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) st_tile(s.atil, t, c8, pack8(a + 8 * c8));
+        } else {
+            float pd = 0.f;
+#pragma unroll
+            for (int sx = 0; sx < 64; sx++) {
+                if (sx == t) pd = a[sx];
+                a[sx] = sx < t ? a[sx] : 0.f;
+            }
+            s.ptt[t] = pd;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) st_tile(s.ptil, t, c8, pack8(a + 8 * c8));
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    const int abort2 = __syncthreads_or(fail) | abort1;
+
+    // ------------------------------------------------- phase 2
+    if (!abort2 && tid == 0) {
+        tc_fence_after();
+        // gv^T[v,s] = gy^T A~ + D^T khat^T
+        {
+            const uint32_t id_mm = make_idesc(64, 64, true, true), id_mk = make_idesc(64, 64, true, false);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_lo + C_GV, desc_mnmajor(&s.in[T_GY], 0, k), desc_mnmajor(&s.atil, 0, k), id_mm, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_lo + C_GV, desc_mnmajor(&s.in[T_D], 0, k), desc_kmajor(&s.khat, 0, k), id_mk, true);
+        }
+        const uint32_t id_mk32 = make_idesc(64, 32, true, false), id_mm32 = make_idesc(64, 32, true, true);
+        const uint32_t id_kk64 = make_idesc(64, 64, false, false);
+        // gr intra, same block: G1[k,t] = sum_{s in blk} Kt[s,k] P~[t,s]
+#pragma unroll
+        for (int bl = 0; bl < 2; bl++)
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+                mma_ss(tm_lo + C_G1 + 32 * bl, desc_mnmajor(&s.kt, 32 * bl, kk),
+                       desc_kmajor(&s.ptil, 32 * bl, 2 * bl + kk), id_mk32, kk > 0);
+        // gr intra, across blocks: G2[k, t in blk1] = sum_{s<32} X[s,k] P~[t,s]
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++)
+            mma_ss(tm_lo + C_G2, desc_mnmajor(&s.x, 0, kk), desc_kmajor(&s.ptil, 32, kk), id_mk32, kk > 0);
+        // gr state part: GS[k,t] = sum_v S[k,v] gy[t,v]
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            mma_ss(tm_lo + C_GS, desc_kmajor(&s.in[T_S], 0, k), desc_kmajor(&s.in[T_GY], 0, k), id_kk64, k > 0);
+        // gk intra, same block: G1[k,s] = sum_{t in blk} Rt[t,k] P~[t,s]
+#pragma unroll
+        for (int bl = 0; bl < 2; bl++)
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+                mma_ss(tm_hi + C_G1 + 32 * bl, desc_mnmajor(&s.rt, 32 * bl, kk),
+                       desc_mnmajor(&s.ptil, 32 * bl, kk) + (bl ? 4 : 0), id_mm32, kk > 0);
+        // gk intra, across blocks: G2[k, s<32] = sum_{t>=32} X[t,k] P~[t,s]
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++)
+            mma_ss(tm_hi + C_G2, desc_mnmajor(&s.x, 32, kk), desc_mnmajor(&s.ptil, 32, kk), id_mm32, kk > 0);
+        // gk state part: GS[k,s] = sum_v D[k,v] v[s,v]
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            mma_ss(tm_hi + C_GS, desc_kmajor(&s.in[T_D], 0, k), desc_kmajor(&s.in[T_V], 0, k), id_kk64, k > 0);
+        mma_commit(&s.mma_bar);
+    }
+
+    // while the tensor core works: T1 = d * sum_v S[k,v] D[k,v] (lo lanes)
+    const int kch = row;   // channel owned in the epilogue
+    float T1 = 0.f;
+    if (lo) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; c8++) {
+            float a[8], d[8];
+            unpack8(ld_tile(s.in[T_S], kch, c8), a);
+            unpack8(ld_tile(s.in[T_D], kch, c8), d);
+#pragma unroll
+            for (int q = 0; q < 8; q++) T1 += a[q] * d[q];
+        }
+        T1 *= s.dvec[kch];
+    }
+    const float uk = __bfloat162float(P.u[h * 64 + kch]);
+    float lw_static = 0.f;
+    bool static_live = true;
+    if (!PER_TOKEN) {
+        const float x = P.wvec[h * 64 + kch];
+        const float l = P.w_kind == WKV_W_RAW ? -__expf(x) : x;
+        static_live = l >= LW_FLOOR;
+        lw_static = fmaxf(l, LW_FLOOR);
+    }
+
+    if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
+    tc_fence_after();
+
+    // ------------------------------------------------- epilogue: gr (lo lanes), gk (hi lanes), gw
+    // output staging reuses tiles whose last reader was phase 2: gr->atil, gk->ptil, gw->v, gv->gy
+    Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
+    {
+        // state part of r*gr summed over the whole chunk (needed for the suffix sums)
+        float totS = 0.f;
+        {
+            float gs[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_GS + c0), gs + c0);
+            tmem_ld_wait();
+            if (lo) {
+#pragma unroll
+                for (int t = 0; t < 64; t++) totS += ld_bf(s.rhat, t, kch) * gs[t];
+            }
+        }
+        float prefS = 0.f, preD = 0.f, C = 0.f, prev_qkI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
+#pragma unroll 1
+        for (int t0 = 0; t0 < 64; t0 += 16) {
+            float g1[16], g2[16], gs[16];
+            tmem_ld16(tmem_addr(tm, lane_base, C_G1 + t0), g1);
+            tmem_ld16(tmem_addr(tm, lane_base, C_GS + t0), gs);
+            // G2 exists for tokens 32..63 on the gr side (columns t-32) and 0..31 on the gk side
+            tmem_ld16(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
+            tmem_ld_wait();
+            const bool has2 = lo ? (t0 >= HB) : (t0 < HB);
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+                const int t = t0 + q;
+                const float pt = s.ptt[t];
+                const float xt = ld_bf(s.x, t, kch), fg = ld_bf(s.f_g, t, kch);
+                const float rraw = ld_bf(s.in[T_R], t, kch), kraw = ld_bf(s.in[T_K], t, kch);
+                const float b2 = has2 ? g2[q] : 0.f;
+                float qI, qS, out;
+                if (lo) {
+                    const float rtv = ld_bf(s.rt, t, kch), rhv = ld_bf(s.rhat, t, kch);
+                    qI = rtv * g1[q] + xt * b2;
+                    qS = rhv * gs[q];
+                    out = ld_bf(s.f_r, t, kch) * g1[q] + fg * b2 + ld_bf(s.f_rh, t, kch) * gs[q] + pt * uk * kraw;
+                } else {
+                    const float ktv = ld_bf(s.kt, t, kch), khv = ld_bf(s.khat, t, kch);
+                    qI = ktv * g1[q] + xt * b2;
+                    qS = khv * gs[q];
+                    out = ld_bf(s.f_k, t, kch) * g1[q] + fg * b2 + ld_bf(s.f_kh, t, kch) * gs[q] + pt * uk * rraw;
+                    gu_acc += pt * rraw * kraw;
+                }
+                // the gk lane hands its two terms to the gr lane of the same channel
+                const float o_qI = __shfl_xor_sync(0xffffffffu, qI, 16);
+                const float o_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
+                if (lo) {
+                    st_bf(o_gr, t, kch, out);
+                    C += prev_qkI - qI;
+                    prefS += qS;
+                    const float glw = T1 + (totS - prefS) + preD + C;
+                    preD += o_qS;
+                    prev_qkI = o_qI;
+                    if (PER_TOKEN) {
+                        const float xraw = ld_bf(s.in[T_W], t, kch);
+                        const float l = P.w_kind == WKV_W_RAW ? -__expf(xraw) : xraw;
+                        st_bf(o_gw, t, kch, l >= LW_FLOOR ? glw * l : 0.f);
+                    } else if (j * CH + t < P.T) {
+                        gw_acc += glw;
+                    }
+                } else {
+                    st_bf(o_gk, t, kch, out);
+                }
+            }
+        }
+        if (!lo) P.gu_part[((size_t)bh * n + j) * 64 + kch] = gu_acc;
+        if (!PER_TOKEN && lo) P.gw_part[((size_t)bh * n + j) * 64 + kch] = static_live ? gw_acc * lw_static : 0.f;
+    }
+    // gv: accumulator [v, s]; lo lanes own value channel v
+    {
+        float gv[64];
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_GV + c0), gv + c0);
+        tmem_ld_wait();
+        if (lo) {
+#pragma unroll
+            for (int t = 0; t < 64; t++) st_bf(o_gv, t, kch, gv[t]);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    const int abort3 = __syncthreads_or(fail) | abort2;
+    if (!abort3 && tid == 0) {
+        tma_store_3d(&map_gr, &o_gr, h * 64, j * CH, b);
+        tma_store_3d(&map_gk, &o_gk, h * 64, j * CH, b);
+        tma_store_3d(&map_gv, &o_gv, h * 64, j * CH, b);
+        if (PER_TOKEN) tma_store_3d(&map_gw, &o_gw, h * 64, j * CH, b);
+        tma_store_commit();
+        tma_store_wait_all();
+    }
+    if (abort3 && P.status && tid == 0) atomicOr(P.status, 4);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
+}
+
+// sum the per-chunk partials: out[bh*64 + k] = sum_j part[(bh*n + j)*64 + k]
+__global__ void k_reduce_partials(const float *__restrict__ part, float *__restrict__ out, int n, int total) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int bh = i >> 6, k = i & 63;
+    float acc = 0.f;
+    for (int j = 0; j < n; j++) acc += part[((size_t)bh * n + j) * 64 + k];
+    out[i] = acc;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct BwdLayout {
+    size_t status, sck, dck, gu_part, gw_part, total;
+};
+BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
+    const size_t n = (a->T + CH - 1) / CH, bh = (size_t)a->B * a->H;
+    BwdLayout L;
+    L.status = 0;
+    L.sck = 256;
+    L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
+    L.gu_part = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
+    L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
+    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
+    return L;
+}
+
+}  // namespace
+
+size_t chunked_backward_workspace(const wkv_args_t *a, bool per_token_w) { return bwd_layout(a, per_token_w).total; }
+
+int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
+    const int B = a->B, T = a->T, H = a->H, C = H * 64, n = (T + CH - 1) / CH;
+    const BwdLayout L = bwd_layout(a, per_token_w);
+    char *ws = (char *)a->workspace;
+    if (cudaMemsetAsync(ws, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
+    void *sck = ws + L.sck, *dck = ws + L.dck;
+    float *gu_part = (float *)(ws + L.gu_part), *gw_part = (float *)(ws + L.gw_part);
+
+    // 1. chunk-start states
+    {
+        wkv_args_t f = *a;
+        f.y = nullptr;
+        f.state_out = nullptr;
+        const int err = chunked_forward_impl(&f, per_token_w, sck, stream);
+        if (err != WKV_OK) return err;
+    }
+    CUtensorMap mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw;
+    bool ok = make_btc_map(&mr, a->r, B, T, C) && make_btc_map(&mk, a->k, B, T, C) &&
+              make_btc_map(&mv, a->v, B, T, C) && make_btc_map(&mgy, a->gy, B, T, C) &&
+              make_btc_map(&mgr, a->gr, B, T, C) && make_btc_map(&mgk, a->gk, B, T, C) &&
+              make_btc_map(&mgv, a->gv, B, T, C) && make_btc_map(&ms, sck, B * H * (n + 1), 64, 64) &&
+              make_btc_map(&md, dck, B * H * (n + 1), 64, 64);
+    if (per_token_w) ok = ok && make_btc_map(&mw, a->w, B, T, C) && make_btc_map(&mgw, a->gw, B, T, C);
+    else { mw = mr; mgw = mgr; }
+    if (!ok) return WKV_ERR_LAUNCH;
+
+    // 2. dS scan
+    {
+        DscanParams p;
+        p.T = T; p.H = H; p.nchunk = n; p.layout = a->state_layout; p.w_kind = a->w_kind;
+        p.wvec = per_token_w ? nullptr : (const float *)a->w;
+        p.gstate_out = a->gstate_out; p.gstate_in = a->gstate_in;
+        p.dck = (__nv_bfloat16 *)dck; p.status = (int *)ws;
+        const size_t smem = sizeof(DscanSmem) + 1024;
+        auto kern = per_token_w ? k_chunk_dscan<true> : k_chunk_dscan<false>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return WKV_ERR_LAUNCH;
+        kern<<<B * H, 128, smem, stream>>>(mr, mgy, mw, p);
+        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+    }
+    // 3. per-chunk gradients
+    {
+        BwdParams p;
+        p.T = T; p.H = H; p.nchunk = n; p.w_kind = a->w_kind;
+        p.u = (const __nv_bfloat16 *)a->u;
+        p.wvec = per_token_w ? nullptr : (const float *)a->w;
+        p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
+        const size_t smem = sizeof(BwdSmem) + 1024;
+        auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return WKV_ERR_LAUNCH;
+        kern<<<B * H * n, 128, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
+        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+    }
+    // 4. fold the per-chunk partial sums
+    {
+        const int total = B * H * 64;
+        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, n, total);
+        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, n, total);
+    }
+    return launch_status();
+}
+
+}  // namespace wkv

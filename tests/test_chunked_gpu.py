@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
 FLOOR = 0.005
 # outputs held to the floored oracle in the decay-extremes test
-EXTREME_CHECKED = ("y", "state_out")
+EXTREME_CHECKED = ("y", "state_out", "gr", "gk", "gv", "gw", "gu", "gstate_in")
 
 
 def _pkg():
