@@ -183,6 +183,8 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     wl = dict(WORKLOAD)
+    if args.small:
+        wl.update(name=wl["name"] + "_small", B=1, T=4096)
     B, T, C, H = wl["B"], wl["T"], wl["C"], wl["H"]
     host, dev = make_inputs(wl, device, pinned_host=True)
     # the op takes contiguous [B,T_seg,C] tensors: lay the segments out once, outside the timing
@@ -247,13 +249,16 @@ def run_ours(args):
     h2d = sum(s.numel() * s.element_size() for n in hseg for s in hseg[n])
     d2h = sum(s.numel() * s.element_size() for n in out_host for s in out_host[n])
     e2e_steps = max(1, min(args.steps, 3))
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    if args.skip_e2e:
+        e2e_s = float("nan")
+    else:
         e2e_step()
-    barrier()
-    e2e_s = time.perf_counter() - t0
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
 
     times = torch.tensor([ms, e2e_s * 1e3], device=device, dtype=torch.float64)
     if dist is not None:
@@ -295,7 +300,7 @@ def run_ours(args):
             "whole_step_roofline_frac": (
                 (FWD_ELEMS + BWD_ELEMS) * 2 * B * T * C / (ms / args.steps * 1e-3) / 1e9 / hbm),
         }
-        if world == 1:
+        if world == 1 and not args.skip_cpu:
             line["cpu_baseline"] = cpu_baseline(steps=8, warmup=1)
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -366,6 +371,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true",
+                    help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
+                         "still larger than L2) instead of the benchmark workload")
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: no end-to-end leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

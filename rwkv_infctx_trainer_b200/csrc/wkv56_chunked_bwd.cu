@@ -25,6 +25,8 @@
 //
 // Math reference: RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:70-293 (what the
 // gradients are), RWKV-v6/src/module/rwkv_inner.py:48-113 (the chunked form).
+#include <cstdlib>
+
 #include "wkv56_chunked.cuh"
 
 namespace wkv {
@@ -221,18 +223,21 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
 
 enum { T_R = 0, T_K, T_V, T_W, T_GY, T_S, T_D, N_IN };
 
+// 14 tiles + 1 KiB: two CTAs fit in one SM's shared memory.
 struct BwdSmem {
-    Tile in[N_IN];                       // raw r, k, v, w, gy; S_j, D_{j+1}
-    Tile rt, kt, x, rhat, khat;          // scaled operands
-    Tile f_r, f_k, f_g, f_rh, f_kh;      // the scale factors themselves (bf16)
-    Tile atil, ptil;                     // masked scores A (with diagonal), P~
-    float dpart[8][CH];
+    Tile in[N_IN];             // raw r, k, v, w, gy; S_j, D_{j+1}.  The w slot becomes rows
+                               // 0..31 of the cumulative-decay table once w has been read.
+    Tile rt, kt, x, khat;      // scaled operands
+    Tile atil, ptil;           // masked scores A (with diagonal), P~
+    Tile ctab_hi;              // rows 32..63 of the cumulative-decay table
     float ptt[CH];
-    float dvec[CH];
+    unsigned char live[CH][8]; // bit ch of live[t][cc]: decay of (t, 8cc+ch) is above the floor
     uint64_t load_bar;
     uint64_t mma_bar;
     uint32_t tmem_base;
 };
+
+static_assert(sizeof(BwdSmem) <= 115712, "two CTAs per SM need <= 113 KiB each");
 
 struct BwdParams {
     int T, H, nchunk, w_kind;
@@ -241,6 +246,7 @@ struct BwdParams {
     float *gu_part;   // [B*H, nchunk, 64]
     float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
+    long long *timeline;  // optional: clock stamps of one CTA (phase boundaries), or NULL
 };
 
 // tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31
@@ -255,17 +261,21 @@ __device__ __forceinline__ float ld_bf(const Tile &t, int row, int col) {
 __device__ __forceinline__ void st_bf(Tile &t, int row, int col, float v) {
     *reinterpret_cast<__nv_bfloat16 *>(t.b + tile_off(row, col >> 3) + ((col & 7) << 1)) = __float2bfloat16_rn(v);
 }
+// fp32 cumulative log-decay table c[t][k]: rows 0..31 in `a`, rows 32..63 in `b`
+__device__ __forceinline__ float *ctab_ptr(Tile &a, Tile &b, int t, int k) {
+    return reinterpret_cast<float *>((t < 32 ? a.b : b.b) + (t & 31) * 256) + k;
+}
 
 template <bool PER_TOKEN>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 2)
 k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
             const __grid_constant__ CUtensorMap map_gy, const __grid_constant__ CUtensorMap map_s,
             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_gr,
             const __grid_constant__ CUtensorMap map_gk, const __grid_constant__ CUtensorMap map_gv,
             const __grid_constant__ CUtensorMap map_gw, const BwdParams P) {
-    extern __shared__ unsigned char smem_raw[];
-    BwdSmem &s = *reinterpret_cast<BwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    BwdSmem &s = *reinterpret_cast<BwdSmem *>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n = P.nchunk;
     const int bh = blockIdx.x / n, j = blockIdx.x % n, b = bh / P.H, h = bh % P.H;
@@ -274,6 +284,13 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const uint32_t lane_base = (uint32_t)(warp * 32);
     const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
 
+    // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (tid == 0 && P.status) atomicOr(P.status, 8);
+        return;
+    }
+    const bool stamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && tid == 0;
+    if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
         mbar_init(&s.load_bar, 1); mbar_init(&s.mma_bar, 1);
         fence_mbar_init();
@@ -293,87 +310,88 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const uint32_t tm = s.tmem_base;
     const uint32_t tm_lo = tm, tm_hi = tm + (16u << 16);
 
-    float uu[8], lwc[8];
-    unpack8(*reinterpret_cast<const uint4 *>(P.u + h * 64 + cc * 8), uu);
+    float lwc[8];
+    bool livec[8];
     if (!PER_TOKEN) {
 #pragma unroll
         for (int ch = 0; ch < 8; ch++) {
             const float x = P.wvec[h * 64 + cc * 8 + ch];
-            lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+            const float l = P.w_kind == WKV_W_RAW ? -__expf(x) : x;
+            livec[ch] = l >= LW_FLOOR;
+            lwc[ch] = fmaxf(l, LW_FLOOR);
         }
     }
     int fail = 0;
+    if (stamp) P.timeline[1] = clock64();
     if (!mbar_wait(&s.load_bar, 0)) fail = 1;
+    if (stamp) P.timeline[2] = clock64();
 
     // ---------------------------------------------------------------- prep
     {
         Prep p;
         float rr[4][8], kk[4][8];
+        unsigned livebits[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = 4 * tg + i;
             unpack8(ld_tile(s.in[T_R], t, cc), rr[i]);
             unpack8(ld_tile(s.in[T_K], t, cc), kk[i]);
             const bool valid = j * CH + t < P.T;
+            livebits[i] = 0;
             if (PER_TOKEN) {
                 float x[8];
                 unpack8(ld_tile(s.in[T_W], t, cc), x);
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++)
-                    p.lw[i][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+                for (int ch = 0; ch < 8; ch++) {
+                    const float l = P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch];
+                    livebits[i] |= (l >= LW_FLOOR ? 1u : 0u) << ch;
+                    p.lw[i][ch] = valid ? fmaxf(l, LW_FLOOR) : 0.f;
+                }
             } else {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+                for (int ch = 0; ch < 8; ch++) {
+                    livebits[i] |= (livec[ch] ? 1u : 0u) << ch;
+                    p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+                }
             }
         }
+        __syncthreads();   // every w value has been read: its slot may now take the table
         prep_scan(p, lane);
         const bool blk1 = tg >= 8;
-        float ee0[8], ee10[8];
+        float ee10[8];
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            ee0[ch] = __expf(p.e0[ch]);
-            ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
-        }
-        if (tg == 0) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
-        }
+        for (int ch = 0; ch < 8; ch++) ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = 4 * tg + i;
-            float rt[8], kt[8], xx[8], rh[8], kh[8], vfr[8], vfk[8], vg[8], vrh[8], vkh[8];
-            float dsum = 0.f;
+            float rt[8], kt[8], xx[8], kh[8], cv[8];
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
                 const float c = p.c[i][ch], cp = c - p.lw[i][ch];
                 const float mb = blk1 ? p.m1[ch] : p.m0[ch];
                 const float fr = __expf(cp - mb), fk = __expf(mb - c);
                 const float g = blk1 ? __expf(cp - p.e0[ch]) : __expf(p.e0[ch] - c);
-                const float frh = blk1 ? g * ee0[ch] : __expf(cp);
                 const float fkh = blk1 ? __expf(p.e1[ch] - c) : g * ee10[ch];
                 const float r = rr[i][ch], k = kk[i][ch];
                 rt[ch] = r * fr; kt[ch] = k * fk;
                 xx[ch] = (blk1 ? r : k) * g;
-                rh[ch] = r * frh; kh[ch] = k * fkh;
-                vfr[ch] = fr; vfk[ch] = fk; vg[ch] = g; vrh[ch] = frh; vkh[ch] = fkh;
-                dsum += r * uu[ch] * k;
+                kh[ch] = k * fkh;
+                cv[ch] = c;
             }
             st_tile(s.rt, t, cc, pack8(rt));
             st_tile(s.kt, t, cc, pack8(kt));
             st_tile(s.x, t, cc, pack8(xx));
-            st_tile(s.rhat, t, cc, pack8(rh));
             st_tile(s.khat, t, cc, pack8(kh));
-            st_tile(s.f_r, t, cc, pack8(vfr));
-            st_tile(s.f_k, t, cc, pack8(vfk));
-            st_tile(s.f_g, t, cc, pack8(vg));
-            st_tile(s.f_rh, t, cc, pack8(vrh));
-            st_tile(s.f_kh, t, cc, pack8(vkh));
-            s.dpart[cc][t] = dsum;
+            float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
+            cdst[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
+            cdst[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
+            s.live[t][cc] = (unsigned char)livebits[i];
         }
     }
     fence_async_smem();
     tc_fence_before();
     const int abort1 = __syncthreads_or(fail);
+    if (stamp) P.timeline[3] = clock64();
 
     // ------------------------------------------------- phase 1: A1, A2, P
     if (!abort1 && tid == 0) {
@@ -390,8 +408,22 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
         mma_commit(&s.mma_bar);
     }
+    // meanwhile (lo lanes): the bonus term of the score diagonal, sum_k r_t u k_t
+    float diag = 0.f;
+    if (lo) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; c8++) {
+            float a[8], d[8], uq[8];
+            unpack8(ld_tile(s.in[T_R], row, c8), a);
+            unpack8(ld_tile(s.in[T_K], row, c8), d);
+            unpack8(__ldg(reinterpret_cast<const uint4 *>(P.u + h * 64) + c8), uq);
+#pragma unroll
+            for (int q = 0; q < 8; q++) diag += a[q] * uq[q] * d[q];
+        }
+    }
     if (!abort1 && !mbar_wait(&s.mma_bar, 0)) fail = 1;
     tc_fence_after();
+    if (stamp) P.timeline[4] = clock64();
 
     // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t)
     {
@@ -403,9 +435,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
         tmem_ld_wait();
         if (lo) {
-            float diag = 0.f;
-#pragma unroll
-            for (int q = 0; q < 8; q++) diag += s.dpart[q][t];
 #pragma unroll
             for (int sx = 0; sx < 64; sx++) {
                 float val;
@@ -432,6 +461,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     fence_async_smem();
     tc_fence_before();
     const int abort2 = __syncthreads_or(fail) | abort1;
+    if (stamp) P.timeline[5] = clock64();
 
     // ------------------------------------------------- phase 2
     if (!abort2 && tid == 0) {
@@ -481,9 +511,12 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         mma_commit(&s.mma_bar);
     }
 
-    // while the tensor core works: T1 = d * sum_v S[k,v] D[k,v] (lo lanes)
+    // while the tensor core works: per-channel constants
     const int kch = row;   // channel owned in the epilogue
-    float T1 = 0.f;
+    Tile &ct_lo = s.in[T_W], &ct_hi = s.ctab_hi;
+    const float m0 = *ctab_ptr(ct_lo, ct_hi, 15, kch), e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch);
+    const float m1 = *ctab_ptr(ct_lo, ct_hi, 47, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
+    float T1 = 0.f;   // d * sum_v S[k,v] D[k,v]
     if (lo) {
 #pragma unroll
         for (int c8 = 0; c8 < 8; c8++) {
@@ -493,7 +526,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 8; q++) T1 += a[q] * d[q];
         }
-        T1 *= s.dvec[kch];
+        T1 *= __expf(e1);
     }
     const float uk = __bfloat162float(P.u[h * 64 + kch]);
     float lw_static = 0.f;
@@ -507,11 +540,13 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
     if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
     tc_fence_after();
+    if (stamp) P.timeline[6] = clock64();
 
     // ------------------------------------------------- epilogue: gr (lo lanes), gk (hi lanes), gw
     // output staging reuses tiles whose last reader was phase 2: gr->atil, gk->ptil, gw->v, gv->gy
     Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
     {
+        const Tile &t_own = lo ? s.rt : s.kt;          // the scaled operand whose product with G1 is qI
         // state part of r*gr summed over the whole chunk (needed for the suffix sums)
         float totS = 0.f;
         {
@@ -520,11 +555,16 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_GS + c0), gs + c0);
             tmem_ld_wait();
             if (lo) {
+                float cprev = 0.f;
 #pragma unroll
-                for (int t = 0; t < 64; t++) totS += ld_bf(s.rhat, t, kch) * gs[t];
+                for (int t = 0; t < 64; t++) {
+                    totS += ld_bf(s.in[T_R], t, kch) * __expf(cprev) * gs[t];
+                    cprev = *ctab_ptr(ct_lo, ct_hi, t, kch);
+                }
             }
         }
         float prefS = 0.f, preD = 0.f, C = 0.f, prev_qkI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
+        float c_prev = 0.f;   // c_{t-1}
 #pragma unroll 1
         for (int t0 = 0; t0 < 64; t0 += 16) {
             float g1[16], g2[16], gs[16];
@@ -532,48 +572,67 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             tmem_ld16(tmem_addr(tm, lane_base, C_GS + t0), gs);
             // G2 exists for tokens 32..63 on the gr side (columns t-32) and 0..31 on the gk side
             tmem_ld16(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
-            tmem_ld_wait();
             const bool has2 = lo ? (t0 >= HB) : (t0 < HB);
+            const float mb = t0 >= HB ? m1 : m0;
+            // stage 1: every shared-memory read of this batch
+            float vown[16], vx[16], vr[16], vk[16], vc[16], vpt[16];
 #pragma unroll
             for (int q = 0; q < 16; q++) {
                 const int t = t0 + q;
-                const float pt = s.ptt[t];
-                const float xt = ld_bf(s.x, t, kch), fg = ld_bf(s.f_g, t, kch);
-                const float rraw = ld_bf(s.in[T_R], t, kch), kraw = ld_bf(s.in[T_K], t, kch);
+                vown[q] = ld_bf(t_own, t, kch);
+                vx[q] = ld_bf(s.x, t, kch);
+                vr[q] = ld_bf(s.in[T_R], t, kch);
+                vk[q] = ld_bf(s.in[T_K], t, kch);
+                vc[q] = *ctab_ptr(ct_lo, ct_hi, t, kch);
+                vpt[q] = s.ptt[t];
+            }
+            unsigned livemask = 0;
+            if (PER_TOKEN && lo) {
+#pragma unroll
+                for (int q = 0; q < 16; q++) livemask |= ((s.live[t0 + q][kch >> 3] >> (kch & 7)) & 1u) << q;
+            }
+            tmem_ld_wait();
+            // stage 2: arithmetic, the lane exchange, and the running sums
+            float out[16], gwv[16];
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+                const float c = vc[q], cp = c_prev;
+                c_prev = c;
                 const float b2 = has2 ? g2[q] : 0.f;
-                float qI, qS, out;
-                if (lo) {
-                    const float rtv = ld_bf(s.rt, t, kch), rhv = ld_bf(s.rhat, t, kch);
-                    qI = rtv * g1[q] + xt * b2;
-                    qS = rhv * gs[q];
-                    out = ld_bf(s.f_r, t, kch) * g1[q] + fg * b2 + ld_bf(s.f_rh, t, kch) * gs[q] + pt * uk * kraw;
-                } else {
-                    const float ktv = ld_bf(s.kt, t, kch), khv = ld_bf(s.khat, t, kch);
-                    qI = ktv * g1[q] + xt * b2;
-                    qS = khv * gs[q];
-                    out = ld_bf(s.f_k, t, kch) * g1[q] + fg * b2 + ld_bf(s.f_kh, t, kch) * gs[q] + pt * uk * rraw;
-                    gu_acc += pt * rraw * kraw;
-                }
+                const float a1 = lo ? cp - mb : mb - c;
+                const float a2 = lo ? cp : e1 - c;
+                const float a3 = lo ? cp - e0 : e0 - c;
+                const float f1 = __expf(a1), fS = __expf(a2), f3 = has2 ? __expf(a3) : 0.f;
+                const float raw_own = lo ? vr[q] : vk[q], raw_other = lo ? vk[q] : vr[q];
+                const float qI = vown[q] * g1[q] + vx[q] * b2;
+                const float qS = raw_own * fS * gs[q];
+                out[q] = f1 * g1[q] + f3 * b2 + fS * gs[q] + vpt[q] * uk * raw_other;
+                if (!lo) gu_acc += vpt[q] * vr[q] * vk[q];
                 // the gk lane hands its two terms to the gr lane of the same channel
                 const float o_qI = __shfl_xor_sync(0xffffffffu, qI, 16);
                 const float o_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
-                if (lo) {
-                    st_bf(o_gr, t, kch, out);
-                    C += prev_qkI - qI;
-                    prefS += qS;
-                    const float glw = T1 + (totS - prefS) + preD + C;
-                    preD += o_qS;
-                    prev_qkI = o_qI;
-                    if (PER_TOKEN) {
-                        const float xraw = ld_bf(s.in[T_W], t, kch);
-                        const float l = P.w_kind == WKV_W_RAW ? -__expf(xraw) : xraw;
-                        st_bf(o_gw, t, kch, l >= LW_FLOOR ? glw * l : 0.f);
-                    } else if (j * CH + t < P.T) {
-                        gw_acc += glw;
-                    }
-                } else {
-                    st_bf(o_gk, t, kch, out);
+                C += prev_qkI - qI;
+                prefS += qS;
+                const float glw = T1 + (totS - prefS) + preD + C;
+                preD += o_qS;
+                prev_qkI = o_qI;
+                if (PER_TOKEN) {
+                    const float l = c - cp;   // floored log-decay of this token
+                    gwv[q] = ((livemask >> q) & 1u) ? glw * l : 0.f;
+                } else if (j * CH + t0 + q < P.T) {
+                    gw_acc += glw;
                 }
+            }
+            // stage 3: stores
+            if (lo) {
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    st_bf(o_gr, t0 + q, kch, out[q]);
+                    if (PER_TOKEN) st_bf(o_gw, t0 + q, kch, gwv[q]);
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 16; q++) st_bf(o_gk, t0 + q, kch, out[q]);
             }
         }
         if (!lo) P.gu_part[((size_t)bh * n + j) * 64 + kch] = gu_acc;
@@ -593,6 +652,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     fence_async_smem();
     tc_fence_before();
     const int abort3 = __syncthreads_or(fail) | abort2;
+    if (stamp) P.timeline[7] = clock64();
     if (!abort3 && tid == 0) {
         tma_store_3d(&map_gr, &o_gr, h * 64, j * CH, b);
         tma_store_3d(&map_gk, &o_gk, h * 64, j * CH, b);
@@ -602,6 +662,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tma_store_wait_all();
     }
     if (abort3 && P.status && tid == 0) atomicOr(P.status, 4);
+    if (stamp) P.timeline[8] = clock64();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
 }
@@ -684,7 +745,9 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.u = (const __nv_bfloat16 *)a->u;
         p.wvec = per_token_w ? nullptr : (const float *)a->w;
         p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
-        const size_t smem = sizeof(BwdSmem) + 1024;
+        // bytes [64,256) of the status block take the optional phase timeline (debug aid)
+        p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)(ws + 64) : nullptr;
+        const size_t smem = sizeof(BwdSmem);
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return WKV_ERR_LAUNCH;
