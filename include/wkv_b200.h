@@ -150,7 +150,18 @@ typedef struct wkv_args {
     /* scratch */
     void *workspace;
     size_t workspace_bytes;
+    /* optional hand-over from forward to backward (chunked path only): the state at the
+     * start of every 64-token chunk, bf16, wkv56_state_ckpt_bytes() bytes.  Forward fills
+     * it when non-NULL; backward given the same buffer skips recomputing those states.
+     * The trainer's activation checkpointing re-runs the op's forward anyway
+     * (RWKV-v6/src/model.py:660-662); this is the op-level equivalent. */
+    void *state_ckpt;
+    size_t state_ckpt_bytes;
 } wkv_args_t;
+
+/* Bytes of wkv_args_t.state_ckpt for these arguments (0 when the call would not run on
+ * the chunked kernels). */
+size_t wkv56_state_ckpt_bytes(const wkv_args_t *a, int per_token_w);
 
 /* v5: replaces cuda_forward_{bf16,fp16,fp32} / cuda_backward_* of
  * RWKV-v5/src/module/cuda/wkv5_cuda.cu:348-383 (bound in wkv5_op.cpp:88-116),

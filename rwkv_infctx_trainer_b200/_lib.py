@@ -32,11 +32,12 @@ class WkvArgs(ctypes.Structure):
         ("gy", _vp), ("gstate_out", _vp),
         ("gr", _vp), ("gk", _vp), ("gv", _vp), ("gw", _vp), ("gu", _vp), ("gstate_in", _vp),
         ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
+        ("state_ckpt", _vp), ("state_ckpt_bytes", ctypes.c_size_t),
     ]
 
 
 EXPORTS = [
-    "wkv_error_string", "wkv_version", "wkv56_uses_chunked",
+    "wkv_error_string", "wkv_version", "wkv56_uses_chunked", "wkv56_state_ckpt_bytes",
     "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
     "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
@@ -78,6 +79,8 @@ def load() -> ctypes.CDLL:
     lib.wkv4_backward_static.argtypes = [i, i, i, i] + [f] * 12 + [_vp]
     lib.wkv56_uses_chunked.restype = i
     lib.wkv56_uses_chunked.argtypes = [ctypes.POINTER(WkvArgs), i]
+    lib.wkv56_state_ckpt_bytes.restype = ctypes.c_size_t
+    lib.wkv56_state_ckpt_bytes.argtypes = [ctypes.POINTER(WkvArgs), i]
     for v in ("wkv5", "wkv6"):
         for d in ("forward", "backward"):
             fn = getattr(lib, f"{v}_{d}")

@@ -389,7 +389,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
 
 int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
     if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
-    return chunked_forward_impl(a, per_token_w, nullptr, stream);
+    return chunked_forward_impl(a, per_token_w, a->state_ckpt, stream);
 }
 
 }  // namespace wkv

@@ -703,11 +703,11 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     const BwdLayout L = bwd_layout(a, per_token_w);
     char *ws = (char *)a->workspace;
     if (cudaMemsetAsync(ws, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
-    void *sck = ws + L.sck, *dck = ws + L.dck;
+    void *sck = a->state_ckpt ? a->state_ckpt : ws + L.sck, *dck = ws + L.dck;
     float *gu_part = (float *)(ws + L.gu_part), *gw_part = (float *)(ws + L.gw_part);
 
-    // 1. chunk-start states
-    {
+    // 1. chunk-start states (unless the forward call handed them over)
+    if (!a->state_ckpt) {
         wkv_args_t f = *a;
         f.y = nullptr;
         f.state_out = nullptr;

@@ -27,7 +27,7 @@ int check_common(const wkv_args_t *a, bool backward, bool per_token_w) {
     }
     if (backward && (!a->gu || (!per_token_w && !a->gw))) return WKV_ERR_NULL;
     const void *ptrs[] = {a->r, a->k, a->v, a->y, a->gy, a->gr, a->gk, a->gv, a->state_in,
-                          a->state_out, a->gstate_out, a->gstate_in, a->workspace};
+                          a->state_out, a->gstate_out, a->gstate_in, a->workspace, a->state_ckpt};
     for (const void *p : ptrs)
         if (p && !aligned16(p)) return WKV_ERR_ALIGN;
     if (per_token_w && a->w && !aligned16(a->w)) return WKV_ERR_ALIGN;
@@ -64,6 +64,7 @@ int forward(const wkv_args_t *a, bool pt, void *stream) {
     if (err != WKV_OK) return err;
     const size_t need = fwd_ws(a, pt);
     if (need && (!a->workspace || a->workspace_bytes < need)) return WKV_ERR_WORKSPACE;
+    if (ch && a->state_ckpt && a->state_ckpt_bytes < wkv56_state_ckpt_bytes(a, pt)) return WKV_ERR_WORKSPACE;
     return ch ? chunked_forward(a, pt, s) : scalar_forward(a, pt, s);
 }
 
@@ -76,6 +77,7 @@ int backward(const wkv_args_t *a, bool pt, void *stream) {
     if (err != WKV_OK) return err;
     const size_t need = bwd_ws(a, pt);
     if (need && (!a->workspace || a->workspace_bytes < need)) return WKV_ERR_WORKSPACE;
+    if (ch && a->state_ckpt && a->state_ckpt_bytes < wkv56_state_ckpt_bytes(a, pt)) return WKV_ERR_WORKSPACE;
     return ch ? chunked_backward(a, pt, s) : scalar_backward(a, pt, s);
 }
 
@@ -98,7 +100,15 @@ const char *wkv_error_string(int code) {
     return "unknown error code";
 }
 
+int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
+
 const char *wkv_version(void) { return "wkv_b200 1 sm_100a"; }
+
+size_t wkv56_state_ckpt_bytes(const wkv_args_t *a, int per_token_w) {
+    if (!wkv56_uses_chunked(a, per_token_w)) return 0;
+    const size_t n = (size_t)(a->T + 63) / 64;
+    return (size_t)a->B * a->H * (n + 1) * 64 * 64 * 2;
+}
 
 int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w) {
     if (!a || a->B <= 0 || a->H <= 0 || a->T <= 0 || a->N != HEAD) return 0;

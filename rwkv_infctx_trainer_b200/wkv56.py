@@ -41,9 +41,11 @@ def _with_workspace(lib, variant, direction, a, dev):
 
 
 def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE_KV,
-            path=L.WKV_PATH_AUTO, state_out=None):
+            path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=False):
     """Launch wkv5_forward / wkv6_forward.  All tensors contiguous, on one device.
-    Returns (y, state_out); ``state_out`` may be given (it may be ``state_in`` itself)."""
+    Returns (y, state_out); ``state_out`` may be given (it may be ``state_in`` itself).
+    With ``save_ckpt`` a third value is returned: the chunk-start states to hand to
+    ``backward(..., ckpt=...)`` (None when the call did not run on the chunked kernels)."""
     B, T, C = r.shape
     H = C // HEAD_SIZE
     dev = L.require_cuda(r, k, v, w, u, state_in)
@@ -54,16 +56,24 @@ def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE
     with torch.cuda.device(dev):
         a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, r=r, k=k, v=v, w=w, u=u,
                   state_in=state_in, y=y, state_out=state_out)
+        ckpt = None
+        if save_ckpt:
+            nck = lib.wkv56_state_ckpt_bytes(ctypes.byref(a), int(variant == "wkv6"))
+            if nck:
+                ckpt = torch.empty(nck, dtype=torch.uint8, device=dev)
+                a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), nck
         ws = _with_workspace(lib, variant, "forward", a, dev)
         L.check(getattr(lib, f"{variant}_forward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_forward")
         _check_status(lib, a, variant, ws, f"{variant}_forward")
         del ws
+    if save_ckpt:
+        return y, state_out, ckpt
     return y, state_out
 
 
 def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
-             layout=L.WKV_STATE_KV, path=L.WKV_PATH_AUTO, want_gstate=True):
+             layout=L.WKV_STATE_KV, path=L.WKV_PATH_AUTO, want_gstate=True, ckpt=None):
     """Launch wkv5_backward / wkv6_backward.  Returns gr, gk, gv, gw, gu, gstate_in with
     gw = [B,T,C] (v6, activation dtype) or [B,C] fp32 per-batch partials (v5); gu [B,C] fp32."""
     B, T, C = r.shape
@@ -82,6 +92,8 @@ def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
         a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, r=r, k=k, v=v, w=w, u=u,
                   state_in=state_in, gy=gy, gstate_out=gstate_out, gr=gr, gk=gk, gv=gv, gw=gw,
                   gu=gu, gstate_in=gsi)
+        if ckpt is not None:
+            a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), ckpt.numel()
         ws = _with_workspace(lib, variant, "backward", a, dev)
         L.check(getattr(lib, f"{variant}_backward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_backward")

@@ -40,8 +40,10 @@ class WKV6(torch.autograd.Function):
         wx = w.to(dt).contiguous()
         uf = u.to(dt).contiguous()
         s_in = state_in.float().contiguous()
-        y, s_out = wkv56.forward("wkv6", r, k, v, wx, uf, s_in, w_kind=L.WKV_W_RAW, path=path)
+        y, s_out, ckpt = wkv56.forward("wkv6", r, k, v, wx, uf, s_in, w_kind=L.WKV_W_RAW, path=path,
+                                       save_ckpt=True)
         ctx.save_for_backward(r, k, v, wx, uf, s_in)
+        ctx.ckpt = ckpt
         ctx.meta = (B, T, C, H, path, w.dtype, u.dtype, u.shape, state_in.dtype)
         return y, s_out.view(B, H, N, N)
 
@@ -52,7 +54,7 @@ class WKV6(torch.autograd.Function):
         gy = gy.to(r.dtype).contiguous()
         gso = None if gstate_out is None else gstate_out.float().contiguous()
         gr, gk, gv, gw, gu, gsi = wkv56.backward("wkv6", r, k, v, wx, uf, s_in, gy, gso,
-                                                 w_kind=L.WKV_W_RAW, path=path)
+                                                 w_kind=L.WKV_W_RAW, path=path, ckpt=ctx.ckpt)
         return (None, None, None, None, gr, gk, gv, gw.to(wdt), gu.sum(0).view(ushape).to(udt),
                 gsi.to(sdt), None)
 

@@ -109,3 +109,25 @@ def test_chunked_bitwise_repeatable():
     for n in a:
         x, y = (TL.back(t) if torch.is_tensor(t) else t for t in (a[n], b[n]))
         assert np.array_equal(x, y), n
+
+
+@pytest.mark.parametrize("variant", ["v6", "v5"])
+def test_checkpoint_handover_equals_recompute(variant):
+    """backward given the chunk-start states that forward saved == backward recomputing them"""
+    W, wkv56 = _pkg()
+    name = "wkv6" if variant == "v6" else "wkv5"
+    q = TL.case56(variant, 2, 200, 2, BF, seed=77)
+    d = {n: TL.to_dev(q[n], BF) for n in ("r", "k", "v", "gy", "u")}
+    w = TL.to_dev(q["x"], BF if variant == "v6" else torch.float32)
+    s_in = TL.to_dev(q["state_in"], torch.float32)
+    gs = TL.to_dev(q["gstate_out"], torch.float32)
+    y, so, ck = wkv56.forward(name, d["r"], d["k"], d["v"], w, d["u"], s_in, w_kind=W.WKV_W_RAW,
+                              save_ckpt=True)
+    assert ck is not None
+    a = wkv56.backward(name, d["r"], d["k"], d["v"], w, d["u"], s_in, d["gy"], gs,
+                       w_kind=W.WKV_W_RAW, ckpt=ck)
+    b = wkv56.backward(name, d["r"], d["k"], d["v"], w, d["u"], s_in, d["gy"], gs,
+                       w_kind=W.WKV_W_RAW)
+    torch.cuda.synchronize()
+    for x, z in zip(a, b):
+        assert torch.equal(x, z)
