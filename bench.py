@@ -38,6 +38,10 @@ WORKLOAD = dict(name="rwkv6_7b_wkv_fwd_bwd", variant="v6", B=4, T=16384, seg=409
 METRIC = "wkv_fwd_bwd_tokens_per_s"
 # bytes each tensor element is touched, once: fwd r,k,v,w -> y ; bwd r,k,v,w,gy -> gr,gk,gv,gw
 FWD_ELEMS, BWD_ELEMS = 5, 9
+# DRAM bytes per head-token of the backward launch group, from the ncu captures of the B=1,
+# T=4096, H=64 case: (100.7 + 13.1 MB dS scan) + (235.0 + 100.8 MB per-chunk kernel) over
+# 64 * 4096 head-tokens.  Traffic grows in proportion to head-tokens.
+NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN = (100.74e6 + 13.05e6 + 234.99e6 + 100.82e6) / (64 * 4096)
 
 
 def peaks():
@@ -187,6 +191,13 @@ def run_ours(args):
     wl = dict(WORKLOAD)
     if args.small:
         wl.update(name=wl["name"] + "_small", B=1, T=4096)
+    H_total = wl["H"]
+    if args.scaling == "strong" and world > 1:
+        from rwkv_infctx_trainer_b200.sharding import shard_units
+        sh = shard_units(wl["B"], wl["H"], world, rank)
+        if sh.b1 - sh.b0 != wl["B"] or wl["H"] % world:
+            raise SystemExit("--scaling strong needs the head count to be divisible by the GPU count")
+        wl.update(H=sh.h1 - sh.h0, C=(sh.h1 - sh.h0) * wl["N"])   # this rank's heads (same distributions)
     B, T, C, H = wl["B"], wl["T"], wl["C"], wl["H"]
     host, dev = make_inputs(wl, device, pinned_host=True)
     # the op takes contiguous [B,T_seg,C] tensors: lay the segments out once, outside the timing
@@ -304,8 +315,9 @@ def run_ours(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
     tokens = B * T
-    value = world * tokens * args.steps / (ms * 1e-3)
-    e2e_value = world * tokens * e2e_steps / (e2e_ms * 1e-3)
+    job = world if args.scaling == "weak" else 1       # strong: the ranks share one workload
+    value = job * tokens * args.steps / (ms * 1e-3)
+    e2e_value = job * tokens * e2e_steps / (e2e_ms * 1e-3)
 
     if rank == 0:
         hbm, which = peaks()
@@ -316,12 +328,14 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": wl["name"], "variant": "v6", "B_per_gpu": B, "T": T,
-                       "bptt_segment": wl["seg"], "C": C, "H": H, "head_size": 64,
+                       "bptt_segment": wl["seg"], "C_per_gpu": C, "H_per_gpu": H, "H": H_total,
+                       "head_size": 64,
                        "state": "fp32 carried across segments, gradient carried back",
-                       "sharding": f"{world} x (batch x head) replicas of the workload, no collective",
+                       "sharding": (f"{world} x (batch x head) replicas of the workload" if args.scaling == "weak"
+                                    else f"heads split {H} per GPU over {world} GPUs") + ", no collective on the data path",
                        "l2": "inputs (2.7 GB per GPU) larger than L2, no flush"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -329,11 +343,16 @@ def run_ours(args):
                     "how": "WKV6.apply + autograd; pinned host buffers; copies of step s+1 (in) and "
                            "s-1 (out) overlap the compute of step s on side streams"},
             "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "kernel": "wkv6 backward (one BPTT segment)",
+            "roofline": {"bound": "hbm",
+                         "kernel": "wkv6 backward of one BPTT segment: k_chunk_dscan + k_chunk_bwd "
+                                   "(+ k_reduce_partials), timed as one launch group",
                          "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                         "frac": achieved / hbm, "peak_source": which,
+                         "frac": achieved / hbm, "peak_source": which + " HBM copy bandwidth",
                          "algorithmic_bytes_per_launch": bwd_bytes,
-                         "avg_launch_ms": avg_bwd_ms, "traffic": None},
+                         "avg_launch_ms": avg_bwd_ms,
+                         "traffic": NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN * B * seg_tokens * H,
+                         "traffic_source": "ncu dram__bytes_read+write of both kernels on the "
+                                           "B=1 small case, scaled by head-tokens"},
             "forward_launch": {"avg_launch_ms": sum(fwd_ms) / len(fwd_ms),
                                "achieved_gbs": (FWD_ELEMS * 2 * B * seg_tokens * C
                                                 + 2 * B * H * 64 * 64 * 4)
@@ -412,6 +431,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU runs the whole workload; strong: the workload's heads "
+                         "are split across the GPUs (needs H divisible by N)")
     ap.add_argument("--small", action="store_true",
                     help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
                          "still larger than L2) instead of the benchmark workload")
