@@ -15,6 +15,8 @@
 // All contractions run on tcgen05.mma (M=64, bf16 operands in 128-byte-swizzled
 // shared-memory tiles, fp32 accumulators in tensor memory); input tiles arrive by
 // TMA; the fp32 state lives in tensor memory for the whole segment.
+#include <cstdlib>
+
 #include "wkv56_chunked.cuh"
 
 namespace wkv {
@@ -45,9 +47,18 @@ struct FwdParams {
     __nv_bfloat16 *y;
     __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
     int *status;
+    long long *timeline;      // optional debug aid: clock stamps of one mid-sequence step of one CTA
 };
 
-enum { COL_S = 0, COL_A1 = 64, COL_A2 = 128, COL_Y = 160, FWD_TMEM_COLS = 256 };
+// Tensor-memory columns.  An M=64 accumulator fills lanes 0..15 of each 32-lane quarter ("lo");
+// a second one can sit in lanes 16..31 ("hi") of the same columns, which lets both halves of a
+// warp work on one token row: score columns 0..31 / y columns 0..31 in lo, 32..63 in hi.
+//   S       lo   0.. 63   state [key, value]
+//   A1a     lo  64.. 95   same-block scores, columns (s) 0..31
+//   A2      lo  96..127   cross-block scores (rows 32..63, columns 0..31)
+//   A1b     hi  96..127   same-block scores, columns (s) 32..63
+//   Y       lo 128..159   y[:, 0..31]      hi 128..159   y[:, 32..63]
+enum { COL_S = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
 
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(128, 2)
@@ -73,7 +84,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tm = s.tmem_base;
+    const uint32_t tm = s.tmem_base, tm_hi = tm + (16u << 16);
 
     auto issue_load = [&](int j) {
         const int st = j & 1;
@@ -108,8 +119,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (!PER_TOKEN) {
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
-                const float x = P.wvec[h * 64 + cc * 8 + ch];
-                lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+                bool live;
+                lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, live);
             }
         }
     }
@@ -125,85 +136,122 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     for (int j = 0; j < P.nchunk; j++) {
         const int st = j & 1;
         Tile *in = s.in[st];
+        const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == P.nchunk / 2;
+        if (stamp) P.timeline[0] = clock64();
         if (j + 1 < P.nchunk) {
             if (tid == 0) issue_load(j + 1);
             issued = j + 1;
         }
         if (mbar_wait(&s.load_bar[st], (uint32_t)((j >> 1) & 1))) landed = j; else fail = 1;
+        if (stamp) P.timeline[1] = clock64();
 
         // ------------------------------------------------------------ prep
         {
-            Prep p;
-            float rr[4][8], kk[4][8];
+            float c[4][8];
+            Decay D;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int t = 4 * tg + i;
-                unpack8(ld_tile(in[0], t, cc), rr[i]);
-                unpack8(ld_tile(in[1], t, cc), kk[i]);
                 const bool valid = j * CH + t < P.T;
                 if (PER_TOKEN) {
                     float x[8];
                     unpack8(ld_tile(in[3], t, cc), x);
 #pragma unroll
-                    for (int ch = 0; ch < 8; ch++)
-                        p.lw[i][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+                    for (int ch = 0; ch < 8; ch++) {
+                        bool live;
+                        const float l2 = log2_decay(x[ch], P.w_kind, live);
+                        c[i][ch] = valid ? l2 : 0.f;
+                    }
                 } else {
 #pragma unroll
-                    for (int ch = 0; ch < 8; ch++) p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+                    for (int ch = 0; ch < 8; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
                 }
             }
-            prep_scan(p, lane);
+            decay_scan(c, lane, D);
             const bool blk1 = tg >= 8;
-            float ee0[8], ee10[8];
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                ee0[ch] = __expf(p.e0[ch]);
-                ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
-            }
             if (tg == 0) {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
+                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e1[ch]);
+            }
+            // r-side operands, walking forward over the thread's tokens:
+            //   fa = 2^{cp - m_blk};  fb = blk1 ? 2^{cp - e0} : 2^{cp}
+            float fa[8], fb[8], ee0[8];
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const float mb = blk1 ? D.m1[ch] : D.m0[ch];
+                fa[ch] = exp2f(D.cp0[ch] - mb);
+                fb[ch] = exp2f(blk1 ? D.cp0[ch] - D.e0[ch] : D.cp0[ch]);
+                ee0[ch] = exp2f(D.e0[ch]);
+            }
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = 4 * tg + i;
+                    float r[8], k[8], rt[8], rh[8], xx[8];
+                    unpack8(ld_tile(in[0], t, cc), r);
+                    unpack8(ld_tile(in[1], t, cc), k);
+                    float dsum = 0.f;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) {
+                        rt[ch] = r[ch] * fa[ch];
+                        xx[ch] = r[ch] * fb[ch];
+                        rh[ch] = blk1 ? xx[ch] * ee0[ch] : xx[ch];
+                        dsum += r[ch] * uu[ch] * k[ch];
+                        fa[ch] *= D.w[i][ch];
+                        fb[ch] *= D.w[i][ch];
+                    }
+                    st_tile(in[0], t, cc, pack8(rt));
+                    st_tile(in[3], t, cc, pack8(rh));
+                    if (blk1) st_tile(s.x, t, cc, pack8(xx));
+                    s.dpart[cc][t] = dsum;
+                }
+            }
+            // k-side operands, walking backward:
+            //   fa = 2^{m_blk - c};  fb = blk1 ? 2^{e1 - c} : 2^{e0 - c}
+            float ee10[8];
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const float mb = blk1 ? D.m1[ch] : D.m0[ch];
+                fa[ch] = exp2f(mb - D.c3[ch]);
+                fb[ch] = exp2f((blk1 ? D.e1[ch] : D.e0[ch]) - D.c3[ch]);
+                ee10[ch] = exp2f(D.e1[ch] - D.e0[ch]);
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 3; i >= 0; i--) {
                 const int t = 4 * tg + i;
-                float rt[8], kt[8], xx[8], rh[8], kh[8];
-                float dsum = 0.f;
+                float k[8], kt[8], kh[8], xx[8];
+                unpack8(ld_tile(in[1], t, cc), k);
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
-                    const float c = p.c[i][ch], cp = c - p.lw[i][ch];
-                    const float mb = blk1 ? p.m1[ch] : p.m0[ch];
-                    const float fr = __expf(cp - mb), fk = __expf(mb - c);
-                    const float g = blk1 ? __expf(cp - p.e0[ch]) : __expf(p.e0[ch] - c);
-                    const float frh = blk1 ? g * ee0[ch] : __expf(cp);
-                    const float fkh = blk1 ? __expf(p.e1[ch] - c) : g * ee10[ch];
-                    const float r = rr[i][ch], k = kk[i][ch];
-                    rt[ch] = r * fr; kt[ch] = k * fk;
-                    xx[ch] = (blk1 ? r : k) * g;
-                    rh[ch] = r * frh; kh[ch] = k * fkh;
-                    dsum += r * uu[ch] * k;
+                    kt[ch] = k[ch] * fa[ch];
+                    xx[ch] = k[ch] * fb[ch];
+                    kh[ch] = blk1 ? xx[ch] : xx[ch] * ee10[ch];
+                    fa[ch] *= D.w[i][ch];
+                    fb[ch] *= D.w[i][ch];
                 }
                 if (full) {
-                    st_tile(in[0], t, cc, pack8(rt));
                     st_tile(in[1], t, cc, pack8(kt));
-                    st_tile(in[3], t, cc, pack8(rh));
-                    st_tile(s.x, t, cc, pack8(xx));
-                    s.dpart[cc][t] = dsum;
+                    if (!blk1) st_tile(s.x, t, cc, pack8(xx));
                 }
                 st_tile(s.khat, t, cc, pack8(kh));
             }
         }
+        if (stamp) P.timeline[2] = clock64();
         fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
+        if (stamp) P.timeline[3] = clock64();
 
         // ------------------------------------------- scores: A1 = Rt Kt^T, A2 = X X[0:32]^T
         if (tid == 0 && full) {
             tc_fence_after();
-            const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
+            const uint32_t id32 = make_idesc(64, 32, false, false);
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_A1, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id64, k > 0);
+                mma_ss(tm + COL_A1A, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id32, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_hi + COL_A2, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 32, k), id32, k > 0);
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm + COL_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
@@ -237,54 +285,65 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
         }
         tmem_st_wait();
+        if (stamp) P.timeline[4] = clock64();
         if (full) {
             if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
             mma_phase ^= 1;
             tc_fence_after();
         }
+        if (stamp) P.timeline[5] = clock64();
 
         // ------------------------------------------------------- mask pass
+        // lo lanes own columns 0..31 of token row t, hi lanes columns 32..63
         if (full) {
             const int t = row;
-            float a[64];
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_A1 + c0), a + c0);
-            float a2[32];
-            tmem_ld16(tmem_addr(tm, lane_base, COL_A2), a2);
-            tmem_ld16(tmem_addr(tm, lane_base, COL_A2 + 16), a2 + 16);
+            const int col0 = active ? 0 : 32;
+            float a[32];
+            // rows 0..31 (warps 0,1): A1a for the lo half, nothing to read for the hi half;
+            // rows 32..63 (warps 2,3): A2 (lo) and A1b (hi) share their columns
+            const int src = warp < 2 ? COL_A1A : COL_A2;
+            tmem_ld16(tmem_addr(tm, lane_base, src), a);
+            tmem_ld16(tmem_addr(tm, lane_base, src + 16), a + 16);
             tmem_ld_wait();
             float diag = 0.f;
 #pragma unroll
             for (int q = 0; q < 8; q++) diag += s.dpart[q][t];
+            const bool cross = t >= HB && active;          // A2 block: every entry is kept
+            const bool empty = t < HB && !active;          // upper-right block: all zero
 #pragma unroll
-            for (int sx = 0; sx < 64; sx++) {
-                float val;
-                if (sx == t) val = diag;
-                else if (sx > t) val = 0.f;
-                else if (t >= HB && sx < HB) val = a2[sx & 31];
-                else val = a[sx];
-                a[sx] = val;
+            for (int q = 0; q < 32; q++) {
+                const int sx = col0 + q;
+                float val = a[q];
+                if (!cross) val = sx < t ? val : (sx == t ? diag : 0.f);
+                if (empty) val = 0.f;
+                a[q] = val;
             }
-            if (active) {
 #pragma unroll
-                for (int c8 = 0; c8 < 8; c8++) st_tile(s.atil, t, c8, pack8(a + 8 * c8));
-            }
+            for (int c8 = 0; c8 < 4; c8++) st_tile(s.atil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
         }
+        if (stamp) P.timeline[6] = clock64();
         fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
+        if (stamp) P.timeline[7] = clock64();
 
         // --------------------------- y = Atil V + Rhat Sbf ;  S = d*S + Khat^T V
         if (tid == 0) {
             tc_fence_after();
-            const uint32_t id_km = make_idesc(64, 64, false, true), id_mm = make_idesc(64, 64, true, true);
+            const uint32_t id_mm = make_idesc(64, 64, true, true);
             if (full) {
+                const uint32_t id_km32 = make_idesc(64, 32, false, true);
 #pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(tm + COL_Y, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k), id_km, k > 0);
+                for (int half = 0; half < 2; half++) {   // value columns 0..31 -> lo, 32..63 -> hi
+                    const uint32_t d = (half ? tm_hi : tm) + COL_Y;
+                    const uint64_t off = half ? 4 : 0;   // +64 bytes along the contiguous dim
 #pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(tm + COL_Y, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k), id_km, true);
+                    for (int k = 0; k < 4; k++)
+                        mma_ss(d, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k) + off, id_km32, k > 0);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        mma_ss(d, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k) + off, id_km32, true);
+                }
             }
 #pragma unroll
             for (int k = 0; k < 4; k++)
@@ -294,22 +353,25 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
         mma_phase ^= 1;
         tc_fence_after();
+        if (stamp) P.timeline[8] = clock64();
 
         // -------------------------------------------------------- epilogue
         if (full) {
             const int t = j * CH + row;
-            float yv[64];
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_Y + c0), yv + c0);
+            float yv[32];
+            tmem_ld16(tmem_addr(tm, lane_base, COL_Y), yv);
+            tmem_ld16(tmem_addr(tm, lane_base, COL_Y + 16), yv + 16);
             tmem_ld_wait();
-            if (active && t < P.T) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64);
+            if (t < P.T) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64 + (active ? 0 : 32));
 #pragma unroll
-                for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(yv + 8 * c8);
+                for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(yv + 8 * c8);
             }
         }
+        if (stamp) P.timeline[9] = clock64();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
+        if (stamp) P.timeline[10] = clock64();
     }
 
     // after a failed wait: let TMA loads that were issued land (bounded), so that the CTA
@@ -379,6 +441,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     p.y = (__nv_bfloat16 *)a->y;
     p.ckpt = (__nv_bfloat16 *)state_ckpt;
     p.status = (int *)a->workspace;
+    p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)((char *)a->workspace + 64) : nullptr;
     const size_t smem = sizeof(FwdSmem) + 1024;
     auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -40,41 +40,64 @@ __device__ __forceinline__ void st_tile(Tile &t, int row, int chunk, const uint4
 }
 
 // ---------------------------------------------------------------------------
-// Per-chunk operand preparation.  Thread layout (128 threads): 16-byte column
+// Per-chunk decay bookkeeping.  Thread layout (128 threads): 16-byte column
 // `cc` = 2*warp + (lane>>4) (8 channels), token group tg = lane & 15 (4 tokens).
 // Everything a thread computes concerns tokens 4*tg..4*tg+3 of channels 8*cc..+7.
-struct Prep {
-    float c[4][8];    // inclusive cumulative log-decay
-    float lw[4][8];   // per-token log-decay (floored), 0 for tokens past the segment end
-    float m0[8], m1[8], e0[8], e1[8];
+//
+// All decay arithmetic is done in the log2 domain (one ex2 per exponential, no
+// extra multiply): l2 = log2(decay) per token, c = inclusive running sum of l2
+// over the chunk, cp = c - l2.  Scale factors of neighbouring tokens differ by
+// exactly one token's decay, so a thread evaluates one exponential per factor
+// for its first (or last) token and walks to the others by multiplying with the
+// per-token decay w = 2^{l2}.
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float L2_FLOOR = LW_FLOOR * LOG2E;
+
+// log2 of the (floored) decay from the two encodings of the decay tensor; `live` tells
+// whether the decay is above the floor (the floor passes no gradient)
+__device__ __forceinline__ float log2_decay(float x, int w_kind, bool &live) {
+    const float l2 = w_kind == WKV_W_RAW ? -exp2f(x * LOG2E) * LOG2E : x * LOG2E;
+    live = l2 >= L2_FLOOR;
+    return fmaxf(l2, L2_FLOOR);
+}
+
+struct Decay {
+    float w[4][8];                     // decay of each of the thread's 4 tokens (1 past the segment end)
+    float cp0[8];                      // cumulative log2-decay before the thread's first token
+    float c3[8];                       // ... up to and including its last token
+    float m0[8], m1[8], e0[8], e1[8];  // c at tokens 15, 47 (block midpoints) and 31, 63 (block ends)
 };
 
-// lw filled by the caller; computes the chunk-wide cumulative sums by a local scan
-// plus a 16-lane segmented warp scan, then the four reference values.
-__device__ __forceinline__ void prep_scan(Prep &p, int lane) {
+// In: l2[i][ch] per-token log2-decay.  Out: l2 holds the inclusive cumulative sums c (local
+// scan + 16-lane segmented warp scan); D holds what the operand passes need.
+__device__ __forceinline__ void decay_scan(float (&l2)[4][8], int lane, Decay &D) {
     const int tg = lane & 15;
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        p.c[0][ch] = p.lw[0][ch];
 #pragma unroll
-        for (int i = 1; i < 4; i++) p.c[i][ch] = p.c[i - 1][ch] + p.lw[i][ch];
-        float tot = p.c[3][ch];
+        for (int i = 0; i < 4; i++) D.w[i][ch] = exp2f(l2[i][ch]);
+        const float first = l2[0][ch];
+#pragma unroll
+        for (int i = 1; i < 4; i++) l2[i][ch] += l2[i - 1][ch];
+        float tot = l2[3][ch];
 #pragma unroll
         for (int off = 1; off < 16; off <<= 1) {
             const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
             if (tg >= off) tot += o;
         }
-        const float excl = tot - p.c[3][ch];
+        const float excl = tot - l2[3][ch];
 #pragma unroll
-        for (int i = 0; i < 4; i++) p.c[i][ch] += excl;
+        for (int i = 0; i < 4; i++) l2[i][ch] += excl;
+        D.cp0[ch] = l2[0][ch] - first;
+        D.c3[ch] = l2[3][ch];
         // inclusive sums at tokens 15, 31, 47, 63 live in lanes tg = 3, 7, 11, 15
-        p.m0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 3, 16);
-        p.e0[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 7, 16);
-        p.m1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 11, 16);
-        p.e1[ch] = __shfl_sync(0xffffffffu, p.c[3][ch], 15, 16);
+        D.m0[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 3, 16);
+        D.e0[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 7, 16);
+        D.m1[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 11, 16);
+        D.e1[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 15, 16);
     }
 }
-
 
 }  // namespace chunked
 

@@ -106,8 +106,8 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     if (!PER_TOKEN) {
 #pragma unroll
         for (int ch = 0; ch < 8; ch++) {
-            const float x = P.wvec[h * 64 + cc * 8 + ch];
-            lwc[ch] = fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x) : x, LW_FLOOR);
+            bool live;
+            lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, live);
         }
     }
 
@@ -126,7 +126,8 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
         if (mbar_wait(&s.load_bar[st], (uint32_t)((i >> 1) & 1))) landed = i; else fail = 1;
 
         {   // r e^{cp}, chunk decay
-            Prep p;
+            float c[4][8];
+            Decay D;
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const int t = 4 * tg + q;
@@ -135,25 +136,34 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                     float x[8];
                     unpack8(ld_tile(in[2], t, cc), x);
 #pragma unroll
-                    for (int ch = 0; ch < 8; ch++)
-                        p.lw[q][ch] = valid ? fmaxf(P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch], LW_FLOOR) : 0.f;
+                    for (int ch = 0; ch < 8; ch++) {
+                        bool live;
+                        const float l2 = log2_decay(x[ch], P.w_kind, live);
+                        c[q][ch] = valid ? l2 : 0.f;
+                    }
                 } else {
 #pragma unroll
-                    for (int ch = 0; ch < 8; ch++) p.lw[q][ch] = valid ? lwc[ch] : 0.f;
+                    for (int ch = 0; ch < 8; ch++) c[q][ch] = valid ? lwc[ch] : 0.f;
                 }
             }
-            prep_scan(p, lane);
+            decay_scan(c, lane, D);
             if (tg == 0) {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = __expf(p.e1[ch]);
+                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e1[ch]);
             }
+            float f[8];
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) f[ch] = exp2f(D.cp0[ch]);
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const int t = 4 * tg + q;
                 float rr[8];
                 unpack8(ld_tile(in[0], t, cc), rr);
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) rr[ch] *= __expf(p.c[q][ch] - p.lw[q][ch]);
+                for (int ch = 0; ch < 8; ch++) {
+                    rr[ch] *= f[ch];
+                    f[ch] *= D.w[q][ch];
+                }
                 st_tile(in[0], t, cc, pack8(rr));
             }
         }
@@ -315,10 +325,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (!PER_TOKEN) {
 #pragma unroll
         for (int ch = 0; ch < 8; ch++) {
-            const float x = P.wvec[h * 64 + cc * 8 + ch];
-            const float l = P.w_kind == WKV_W_RAW ? -__expf(x) : x;
-            livec[ch] = l >= LW_FLOOR;
-            lwc[ch] = fmaxf(l, LW_FLOOR);
+            lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, livec[ch]);
         }
     }
     int fail = 0;
@@ -328,14 +335,12 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
     // ---------------------------------------------------------------- prep
     {
-        Prep p;
-        float rr[4][8], kk[4][8];
+        float c[4][8];
+        Decay D;
         unsigned livebits[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = 4 * tg + i;
-            unpack8(ld_tile(s.in[T_R], t, cc), rr[i]);
-            unpack8(ld_tile(s.in[T_K], t, cc), kk[i]);
             const bool valid = j * CH + t < P.T;
             livebits[i] = 0;
             if (PER_TOKEN) {
@@ -343,49 +348,76 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 unpack8(ld_tile(s.in[T_W], t, cc), x);
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
-                    const float l = P.w_kind == WKV_W_RAW ? -__expf(x[ch]) : x[ch];
-                    livebits[i] |= (l >= LW_FLOOR ? 1u : 0u) << ch;
-                    p.lw[i][ch] = valid ? fmaxf(l, LW_FLOOR) : 0.f;
+                    bool live;
+                    const float l2 = log2_decay(x[ch], P.w_kind, live);
+                    livebits[i] |= (live ? 1u : 0u) << ch;
+                    c[i][ch] = valid ? l2 : 0.f;
                 }
             } else {
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
                     livebits[i] |= (livec[ch] ? 1u : 0u) << ch;
-                    p.lw[i][ch] = valid ? lwc[ch] : 0.f;
+                    c[i][ch] = valid ? lwc[ch] : 0.f;
                 }
             }
         }
         __syncthreads();   // every w value has been read: its slot may now take the table
-        prep_scan(p, lane);
-        const bool blk1 = tg >= 8;
-        float ee10[8];
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) ee10[ch] = __expf(p.e1[ch] - p.e0[ch]);
+        decay_scan(c, lane, D);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = 4 * tg + i;
-            float rt[8], kt[8], xx[8], kh[8], cv[8];
+            float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
+            cdst[0] = make_float4(c[i][0], c[i][1], c[i][2], c[i][3]);
+            cdst[1] = make_float4(c[i][4], c[i][5], c[i][6], c[i][7]);
+            s.live[t][cc] = (unsigned char)livebits[i];
+        }
+        const bool blk1 = tg >= 8;
+        // r-side operands, walking forward:  fa = 2^{cp - m_blk};  fb = 2^{cp - e0} (block 1 only)
+        float fa[8], fb[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            fa[ch] = exp2f(D.cp0[ch] - (blk1 ? D.m1[ch] : D.m0[ch]));
+            fb[ch] = exp2f(D.cp0[ch] - D.e0[ch]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int t = 4 * tg + i;
+            float r[8], rt[8], xx[8];
+            unpack8(ld_tile(s.in[T_R], t, cc), r);
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
-                const float c = p.c[i][ch], cp = c - p.lw[i][ch];
-                const float mb = blk1 ? p.m1[ch] : p.m0[ch];
-                const float fr = __expf(cp - mb), fk = __expf(mb - c);
-                const float g = blk1 ? __expf(cp - p.e0[ch]) : __expf(p.e0[ch] - c);
-                const float fkh = blk1 ? __expf(p.e1[ch] - c) : g * ee10[ch];
-                const float r = rr[i][ch], k = kk[i][ch];
-                rt[ch] = r * fr; kt[ch] = k * fk;
-                xx[ch] = (blk1 ? r : k) * g;
-                kh[ch] = k * fkh;
-                cv[ch] = c;
+                rt[ch] = r[ch] * fa[ch];
+                xx[ch] = r[ch] * fb[ch];
+                fa[ch] *= D.w[i][ch];
+                fb[ch] *= D.w[i][ch];
             }
             st_tile(s.rt, t, cc, pack8(rt));
+            if (blk1) st_tile(s.x, t, cc, pack8(xx));
+        }
+        // k-side operands, walking backward:  fa = 2^{m_blk - c};  fb = blk1 ? 2^{e1 - c} : 2^{e0 - c}
+        float ee10[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            fa[ch] = exp2f((blk1 ? D.m1[ch] : D.m0[ch]) - D.c3[ch]);
+            fb[ch] = exp2f((blk1 ? D.e1[ch] : D.e0[ch]) - D.c3[ch]);
+            ee10[ch] = exp2f(D.e1[ch] - D.e0[ch]);
+        }
+#pragma unroll
+        for (int i = 3; i >= 0; i--) {
+            const int t = 4 * tg + i;
+            float k[8], kt[8], kh[8], xx[8];
+            unpack8(ld_tile(s.in[T_K], t, cc), k);
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                kt[ch] = k[ch] * fa[ch];
+                xx[ch] = k[ch] * fb[ch];
+                kh[ch] = blk1 ? xx[ch] : xx[ch] * ee10[ch];
+                fa[ch] *= D.w[i][ch];
+                fb[ch] *= D.w[i][ch];
+            }
             st_tile(s.kt, t, cc, pack8(kt));
-            st_tile(s.x, t, cc, pack8(xx));
+            if (!blk1) st_tile(s.x, t, cc, pack8(xx));
             st_tile(s.khat, t, cc, pack8(kh));
-            float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
-            cdst[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
-            cdst[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
-            s.live[t][cc] = (unsigned char)livebits[i];
         }
     }
     fence_async_smem();
@@ -526,16 +558,13 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 8; q++) T1 += a[q] * d[q];
         }
-        T1 *= __expf(e1);
+        T1 *= exp2f(e1);
     }
     const float uk = __bfloat162float(P.u[h * 64 + kch]);
     float lw_static = 0.f;
     bool static_live = true;
     if (!PER_TOKEN) {
-        const float x = P.wvec[h * 64 + kch];
-        const float l = P.w_kind == WKV_W_RAW ? -__expf(x) : x;
-        static_live = l >= LW_FLOOR;
-        lw_static = fmaxf(l, LW_FLOOR);
+        lw_static = log2_decay(P.wvec[h * 64 + kch], P.w_kind, static_live) * LN2;
     }
 
     if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
@@ -558,7 +587,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 float cprev = 0.f;
 #pragma unroll
                 for (int t = 0; t < 64; t++) {
-                    totS += ld_bf(s.in[T_R], t, kch) * __expf(cprev) * gs[t];
+                    totS += ld_bf(s.in[T_R], t, kch) * exp2f(cprev) * gs[t];
                     cprev = *ctab_ptr(ct_lo, ct_hi, t, kch);
                 }
             }
@@ -602,7 +631,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const float a1 = lo ? cp - mb : mb - c;
                 const float a2 = lo ? cp : e1 - c;
                 const float a3 = lo ? cp - e0 : e0 - c;
-                const float f1 = __expf(a1), fS = __expf(a2), f3 = has2 ? __expf(a3) : 0.f;
+                const float f1 = exp2f(a1), fS = exp2f(a2), f3 = has2 ? exp2f(a3) : 0.f;
                 const float raw_own = lo ? vr[q] : vk[q], raw_other = lo ? vk[q] : vr[q];
                 const float qI = vown[q] * g1[q] + vx[q] * b2;
                 const float qS = raw_own * fS * gs[q];
@@ -617,7 +646,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 preD += o_qS;
                 prev_qkI = o_qI;
                 if (PER_TOKEN) {
-                    const float l = c - cp;   // floored log-decay of this token
+                    const float l = (c - cp) * LN2;   // floored log-decay of this token
                     gwv[q] = ((livemask >> q) & 1u) ? glw * l : 0.f;
                 } else if (j * CH + t0 + q < P.T) {
                     gw_acc += glw;
