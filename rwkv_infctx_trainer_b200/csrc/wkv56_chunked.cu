@@ -33,6 +33,7 @@ struct FwdSmem {
     Tile x, khat, atil, sbf;
     float dpart[8][CH];
     float dvec[CH];
+    float btot[2][CH];     // log2-decay total of each 32-token block, per channel
     uint64_t load_bar[2];
     uint64_t mma_bar;
     uint32_t tmem_base;
@@ -72,7 +73,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const bool active = (lane & 16) == 0;          // owns an accumulator row
     const int row = warp * 16 + (lane & 15);       // that row
     const uint32_t lane_base = (uint32_t)(warp * 32);
-    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+    // operand-pass coordinates (see wkv56_chunked.cuh)
+    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
 
     if (tid == 0) {
         mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 1);
@@ -151,7 +153,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             Decay D;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int t = 4 * tg + i;
+                const int t = tok0 + i;
                 const bool valid = j * CH + t < P.T;
                 if (PER_TOKEN) {
                     float x[8];
@@ -168,25 +170,31 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             }
             decay_scan(c, lane, D);
-            const bool blk1 = tg >= 8;
-            if (tg == 0) {
+            if (tgl == 7) {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e1[ch]);
+                for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
+            }
+            __syncthreads();
+            float other[8];          // 2^{total of the other block}
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) other[ch] = exp2f(s.btot[blk ^ 1][cc * 8 + ch]);
+            if (blk == 0 && tgl == 7) {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e[ch]) * other[ch];
             }
             // r-side operands, walking forward over the thread's tokens:
-            //   fa = 2^{cp - m_blk};  fb = blk1 ? 2^{cp - e0} : 2^{cp}
-            float fa[8], fb[8], ee0[8];
+            //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
+            //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
+            float fa[8], fb[8];
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
-                const float mb = blk1 ? D.m1[ch] : D.m0[ch];
-                fa[ch] = exp2f(D.cp0[ch] - mb);
-                fb[ch] = exp2f(blk1 ? D.cp0[ch] - D.e0[ch] : D.cp0[ch]);
-                ee0[ch] = exp2f(D.e0[ch]);
+                fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+                fb[ch] = exp2f(D.cp0[ch]);
             }
             if (full) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int t = 4 * tg + i;
+                    const int t = tok0 + i;
                     float r[8], k[8], rt[8], rh[8], xx[8];
                     unpack8(ld_tile(in[0], t, cc), r);
                     unpack8(ld_tile(in[1], t, cc), k);
@@ -195,43 +203,41 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     for (int ch = 0; ch < 8; ch++) {
                         rt[ch] = r[ch] * fa[ch];
                         xx[ch] = r[ch] * fb[ch];
-                        rh[ch] = blk1 ? xx[ch] * ee0[ch] : xx[ch];
+                        rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
                         dsum += r[ch] * uu[ch] * k[ch];
                         fa[ch] *= D.w[i][ch];
                         fb[ch] *= D.w[i][ch];
                     }
                     st_tile(in[0], t, cc, pack8(rt));
                     st_tile(in[3], t, cc, pack8(rh));
-                    if (blk1) st_tile(s.x, t, cc, pack8(xx));
+                    if (blk) st_tile(s.x, t, cc, pack8(xx));
                     s.dpart[cc][t] = dsum;
                 }
             }
             // k-side operands, walking backward:
-            //   fa = 2^{m_blk - c};  fb = blk1 ? 2^{e1 - c} : 2^{e0 - c}
-            float ee10[8];
+            //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
+            //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
-                const float mb = blk1 ? D.m1[ch] : D.m0[ch];
-                fa[ch] = exp2f(mb - D.c3[ch]);
-                fb[ch] = exp2f((blk1 ? D.e1[ch] : D.e0[ch]) - D.c3[ch]);
-                ee10[ch] = exp2f(D.e1[ch] - D.e0[ch]);
+                fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+                fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
             }
 #pragma unroll
             for (int i = 3; i >= 0; i--) {
-                const int t = 4 * tg + i;
+                const int t = tok0 + i;
                 float k[8], kt[8], kh[8], xx[8];
                 unpack8(ld_tile(in[1], t, cc), k);
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
                     kt[ch] = k[ch] * fa[ch];
                     xx[ch] = k[ch] * fb[ch];
-                    kh[ch] = blk1 ? xx[ch] : xx[ch] * ee10[ch];
+                    kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
                     fa[ch] *= D.w[i][ch];
                     fb[ch] *= D.w[i][ch];
                 }
                 if (full) {
                     st_tile(in[1], t, cc, pack8(kt));
-                    if (!blk1) st_tile(s.x, t, cc, pack8(xx));
+                    if (!blk) st_tile(s.x, t, cc, pack8(xx));
                 }
                 st_tile(s.khat, t, cc, pack8(kh));
             }

@@ -40,16 +40,22 @@ __device__ __forceinline__ void st_tile(Tile &t, int row, int chunk, const uint4
 }
 
 // ---------------------------------------------------------------------------
-// Per-chunk decay bookkeeping.  Thread layout (128 threads): 16-byte column
-// `cc` = 2*warp + (lane>>4) (8 channels), token group tg = lane & 15 (4 tokens).
-// Everything a thread computes concerns tokens 4*tg..4*tg+3 of channels 8*cc..+7.
+// Per-chunk decay bookkeeping.  Thread layout of the operand passes (128 threads):
+//   warp  = 2*blk + cch     blk: which 32-token block of the chunk, cch: upper/lower 4
+//                           of the 8 16-byte columns of a tile row
+//   lane  = 4*tgl + ccl     tgl: group of 4 consecutive tokens inside the block (0..7),
+//                           ccl: column inside the group of 4
+// so a thread owns tokens 32*blk + 4*tgl .. +3 of channels 8*(4*cch+ccl) .. +7.  With the
+// 128-byte swizzle every 8 consecutive lanes then touch 8 different 16-byte bank groups:
+// the tile loads and stores are free of bank conflicts.
 //
 // All decay arithmetic is done in the log2 domain (one ex2 per exponential, no
-// extra multiply): l2 = log2(decay) per token, c = inclusive running sum of l2
-// over the chunk, cp = c - l2.  Scale factors of neighbouring tokens differ by
+// extra multiply): l2 = log2(decay) per token, c = running sum of l2 from the start
+// of the thread's block, cp = c - l2.  Scale factors of neighbouring tokens differ by
 // exactly one token's decay, so a thread evaluates one exponential per factor
 // for its first (or last) token and walks to the others by multiplying with the
-// per-token decay w = 2^{l2}.
+// per-token decay w = 2^{l2}.  Everything a block needs from the other block is that
+// block's total, exchanged through shared memory.
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float L2_FLOOR = LW_FLOOR * LOG2E;
@@ -63,16 +69,17 @@ __device__ __forceinline__ float log2_decay(float x, int w_kind, bool &live) {
 }
 
 struct Decay {
-    float w[4][8];                     // decay of each of the thread's 4 tokens (1 past the segment end)
-    float cp0[8];                      // cumulative log2-decay before the thread's first token
-    float c3[8];                       // ... up to and including its last token
-    float m0[8], m1[8], e0[8], e1[8];  // c at tokens 15, 47 (block midpoints) and 31, 63 (block ends)
+    float w[4][8];   // decay of each of the thread's 4 tokens (1 past the segment end)
+    float cp0[8];    // log2-decay accumulated from the block start to before the thread's first token
+    float c3[8];     // ... up to and including its last token
+    float m[8];      // ... up to and including token 15 of the block (the block midpoint reference)
+    float e[8];      // the whole block
 };
 
-// In: l2[i][ch] per-token log2-decay.  Out: l2 holds the inclusive cumulative sums c (local
-// scan + 16-lane segmented warp scan); D holds what the operand passes need.
+// In: l2[i][ch] per-token log2-decay.  Out: l2 holds the block-local inclusive sums c
+// (local scan + scan over the 8 threads that share a column, which sit 4 lanes apart).
 __device__ __forceinline__ void decay_scan(float (&l2)[4][8], int lane, Decay &D) {
-    const int tg = lane & 15;
+    const int tgl = lane >> 2, ccl = lane & 3;
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
 #pragma unroll
@@ -82,20 +89,17 @@ __device__ __forceinline__ void decay_scan(float (&l2)[4][8], int lane, Decay &D
         for (int i = 1; i < 4; i++) l2[i][ch] += l2[i - 1][ch];
         float tot = l2[3][ch];
 #pragma unroll
-        for (int off = 1; off < 16; off <<= 1) {
-            const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
-            if (tg >= off) tot += o;
+        for (int off = 1; off < 8; off <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, tot, 4 * off);
+            if (tgl >= off) tot += o;
         }
         const float excl = tot - l2[3][ch];
 #pragma unroll
         for (int i = 0; i < 4; i++) l2[i][ch] += excl;
         D.cp0[ch] = l2[0][ch] - first;
         D.c3[ch] = l2[3][ch];
-        // inclusive sums at tokens 15, 31, 47, 63 live in lanes tg = 3, 7, 11, 15
-        D.m0[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 3, 16);
-        D.e0[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 7, 16);
-        D.m1[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 11, 16);
-        D.e1[ch] = __shfl_sync(0xffffffffu, l2[3][ch], 15, 16);
+        D.m[ch] = __shfl_sync(0xffffffffu, l2[3][ch], ccl + 12);   // tgl = 3: token 15 of the block
+        D.e[ch] = __shfl_sync(0xffffffffu, l2[3][ch], ccl + 28);   // tgl = 7: token 31
     }
 }
 

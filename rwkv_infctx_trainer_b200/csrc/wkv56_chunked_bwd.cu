@@ -41,6 +41,7 @@ using namespace chunked;
 struct DscanSmem {
     Tile in[2][3];  // r (overwritten by r e^{cp}), gy, w
     float dvec[CH];
+    float btot[2][CH];
     uint64_t load_bar[2];
     uint64_t mma_bar;
     uint32_t tmem_base;
@@ -66,7 +67,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     const bool active = (lane & 16) == 0;
     const int row = warp * 16 + (lane & 15);
     const uint32_t lane_base = (uint32_t)(warp * 32);
-    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
     const int n = P.nchunk;
 
     if (tid == 0) {
@@ -130,7 +131,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
             Decay D;
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const int t = 4 * tg + q;
+                const int t = tok0 + q;
                 const bool valid = j * CH + t < P.T;
                 if (PER_TOKEN) {
                     float x[8];
@@ -147,16 +148,21 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                 }
             }
             decay_scan(c, lane, D);
-            if (tg == 0) {
+            if (tgl == 7) {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e1[ch]);
+                for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
             }
-            float f[8];
+            __syncthreads();
+            float f[8];      // 2^{cp} counted from the chunk start
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) f[ch] = exp2f(D.cp0[ch]);
+            for (int ch = 0; ch < 8; ch++) {
+                const float other = s.btot[blk ^ 1][cc * 8 + ch];
+                f[ch] = exp2f(blk ? D.cp0[ch] + other : D.cp0[ch]);
+                if (blk == 0 && tgl == 7) s.dvec[cc * 8 + ch] = exp2f(D.e[ch] + other);
+            }
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const int t = 4 * tg + q;
+                const int t = tok0 + q;
                 float rr[8];
                 unpack8(ld_tile(in[0], t, cc), rr);
 #pragma unroll
@@ -292,7 +298,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const bool lo = (lane & 16) == 0;
     const int row = warp * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
     const uint32_t lane_base = (uint32_t)(warp * 32);
-    const int cc = warp * 2 + (lane >> 4), tg = lane & 15;
+    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
 
     // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise
     if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -338,9 +344,11 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         float c[4][8];
         Decay D;
         unsigned livebits[4];
+        // per-block totals are exchanged through the first bytes of the A~ tile (unused until the mask pass)
+        float (*btot)[CH] = reinterpret_cast<float (*)[CH]>(s.atil.b);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = 4 * tg + i;
+            const int t = tok0 + i;
             const bool valid = j * CH + t < P.T;
             livebits[i] = 0;
             if (PER_TOKEN) {
@@ -361,27 +369,39 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             }
         }
-        __syncthreads();   // every w value has been read: its slot may now take the table
         decay_scan(c, lane, D);
+        if (tgl == 7) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) btot[blk][cc * 8 + ch] = D.e[ch];
+        }
+        __syncthreads();   // block totals visible; every w value has been read, so its slot may take the table
+        float other_l2[8], other[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            other_l2[ch] = btot[blk ^ 1][cc * 8 + ch];
+            other[ch] = exp2f(other_l2[ch]);
+        }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = 4 * tg + i;
+            const int t = tok0 + i;
+            float cv[8];      // cumulative log2-decay counted from the chunk start
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) cv[ch] = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
             float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
-            cdst[0] = make_float4(c[i][0], c[i][1], c[i][2], c[i][3]);
-            cdst[1] = make_float4(c[i][4], c[i][5], c[i][6], c[i][7]);
+            cdst[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
+            cdst[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
             s.live[t][cc] = (unsigned char)livebits[i];
         }
-        const bool blk1 = tg >= 8;
-        // r-side operands, walking forward:  fa = 2^{cp - m_blk};  fb = 2^{cp - e0} (block 1 only)
+        // r-side operands, walking forward:  fa = 2^{cp - m};  block 1 also x = r 2^{cp}  (block-local cp)
         float fa[8], fb[8];
 #pragma unroll
         for (int ch = 0; ch < 8; ch++) {
-            fa[ch] = exp2f(D.cp0[ch] - (blk1 ? D.m1[ch] : D.m0[ch]));
-            fb[ch] = exp2f(D.cp0[ch] - D.e0[ch]);
+            fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+            fb[ch] = exp2f(D.cp0[ch]);
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = 4 * tg + i;
+            const int t = tok0 + i;
             float r[8], rt[8], xx[8];
             unpack8(ld_tile(s.in[T_R], t, cc), r);
 #pragma unroll
@@ -392,31 +412,30 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 fb[ch] *= D.w[i][ch];
             }
             st_tile(s.rt, t, cc, pack8(rt));
-            if (blk1) st_tile(s.x, t, cc, pack8(xx));
+            if (blk) st_tile(s.x, t, cc, pack8(xx));
         }
-        // k-side operands, walking backward:  fa = 2^{m_blk - c};  fb = blk1 ? 2^{e1 - c} : 2^{e0 - c}
-        float ee10[8];
+        // k-side operands, walking backward:  fa = 2^{m - c};  fb = 2^{e - c}
+        //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
 #pragma unroll
         for (int ch = 0; ch < 8; ch++) {
-            fa[ch] = exp2f((blk1 ? D.m1[ch] : D.m0[ch]) - D.c3[ch]);
-            fb[ch] = exp2f((blk1 ? D.e1[ch] : D.e0[ch]) - D.c3[ch]);
-            ee10[ch] = exp2f(D.e1[ch] - D.e0[ch]);
+            fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+            fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
         }
 #pragma unroll
         for (int i = 3; i >= 0; i--) {
-            const int t = 4 * tg + i;
+            const int t = tok0 + i;
             float k[8], kt[8], kh[8], xx[8];
             unpack8(ld_tile(s.in[T_K], t, cc), k);
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
                 kt[ch] = k[ch] * fa[ch];
                 xx[ch] = k[ch] * fb[ch];
-                kh[ch] = blk1 ? xx[ch] : xx[ch] * ee10[ch];
+                kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
                 fa[ch] *= D.w[i][ch];
                 fb[ch] *= D.w[i][ch];
             }
             st_tile(s.kt, t, cc, pack8(kt));
-            if (!blk1) st_tile(s.x, t, cc, pack8(xx));
+            if (!blk) st_tile(s.x, t, cc, pack8(xx));
             st_tile(s.khat, t, cc, pack8(kh));
         }
     }
