@@ -30,7 +30,8 @@ using namespace chunked;
 struct FwdSmem {
     Tile in[2][4];     // per stage: r, k, v, w  (r,k,w are overwritten in place by
                        // r*fr, k*fk, r*e^{cp})
-    Tile x, khat, atil, sbf;
+    Tile x, khat[2], atil, sbf;   // khat is double-buffered: chunk j+1 is prepared while the
+                                  // state update of chunk j still reads khat of chunk j
     float dpart[8][CH];
     float dvec[CH];
     float btot[2][CH];     // log2-decay total of each 32-token block, per channel
@@ -70,14 +71,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, C = P.H * 64;
-    const bool active = (lane & 16) == 0;          // owns an accumulator row
+    const bool active = (lane & 16) == 0;          // lo half-warp: owns an accumulator row in lanes 0..15
     const int row = warp * 16 + (lane & 15);       // that row
     const uint32_t lane_base = (uint32_t)(warp * 32);
     // operand-pass coordinates (see wkv56_chunked.cuh)
     const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
+    const int n = P.nchunk;
+    const bool full = P.state_only == 0;
 
     if (tid == 0) {
-        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 1);
+        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1);
+        mbar_init(&s.mma_bar, 4);   // lane 0 of every warp issues a share of each MMA group and commits
         fence_mbar_init();
         prefetch_tmap(&map_r); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
         if (PER_TOKEN) prefetch_tmap(&map_w);
@@ -97,16 +101,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, j * CH, b);
         if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, j * CH, b);
     };
-    if (tid == 0 && P.nchunk > 0) issue_load(0);
+    if (tid == 0 && n > 0) issue_load(0);
 
-    // state -> tensor memory (row = key channel, column = value channel)
+    // state -> tensor memory (row = key channel, column = value channel); tcgen05.ld/st are
+    // warp-wide, lanes 16..31 of a warp touch the unused upper half of the quarter
     const size_t sbase = (size_t)bh * 64 * 64;
     {
         float v[64];
 #pragma unroll
-        for (int j = 0; j < 64; j++) {
-            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
-            v[j] = P.state_in ? P.state_in[sbase + idx] : 0.f;
+        for (int q = 0; q < 64; q++) {
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + q : (size_t)q * 64 + row;
+            v[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
         }
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
@@ -127,145 +132,153 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
     }
 
-    const bool full = P.state_only == 0;
-    uint32_t mma_phase = 0;
-    int fail = 0;        // a bounded wait ran out (carried through the next barrier)
-    int aborted = 0;
-    int issued = P.nchunk > 0 ? 0 : -1, landed = -1;   // TMA loads issued / seen complete
-    tc_fence_before();
-    __syncthreads();
-
-    for (int j = 0; j < P.nchunk; j++) {
-        const int st = j & 1;
-        Tile *in = s.in[st];
-        const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == P.nchunk / 2;
-        if (stamp) P.timeline[0] = clock64();
-        if (j + 1 < P.nchunk) {
-            if (tid == 0) issue_load(j + 1);
-            issued = j + 1;
+    // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
+    // score-diagonal partials and the chunk decay.  Contains one __syncthreads.
+    auto prep = [&](int j) {
+        Tile *in = s.in[j & 1];
+        Tile &khat = s.khat[j & 1];
+        float c[4][8];
+        Decay D;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int t = tok0 + i;
+            const bool valid = j * CH + t < P.T;
+            if (PER_TOKEN) {
+                float x[8];
+                unpack8(ld_tile(in[3], t, cc), x);
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) {
+                    bool live;
+                    const float l2 = log2_decay(x[ch], P.w_kind, live);
+                    c[i][ch] = valid ? l2 : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
+            }
         }
-        if (mbar_wait(&s.load_bar[st], (uint32_t)((j >> 1) & 1))) landed = j; else fail = 1;
-        if (stamp) P.timeline[1] = clock64();
-
-        // ------------------------------------------------------------ prep
-        {
-            float c[4][8];
-            Decay D;
+        decay_scan(c, lane, D);
+        if (tgl == 7) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
+        }
+        __syncthreads();
+        float other[8];          // 2^{total of the other block}
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) other[ch] = exp2f(s.btot[blk ^ 1][cc * 8 + ch]);
+        if (blk == 0 && tgl == 7) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e[ch]) * other[ch];
+        }
+        // r-side operands, walking forward over the thread's tokens:
+        //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
+        //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
+        float fa[8], fb[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+            fb[ch] = exp2f(D.cp0[ch]);
+        }
+        if (full) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int t = tok0 + i;
-                const bool valid = j * CH + t < P.T;
-                if (PER_TOKEN) {
-                    float x[8];
-                    unpack8(ld_tile(in[3], t, cc), x);
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) {
-                        bool live;
-                        const float l2 = log2_decay(x[ch], P.w_kind, live);
-                        c[i][ch] = valid ? l2 : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
-                }
-            }
-            decay_scan(c, lane, D);
-            if (tgl == 7) {
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
-            }
-            __syncthreads();
-            float other[8];          // 2^{total of the other block}
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) other[ch] = exp2f(s.btot[blk ^ 1][cc * 8 + ch]);
-            if (blk == 0 && tgl == 7) {
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e[ch]) * other[ch];
-            }
-            // r-side operands, walking forward over the thread's tokens:
-            //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
-            //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
-            float fa[8], fb[8];
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
-                fb[ch] = exp2f(D.cp0[ch]);
-            }
-            if (full) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int t = tok0 + i;
-                    float r[8], k[8], rt[8], rh[8], xx[8];
-                    unpack8(ld_tile(in[0], t, cc), r);
-                    unpack8(ld_tile(in[1], t, cc), k);
-                    float dsum = 0.f;
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) {
-                        rt[ch] = r[ch] * fa[ch];
-                        xx[ch] = r[ch] * fb[ch];
-                        rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
-                        dsum += r[ch] * uu[ch] * k[ch];
-                        fa[ch] *= D.w[i][ch];
-                        fb[ch] *= D.w[i][ch];
-                    }
-                    st_tile(in[0], t, cc, pack8(rt));
-                    st_tile(in[3], t, cc, pack8(rh));
-                    if (blk) st_tile(s.x, t, cc, pack8(xx));
-                    s.dpart[cc][t] = dsum;
-                }
-            }
-            // k-side operands, walking backward:
-            //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
-            //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
-                fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
-            }
-#pragma unroll
-            for (int i = 3; i >= 0; i--) {
-                const int t = tok0 + i;
-                float k[8], kt[8], kh[8], xx[8];
+                float r[8], k[8], rt[8], rh[8], xx[8];
+                unpack8(ld_tile(in[0], t, cc), r);
                 unpack8(ld_tile(in[1], t, cc), k);
+                float dsum = 0.f;
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
-                    kt[ch] = k[ch] * fa[ch];
-                    xx[ch] = k[ch] * fb[ch];
-                    kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
+                    rt[ch] = r[ch] * fa[ch];
+                    xx[ch] = r[ch] * fb[ch];
+                    rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
+                    dsum += r[ch] * uu[ch] * k[ch];
                     fa[ch] *= D.w[i][ch];
                     fb[ch] *= D.w[i][ch];
                 }
-                if (full) {
-                    st_tile(in[1], t, cc, pack8(kt));
-                    if (!blk) st_tile(s.x, t, cc, pack8(xx));
-                }
-                st_tile(s.khat, t, cc, pack8(kh));
+                st_tile(in[0], t, cc, pack8(rt));
+                st_tile(in[3], t, cc, pack8(rh));
+                if (blk) st_tile(s.x, t, cc, pack8(xx));
+                s.dpart[cc][t] = dsum;
             }
         }
-        if (stamp) P.timeline[2] = clock64();
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(fail)) { aborted = 1; break; }
-        if (stamp) P.timeline[3] = clock64();
+        // k-side operands, walking backward:
+        //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
+        //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+            fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
+        }
+#pragma unroll
+        for (int i = 3; i >= 0; i--) {
+            const int t = tok0 + i;
+            float k[8], kt[8], kh[8], xx[8];
+            unpack8(ld_tile(in[1], t, cc), k);
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                kt[ch] = k[ch] * fa[ch];
+                xx[ch] = k[ch] * fb[ch];
+                kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
+                fa[ch] *= D.w[i][ch];
+                fb[ch] *= D.w[i][ch];
+            }
+            if (full) {
+                st_tile(in[1], t, cc, pack8(kt));
+                if (!blk) st_tile(s.x, t, cc, pack8(xx));
+            }
+            st_tile(khat, t, cc, pack8(kh));
+        }
+    };
 
-        // ------------------------------------------- scores: A1 = Rt Kt^T, A2 = X X[0:32]^T
-        if (tid == 0 && full) {
+    uint32_t mma_phase = 0;
+    int fail = 0;        // a bounded wait ran out (carried through the next barrier)
+    int aborted = 0;
+    int issued = n > 0 ? 0 : -1, landed = -1;   // TMA loads issued / seen complete
+
+    // prologue: operands of chunk 0
+    if (n > 0) {
+        if (mbar_wait(&s.load_bar[0], 0)) landed = 0; else fail = 1;
+        prep(0);
+        if (n > 1) {
+            if (tid == 0) issue_load(1);
+            issued = 1;
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    if (__syncthreads_or(fail)) aborted = 1;
+
+    // Software pipeline: while the tensor core runs y/state of chunk j, the CUDA cores prepare
+    // the operands of chunk j+1.
+    for (int j = 0; j < n && !aborted; j++) {
+        const int st = j & 1;
+        Tile *in = s.in[st];
+        const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
+        if (stamp) P.timeline[0] = clock64();
+
+        // (A) scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T.  A tcgen05.mma is
+        // issued by one thread and costs it ~100 cycles of descriptor arithmetic, so the three
+        // accumulators go out from three warps at once; every warp's lane 0 commits.
+        if (lane == 0 && full) {
             tc_fence_after();
             const uint32_t id32 = make_idesc(64, 32, false, false);
+            if (warp == 0) {
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_A1A, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id32, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm + COL_A1A, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id32, k > 0);
+            } else if (warp == 1) {
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm_hi + COL_A2, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 32, k), id32, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm_hi + COL_A2, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 32, k), id32, k > 0);
+            } else if (warp == 2) {
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm + COL_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+            }
             mma_commit(&s.mma_bar);
         }
-        // ---- meanwhile: snapshot the state as bf16 (operand of r*S, checkpoint) and decay it.
-        // tcgen05.ld/st are warp-wide: every lane runs them, lanes 16..31 of a warp touch the
-        // unused upper half of the 32 tensor-memory lanes and store nothing.
+        // (B) meanwhile: snapshot the state as bf16 (operand of rhat*S, checkpoint) and decay it
         {
             float v[64];
 #pragma unroll
@@ -280,7 +293,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     st_tile(s.sbf, row, c8, q[c8]);
                 }
                 if (P.ckpt) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (P.nchunk + 1) + j) * 64 + row) * 64);
+                    uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + j) * 64 + row) * 64);
 #pragma unroll
                     for (int c8 = 0; c8 < 8; c8++) dst[c8] = q[c8];
                 }
@@ -291,17 +304,12 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
         }
         tmem_st_wait();
-        if (stamp) P.timeline[4] = clock64();
+        if (stamp) P.timeline[1] = clock64();
+        // (C) mask pass: lo lanes own columns 0..31 of token row t, hi lanes columns 32..63
         if (full) {
             if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
             mma_phase ^= 1;
             tc_fence_after();
-        }
-        if (stamp) P.timeline[5] = clock64();
-
-        // ------------------------------------------------------- mask pass
-        // lo lanes own columns 0..31 of token row t, hi lanes columns 32..63
-        if (full) {
             const int t = row;
             const int col0 = active ? 0 : 32;
             float a[32];
@@ -327,41 +335,45 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int c8 = 0; c8 < 4; c8++) st_tile(s.atil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
         }
-        if (stamp) P.timeline[6] = clock64();
+        if (stamp) P.timeline[2] = clock64();
         fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
-        if (stamp) P.timeline[7] = clock64();
 
-        // --------------------------- y = Atil V + Rhat Sbf ;  S = d*S + Khat^T V
-        if (tid == 0) {
+        // (D) y = Atil V + Rhat Sbf (value columns 0..31 -> lo lanes, 32..63 -> hi lanes) ;
+        //     S = d*S + Khat^T V
+        if (lane == 0) {
             tc_fence_after();
-            const uint32_t id_mm = make_idesc(64, 64, true, true);
-            if (full) {
+            if (warp < 2 && full) {
                 const uint32_t id_km32 = make_idesc(64, 32, false, true);
+                const uint32_t d = (warp ? tm_hi : tm) + COL_Y;
+                const uint64_t off = warp ? 4 : 0;   // +64 bytes along the contiguous dim
 #pragma unroll
-                for (int half = 0; half < 2; half++) {   // value columns 0..31 -> lo, 32..63 -> hi
-                    const uint32_t d = (half ? tm_hi : tm) + COL_Y;
-                    const uint64_t off = half ? 4 : 0;   // +64 bytes along the contiguous dim
+                for (int k = 0; k < 4; k++)
+                    mma_ss(d, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k) + off, id_km32, k > 0);
 #pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        mma_ss(d, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k) + off, id_km32, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(d, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k) + off, id_km32, true);
+            } else if (warp == 2) {
+                const uint32_t id_mm = make_idesc(64, 64, true, true);
 #pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        mma_ss(d, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k) + off, id_km32, true);
-                }
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm + COL_S, desc_mnmajor(&s.khat[st], 0, k), desc_mnmajor(&in[2], 0, k), id_mm, true);
             }
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm + COL_S, desc_mnmajor(&s.khat, 0, k), desc_mnmajor(&in[2], 0, k), id_mm, true);
             mma_commit(&s.mma_bar);
         }
+        if (stamp) P.timeline[3] = clock64();
+        // (E) operands of the next chunk while the tensor core works
+        if (j + 1 < n) {
+            if (mbar_wait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) landed = j + 1; else fail = 1;
+            prep(j + 1);
+        }
+        if (stamp) P.timeline[4] = clock64();
+        // (F) y of this chunk
         if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
         mma_phase ^= 1;
         tc_fence_after();
-        if (stamp) P.timeline[8] = clock64();
-
-        // -------------------------------------------------------- epilogue
+        if (stamp) P.timeline[5] = clock64();
         if (full) {
             const int t = j * CH + row;
             float yv[32];
@@ -374,10 +386,16 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(yv + 8 * c8);
             }
         }
-        if (stamp) P.timeline[9] = clock64();
+        if (stamp) P.timeline[6] = clock64();
+        fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
-        if (stamp) P.timeline[10] = clock64();
+        // stage j&1 is free now (its last reader was the MMA group that just completed)
+        if (j + 2 < n) {
+            if (tid == 0) issue_load(j + 2);
+            issued = j + 2;
+        }
+        if (stamp) P.timeline[7] = clock64();
     }
 
     // after a failed wait: let TMA loads that were issued land (bounded), so that the CTA
@@ -394,13 +412,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         const bool wr = active && !aborted;
         if (wr && P.state_out) {
 #pragma unroll
-            for (int j = 0; j < 64; j++) {
-                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
-                P.state_out[sbase + idx] = v[j];
+            for (int q = 0; q < 64; q++) {
+                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + q : (size_t)q * 64 + row;
+                P.state_out[sbase + idx] = v[q];
             }
         }
         if (wr && P.ckpt) {
-            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (P.nchunk + 1) + P.nchunk) * 64 + row) * 64);
+            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + n) * 64 + row) * 64);
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(v + 8 * c8);
         }
@@ -411,7 +429,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (warp == 0) tmem_dealloc(tm, FWD_TMEM_COLS);
 }
 
-size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static_assert(sizeof(FwdSmem) + 1024 <= 115712, "two CTAs per SM need <= 113 KiB each");
 
 }  // namespace
 

@@ -247,7 +247,6 @@ struct BwdSmem {
     Tile atil, ptil;           // masked scores A (with diagonal), P~
     Tile ctab_hi;              // rows 32..63 of the cumulative-decay table
     float ptt[CH];
-    unsigned char live[CH][8]; // bit ch of live[t][cc]: decay of (t, 8cc+ch) is above the floor
     uint64_t load_bar;
     uint64_t mma_bar;
     uint32_t tmem_base;
@@ -308,7 +307,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const bool stamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && tid == 0;
     if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
-        mbar_init(&s.load_bar, 1); mbar_init(&s.mma_bar, 1);
+        mbar_init(&s.load_bar, 1);
+        mbar_init(&s.mma_bar, 4);   // lane 0 of every warp issues a share of each MMA group and commits
         fence_mbar_init();
         mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
         tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
@@ -384,13 +384,16 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = tok0 + i;
-            float cv[8];      // cumulative log2-decay counted from the chunk start
+            float cv[8];      // cumulative log2-decay counted from the chunk start; its lowest mantissa
+                              // bit is replaced by the "decay above the floor" flag of the token
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) cv[ch] = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
+            for (int ch = 0; ch < 8; ch++) {
+                const float cabs = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
+                cv[ch] = __uint_as_float((__float_as_uint(cabs) & ~1u) | ((livebits[i] >> ch) & 1u));
+            }
             float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
             cdst[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
             cdst[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
-            s.live[t][cc] = (unsigned char)livebits[i];
         }
         // r-side operands, walking forward:  fa = 2^{cp - m};  block 1 also x = r 2^{cp}  (block-local cp)
         float fa[8], fb[8];
@@ -445,18 +448,24 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (stamp) P.timeline[3] = clock64();
 
     // ------------------------------------------------- phase 1: A1, A2, P
-    if (!abort1 && tid == 0) {
+    // (a tcgen05.mma is issued by one thread and costs it ~100 cycles of descriptor
+    // arithmetic: the accumulators of a group go out from different warps at once)
+    if (!abort1 && lane == 0) {
         tc_fence_after();
         const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
+        if (warp == 0) {
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
+        } else if (warp == 1) {
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            mma_ss(tm_lo + C_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_lo + C_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+        } else if (warp == 2) {
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
+        }
         mma_commit(&s.mma_bar);
     }
     // meanwhile (lo lanes): the bonus term of the score diagonal, sum_k r_t u k_t
@@ -515,10 +524,12 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (stamp) P.timeline[5] = clock64();
 
     // ------------------------------------------------- phase 2
-    if (!abort2 && tid == 0) {
+    if (!abort2 && lane == 0) {
         tc_fence_after();
-        // gv^T[v,s] = gy^T A~ + D^T khat^T
-        {
+        const uint32_t id_mk32 = make_idesc(64, 32, true, false), id_mm32 = make_idesc(64, 32, true, true);
+        const uint32_t id_kk64 = make_idesc(64, 64, false, false);
+        if (warp == 0) {
+            // gv^T[v,s] = gy^T A~ + D^T khat^T
             const uint32_t id_mm = make_idesc(64, 64, true, true), id_mk = make_idesc(64, 64, true, false);
 #pragma unroll
             for (int k = 0; k < 4; k++)
@@ -526,39 +537,39 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm_lo + C_GV, desc_mnmajor(&s.in[T_D], 0, k), desc_kmajor(&s.khat, 0, k), id_mk, true);
+        } else if (warp == 1) {
+            // gr intra, same block: G1[k,t] = sum_{s in blk} Kt[s,k] P~[t,s]
+#pragma unroll
+            for (int bl = 0; bl < 2; bl++)
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++)
+                    mma_ss(tm_lo + C_G1 + 32 * bl, desc_mnmajor(&s.kt, 32 * bl, kk),
+                           desc_kmajor(&s.ptil, 32 * bl, 2 * bl + kk), id_mk32, kk > 0);
+            // gr intra, across blocks: G2[k, t in blk1] = sum_{s<32} X[s,k] P~[t,s]
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+                mma_ss(tm_lo + C_G2, desc_mnmajor(&s.x, 0, kk), desc_kmajor(&s.ptil, 32, kk), id_mk32, kk > 0);
+        } else if (warp == 2) {
+            // gk intra, same block: G1[k,s] = sum_{t in blk} Rt[t,k] P~[t,s]
+#pragma unroll
+            for (int bl = 0; bl < 2; bl++)
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++)
+                    mma_ss(tm_hi + C_G1 + 32 * bl, desc_mnmajor(&s.rt, 32 * bl, kk),
+                           desc_mnmajor(&s.ptil, 32 * bl, kk) + (bl ? 4 : 0), id_mm32, kk > 0);
+            // gk intra, across blocks: G2[k, s<32] = sum_{t>=32} X[t,k] P~[t,s]
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+                mma_ss(tm_hi + C_G2, desc_mnmajor(&s.x, 32, kk), desc_mnmajor(&s.ptil, 32, kk), id_mm32, kk > 0);
+        } else {
+            // state parts: GS[k,t] = sum_v S[k,v] gy[t,v] (gr side), GS[k,s] = sum_v D[k,v] v[s,v] (gk side)
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_lo + C_GS, desc_kmajor(&s.in[T_S], 0, k), desc_kmajor(&s.in[T_GY], 0, k), id_kk64, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tm_hi + C_GS, desc_kmajor(&s.in[T_D], 0, k), desc_kmajor(&s.in[T_V], 0, k), id_kk64, k > 0);
         }
-        const uint32_t id_mk32 = make_idesc(64, 32, true, false), id_mm32 = make_idesc(64, 32, true, true);
-        const uint32_t id_kk64 = make_idesc(64, 64, false, false);
-        // gr intra, same block: G1[k,t] = sum_{s in blk} Kt[s,k] P~[t,s]
-#pragma unroll
-        for (int bl = 0; bl < 2; bl++)
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-                mma_ss(tm_lo + C_G1 + 32 * bl, desc_mnmajor(&s.kt, 32 * bl, kk),
-                       desc_kmajor(&s.ptil, 32 * bl, 2 * bl + kk), id_mk32, kk > 0);
-        // gr intra, across blocks: G2[k, t in blk1] = sum_{s<32} X[s,k] P~[t,s]
-#pragma unroll
-        for (int kk = 0; kk < 2; kk++)
-            mma_ss(tm_lo + C_G2, desc_mnmajor(&s.x, 0, kk), desc_kmajor(&s.ptil, 32, kk), id_mk32, kk > 0);
-        // gr state part: GS[k,t] = sum_v S[k,v] gy[t,v]
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-            mma_ss(tm_lo + C_GS, desc_kmajor(&s.in[T_S], 0, k), desc_kmajor(&s.in[T_GY], 0, k), id_kk64, k > 0);
-        // gk intra, same block: G1[k,s] = sum_{t in blk} Rt[t,k] P~[t,s]
-#pragma unroll
-        for (int bl = 0; bl < 2; bl++)
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-                mma_ss(tm_hi + C_G1 + 32 * bl, desc_mnmajor(&s.rt, 32 * bl, kk),
-                       desc_mnmajor(&s.ptil, 32 * bl, kk) + (bl ? 4 : 0), id_mm32, kk > 0);
-        // gk intra, across blocks: G2[k, s<32] = sum_{t>=32} X[t,k] P~[t,s]
-#pragma unroll
-        for (int kk = 0; kk < 2; kk++)
-            mma_ss(tm_hi + C_G2, desc_mnmajor(&s.x, 32, kk), desc_mnmajor(&s.ptil, 32, kk), id_mm32, kk > 0);
-        // gk state part: GS[k,s] = sum_v D[k,v] v[s,v]
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-            mma_ss(tm_hi + C_GS, desc_kmajor(&s.in[T_D], 0, k), desc_kmajor(&s.in[T_V], 0, k), id_kk64, k > 0);
         mma_commit(&s.mma_bar);
     }
 
@@ -622,6 +633,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             tmem_ld16(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
             const bool has2 = lo ? (t0 >= HB) : (t0 < HB);
             const float mb = t0 >= HB ? m1 : m0;
+            // exponents: gr side  cp - mb, cp, cp - e0 ;  gk side  mb - c, e1 - c, e0 - c
+            const float sg = lo ? 1.f : -1.f;
+            const float o1 = lo ? -mb : mb, o2 = lo ? 0.f : e1, o3 = lo ? -e0 : e0;
             // stage 1: every shared-memory read of this batch
             float vown[16], vx[16], vr[16], vk[16], vc[16], vpt[16];
 #pragma unroll
@@ -634,11 +648,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 vc[q] = *ctab_ptr(ct_lo, ct_hi, t, kch);
                 vpt[q] = s.ptt[t];
             }
-            unsigned livemask = 0;
-            if (PER_TOKEN && lo) {
-#pragma unroll
-                for (int q = 0; q < 16; q++) livemask |= ((s.live[t0 + q][kch >> 3] >> (kch & 7)) & 1u) << q;
-            }
             tmem_ld_wait();
             // stage 2: arithmetic, the lane exchange, and the running sums
             float out[16], gwv[16];
@@ -647,10 +656,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const float c = vc[q], cp = c_prev;
                 c_prev = c;
                 const float b2 = has2 ? g2[q] : 0.f;
-                const float a1 = lo ? cp - mb : mb - c;
-                const float a2 = lo ? cp : e1 - c;
-                const float a3 = lo ? cp - e0 : e0 - c;
-                const float f1 = exp2f(a1), fS = exp2f(a2), f3 = has2 ? exp2f(a3) : 0.f;
+                const float z = lo ? cp : c;
+                const float f1 = exp2f(fmaf(sg, z, o1)), fS = exp2f(fmaf(sg, z, o2));
+                const float f3 = has2 ? exp2f(fmaf(sg, z, o3)) : 0.f;
                 const float raw_own = lo ? vr[q] : vk[q], raw_other = lo ? vk[q] : vr[q];
                 const float qI = vown[q] * g1[q] + vx[q] * b2;
                 const float qS = raw_own * fS * gs[q];
@@ -666,7 +674,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 prev_qkI = o_qI;
                 if (PER_TOKEN) {
                     const float l = (c - cp) * LN2;   // floored log-decay of this token
-                    gwv[q] = ((livemask >> q) & 1u) ? glw * l : 0.f;
+                    gwv[q] = (__float_as_uint(c) & 1u) ? glw * l : 0.f;
                 } else if (j * CH + t0 + q < P.T) {
                     gw_acc += glw;
                 }
