@@ -55,12 +55,12 @@ struct FwdParams {
 // Tensor-memory columns.  An M=64 accumulator fills lanes 0..15 of each 32-lane quarter ("lo");
 // a second one can sit in lanes 16..31 ("hi") of the same columns, which lets both halves of a
 // warp work on one token row: score columns 0..31 / y columns 0..31 in lo, 32..63 in hi.
-//   S       lo   0.. 63   state [key, value]
-//   A1a     lo  64.. 95   same-block scores, columns (s) 0..31
-//   A2      lo  96..127   cross-block scores (rows 32..63, columns 0..31)
-//   A1b     hi  96..127   same-block scores, columns (s) 32..63
-//   Y       lo 128..159   y[:, 0..31]      hi 128..159   y[:, 32..63]
-enum { COL_S = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
+//   S       lo   0.. 31   state[key, value 0..31]      hi  0.. 31   state[key, value 32..63]
+//   A1a     lo  32.. 63   same-block scores, columns (s) 0..31
+//   A2      lo  64.. 95   cross-block scores (rows 32..63, columns 0..31)
+//   A1b     hi  64.. 95   same-block scores, columns (s) 32..63
+//   Y       lo  96..127   y[:, 0..31]                  hi 96..127   y[:, 32..63]
+enum { COL_S = 0, COL_A1A = 32, COL_A2 = 64, COL_Y = 96, FWD_TMEM_COLS = 128 };
 
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(128, 2)
@@ -106,15 +106,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     // state -> tensor memory (row = key channel, column = value channel); tcgen05.ld/st are
     // warp-wide, lanes 16..31 of a warp touch the unused upper half of the quarter
     const size_t sbase = (size_t)bh * 64 * 64;
+    const int vcol0 = active ? 0 : 32;             // value columns this thread holds of state row `row`
     {
-        float v[64];
+        float v[32];
 #pragma unroll
-        for (int q = 0; q < 64; q++) {
-            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + q : (size_t)q * 64 + row;
+        for (int q = 0; q < 32; q++) {
+            const int vc = vcol0 + q;
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
             v[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
         }
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+        tmem_st16(tmem_addr(tm, lane_base, COL_S), v);
+        tmem_st16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
     }
     tmem_st_wait();
 
@@ -278,30 +280,29 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             }
             mma_commit(&s.mma_bar);
         }
-        // (B) meanwhile: snapshot the state as bf16 (operand of rhat*S, checkpoint) and decay it
+        // (B) meanwhile: snapshot the state as bf16 (operand of rhat*S, checkpoint) and decay it;
+        // each half-warp holds 32 of the 64 value columns of its state row
         {
-            float v[64];
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+            float v[32];
+            tmem_ld16(tmem_addr(tm, lane_base, COL_S), v);
+            tmem_ld16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
             tmem_ld_wait();
             const float d = s.dvec[row];
-            if (active) {
-                uint4 q[8];
+            uint4 q[4];
 #pragma unroll
-                for (int c8 = 0; c8 < 8; c8++) {
-                    q[c8] = pack8(v + 8 * c8);
-                    st_tile(s.sbf, row, c8, q[c8]);
-                }
-                if (P.ckpt) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + j) * 64 + row) * 64);
+            for (int c8 = 0; c8 < 4; c8++) {
+                q[c8] = pack8(v + 8 * c8);
+                st_tile(s.sbf, row, (vcol0 >> 3) + c8, q[c8]);
+            }
+            if (P.ckpt) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + j) * 64 + row) * 64 + vcol0);
 #pragma unroll
-                    for (int c8 = 0; c8 < 8; c8++) dst[c8] = q[c8];
-                }
+                for (int c8 = 0; c8 < 4; c8++) dst[c8] = q[c8];
             }
 #pragma unroll
-            for (int c = 0; c < 64; c++) v[c] *= d;
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+            for (int c = 0; c < 32; c++) v[c] *= d;
+            tmem_st16(tmem_addr(tm, lane_base, COL_S), v);
+            tmem_st16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
         }
         tmem_st_wait();
         if (stamp) P.timeline[1] = clock64();
@@ -354,11 +355,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
                 for (int k = 0; k < 4; k++)
                     mma_ss(d, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k) + off, id_km32, true);
-            } else if (warp == 2) {
-                const uint32_t id_mm = make_idesc(64, 64, true, true);
+            } else if (warp >= 2) {
+                const uint32_t id_mm32 = make_idesc(64, 32, true, true);
+                const uint32_t d = (warp == 3 ? tm_hi : tm) + COL_S;
+                const uint64_t off = warp == 3 ? 4 : 0;
 #pragma unroll
                 for (int k = 0; k < 4; k++)
-                    mma_ss(tm + COL_S, desc_mnmajor(&s.khat[st], 0, k), desc_mnmajor(&in[2], 0, k), id_mm, true);
+                    mma_ss(d, desc_mnmajor(&s.khat[st], 0, k), desc_mnmajor(&in[2], 0, k) + off, id_mm32, true);
             }
             mma_commit(&s.mma_bar);
         }
@@ -405,22 +408,22 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     }
     tc_fence_after();
     {
-        float v[64];
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, COL_S + c0), v + c0);
+        float v[32];
+        tmem_ld16(tmem_addr(tm, lane_base, COL_S), v);
+        tmem_ld16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
         tmem_ld_wait();
-        const bool wr = active && !aborted;
-        if (wr && P.state_out) {
+        if (!aborted && P.state_out) {
 #pragma unroll
-            for (int q = 0; q < 64; q++) {
-                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + q : (size_t)q * 64 + row;
+            for (int q = 0; q < 32; q++) {
+                const int vc = vcol0 + q;
+                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
                 P.state_out[sbase + idx] = v[q];
             }
         }
-        if (wr && P.ckpt) {
-            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + n) * 64 + row) * 64);
+        if (!aborted && P.ckpt) {
+            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + n) * 64 + row) * 64 + vcol0);
 #pragma unroll
-            for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(v + 8 * c8);
+            for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
         }
     }
     if (aborted && P.status && tid == 0) atomicOr(P.status, 1);

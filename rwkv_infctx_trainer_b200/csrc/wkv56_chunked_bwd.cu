@@ -71,14 +71,16 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     const int n = P.nchunk;
 
     if (tid == 0) {
-        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 1);
+        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 2);
         fence_mbar_init();
     }
-    if (warp == 0) { tmem_alloc(&s.tmem_base, 64); tmem_relinquish(); }
+    if (warp == 0) { tmem_alloc(&s.tmem_base, 32); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = s.tmem_base;
+    // dS[key, value 0..31] sits in lanes 0..15 of each quarter, dS[key, value 32..63] in lanes 16..31
+    const int vcol0 = active ? 0 : 32;
 
     // step i = 0..n-1 handles chunk j = n-1-i
     auto issue_load = [&](int i) {
@@ -92,14 +94,15 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
 
     const size_t sbase = (size_t)bh * 64 * 64;
     {
-        float v[64];
+        float v[32];
 #pragma unroll
-        for (int j = 0; j < 64; j++) {
-            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
-            v[j] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
+        for (int q = 0; q < 32; q++) {
+            const int vc = vcol0 + q;
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+            v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
         }
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, c0), v + c0);
+        tmem_st16(tmem_addr(tm, lane_base, 0), v);
+        tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
     }
     tmem_st_wait();
 
@@ -179,30 +182,30 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
         tc_fence_after();
 
         {   // checkpoint D_{j+1}, decay it
-            float v[64];
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, c0), v + c0);
+            float v[32];
+            tmem_ld16(tmem_addr(tm, lane_base, 0), v);
+            tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
             tmem_ld_wait();
             const float d = s.dvec[row];
-            if (active) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64);
+            uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
 #pragma unroll
-                for (int c8 = 0; c8 < 8; c8++) dst[c8] = pack8(v + 8 * c8);
-            }
+            for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
 #pragma unroll
-            for (int c = 0; c < 64; c++) v[c] *= d;
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem_addr(tm, lane_base, c0), v + c0);
+            for (int c = 0; c < 32; c++) v[c] *= d;
+            tmem_st16(tmem_addr(tm, lane_base, 0), v);
+            tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
         }
         tmem_st_wait();
         tc_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if (lane == 0 && warp < 2) {   // value columns 0..31 from warp 0, 32..63 from warp 1
             tc_fence_after();
-            const uint32_t id = make_idesc(64, 64, true, true);
+            const uint32_t id = make_idesc(64, 32, true, true);
+            const uint32_t d = tm + (warp ? (16u << 16) : 0u);
+            const uint64_t off = warp ? 4 : 0;
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k), id, true);
+                mma_ss(d, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k) + off, id, true);
             mma_commit(&s.mma_bar);
         }
         if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
@@ -216,22 +219,23 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     }
     tc_fence_after();
     {
-        float v[64];
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, c0), v + c0);
+        float v[32];
+        tmem_ld16(tmem_addr(tm, lane_base, 0), v);
+        tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
         tmem_ld_wait();
-        if (active && !aborted && P.gstate_in) {
+        if (!aborted && P.gstate_in) {
 #pragma unroll
-            for (int j = 0; j < 64; j++) {
-                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + j : (size_t)j * 64 + row;
-                P.gstate_in[sbase + idx] = v[j];
+            for (int q = 0; q < 32; q++) {
+                const int vc = vcol0 + q;
+                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+                P.gstate_in[sbase + idx] = v[q];
             }
         }
     }
     if (aborted && P.status && tid == 0) atomicOr(P.status, 2);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tm, 64);
+    if (warp == 0) tmem_dealloc(tm, 32);
 }
 
 // ----------------------------------------------------------------------------
