@@ -39,7 +39,7 @@ using namespace chunked;
 // dS scan
 
 struct DscanSmem {
-    Tile in[2][3];  // r (overwritten by r e^{cp}), gy, w
+    Tile in[2][4];  // r (overwritten by r e^{cp}), gy, w of the step's chunk; S at the chunk's end
     float dvec[CH];
     float btot[2][CH];
     uint64_t load_bar[2];
@@ -53,13 +53,18 @@ struct DscanParams {
     const float *gstate_out;
     float *gstate_in;
     __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
+    float *e0;           // [B*H, nchunk, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at the START of chunk j
     int *status;
 };
 
+// Step i = 0..n-1 handles chunk j = n-1-i: with D_{j+1} in tensor memory it writes the D_{j+1}
+// checkpoint and E_{j+1} = rowsum(S_{j+1} * D_{j+1}) (the decay-gradient constant of chunk j+1),
+// then forms D_j = d_j D_{j+1} + (r e^{cp})^T gy.  A last step i = n only writes E_0 and D_0.
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(128)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_gy,
-              const __grid_constant__ CUtensorMap map_w, const DscanParams P) {
+              const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+              const DscanParams P) {
     extern __shared__ unsigned char smem_raw[];
     DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -82,15 +87,18 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     // dS[key, value 0..31] sits in lanes 0..15 of each quarter, dS[key, value 32..63] in lanes 16..31
     const int vcol0 = active ? 0 : 32;
 
-    // step i = 0..n-1 handles chunk j = n-1-i
     auto issue_load = [&](int i) {
         const int st = i & 1, j = n - 1 - i;
-        mbar_expect_tx(&s.load_bar[st], (PER_TOKEN ? 3 : 2) * TILE_BYTES);
-        tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
-        tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
-        if (PER_TOKEN) tma_load_3d(&s.in[st][2], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+        const int tiles = (i < n ? (PER_TOKEN ? 3 : 2) : 0) + (i >= 1 ? 1 : 0);
+        mbar_expect_tx(&s.load_bar[st], tiles * TILE_BYTES);
+        if (i < n) {
+            tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
+            tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
+            if (PER_TOKEN) tma_load_3d(&s.in[st][2], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+        }
+        if (i >= 1) tma_load_3d(&s.in[st][3], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
     };
-    if (tid == 0 && n > 0) issue_load(0);
+    if (tid == 0) issue_load(0);
 
     const size_t sbase = (size_t)bh * 64 * 64;
     {
@@ -116,20 +124,20 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     }
 
     uint32_t mma_phase = 0;
-    int fail = 0, aborted = 0, issued = n > 0 ? 0 : -1, landed = -1;
+    int fail = 0, aborted = 0, issued = 0, landed = -1;
     tc_fence_before();
     __syncthreads();
 
-    for (int i = 0; i < n; i++) {
+    for (int i = 0; i <= n; i++) {
         const int st = i & 1, j = n - 1 - i;
         Tile *in = s.in[st];
-        if (i + 1 < n) {
+        if (i + 1 <= n) {
             if (tid == 0) issue_load(i + 1);
             issued = i + 1;
         }
         if (mbar_wait(&s.load_bar[st], (uint32_t)((i >> 1) & 1))) landed = i; else fail = 1;
 
-        {   // r e^{cp}, chunk decay
+        if (i < n) {   // r e^{cp}, chunk decay
             float c[4][8];
             Decay D;
 #pragma unroll
@@ -181,20 +189,42 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
         if (__syncthreads_or(fail)) { aborted = 1; break; }
         tc_fence_after();
 
-        {   // checkpoint D_{j+1}, decay it
+        {   // with D_{j+1} in hand: its checkpoint, E_{j+1}, then the decay
             float v[32];
             tmem_ld16(tmem_addr(tm, lane_base, 0), v);
             tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
             tmem_ld_wait();
-            const float d = s.dvec[row];
-            uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+            if (i >= 1) {
+                float dot = 0.f;
 #pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
+                for (int c8 = 0; c8 < 4; c8++) {
+                    float sv[8];
+                    unpack8(ld_tile(in[3], row, (vcol0 >> 3) + c8), sv);
 #pragma unroll
-            for (int c = 0; c < 32; c++) v[c] *= d;
-            tmem_st16(tmem_addr(tm, lane_base, 0), v);
-            tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
+                    for (int q = 0; q < 8; q++) dot += sv[q] * v[8 * c8 + q];
+                }
+                dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+                if (active) P.e0[((size_t)bh * n + (j + 1)) * 64 + row] = dot;
+            }
+            if (i < n) {
+                const float d = s.dvec[row];
+                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+#pragma unroll
+                for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
+#pragma unroll
+                for (int c = 0; c < 32; c++) v[c] *= d;
+                tmem_st16(tmem_addr(tm, lane_base, 0), v);
+                tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
+            } else if (P.gstate_in) {   // last step: D_0 is the state gradient
+#pragma unroll
+                for (int q = 0; q < 32; q++) {
+                    const int vc = vcol0 + q;
+                    const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+                    P.gstate_in[sbase + idx] = v[q];
+                }
+            }
         }
+        if (i == n) break;
         tmem_st_wait();
         tc_fence_before();
         __syncthreads();
@@ -216,21 +246,6 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
     }
     if (aborted) {
         for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
-    }
-    tc_fence_after();
-    {
-        float v[32];
-        tmem_ld16(tmem_addr(tm, lane_base, 0), v);
-        tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
-        tmem_ld_wait();
-        if (!aborted && P.gstate_in) {
-#pragma unroll
-            for (int q = 0; q < 32; q++) {
-                const int vc = vcol0 + q;
-                const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-                P.gstate_in[sbase + idx] = v[q];
-            }
-        }
     }
     if (aborted && P.status && tid == 0) atomicOr(P.status, 2);
     tc_fence_before();
@@ -262,6 +277,7 @@ struct BwdParams {
     int T, H, nchunk, w_kind;
     const __nv_bfloat16 *u;
     const float *wvec;
+    const float *e0;  // [B*H, nchunk, 64]: sum_v S_j[k,v] D_j[k,v] at the start of chunk j (from the dS scan)
     float *gu_part;   // [B*H, nchunk, 64]
     float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
@@ -582,18 +598,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     Tile &ct_lo = s.in[T_W], &ct_hi = s.ctab_hi;
     const float m0 = *ctab_ptr(ct_lo, ct_hi, 15, kch), e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch);
     const float m1 = *ctab_ptr(ct_lo, ct_hi, 47, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
-    float T1 = 0.f;   // d * sum_v S[k,v] D[k,v]
-    if (lo) {
-#pragma unroll
-        for (int c8 = 0; c8 < 8; c8++) {
-            float a[8], d[8];
-            unpack8(ld_tile(s.in[T_S], kch, c8), a);
-            unpack8(ld_tile(s.in[T_D], kch, c8), d);
-#pragma unroll
-            for (int q = 0; q < 8; q++) T1 += a[q] * d[q];
-        }
-        T1 *= exp2f(e1);
-    }
+    // decay-gradient constant of the chunk: sum_v S_j[k,v] D_j[k,v]
+    const float K0 = P.e0[((size_t)bh * n + j) * 64 + kch];
     const float uk = __bfloat162float(P.u[h * 64 + kch]);
     float lw_static = 0.f;
     bool static_live = true;
@@ -610,22 +616,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
     {
         const Tile &t_own = lo ? s.rt : s.kt;          // the scaled operand whose product with G1 is qI
-        // state part of r*gr summed over the whole chunk (needed for the suffix sums)
-        float totS = 0.f;
-        {
-            float gs[64];
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_GS + c0), gs + c0);
-            tmem_ld_wait();
-            if (lo) {
-                float cprev = 0.f;
-#pragma unroll
-                for (int t = 0; t < 64; t++) {
-                    totS += ld_bf(s.in[T_R], t, kch) * exp2f(cprev) * gs[t];
-                    cprev = *ctab_ptr(ct_lo, ct_hi, t, kch);
-                }
-            }
-        }
         float prefS = 0.f, preD = 0.f, C = 0.f, prev_qkI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
         float c_prev = 0.f;   // c_{t-1}
 #pragma unroll 1
@@ -673,7 +663,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const float o_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
                 C += prev_qkI - qI;
                 prefS += qS;
-                const float glw = T1 + (totS - prefS) + preD + C;
+                const float glw = K0 - prefS + preD + C;
                 preD += o_qS;
                 prev_qkI = o_qI;
                 if (PER_TOKEN) {
@@ -740,7 +730,7 @@ __global__ void k_reduce_partials(const float *__restrict__ part, float *__restr
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct BwdLayout {
-    size_t status, sck, dck, gu_part, gw_part, total;
+    size_t status, sck, dck, e0, gu_part, gw_part, total;
 };
 BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     const size_t n = (a->T + CH - 1) / CH, bh = (size_t)a->B * a->H;
@@ -748,7 +738,8 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     L.status = 0;
     L.sck = 256;
     L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
-    L.gu_part = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
+    L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
+    L.gu_part = L.e0 + align256(bh * n * 64 * 4);
     L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
     L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
     return L;
@@ -764,7 +755,7 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     char *ws = (char *)a->workspace;
     if (cudaMemsetAsync(ws, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
     void *sck = a->state_ckpt ? a->state_ckpt : ws + L.sck, *dck = ws + L.dck;
-    float *gu_part = (float *)(ws + L.gu_part), *gw_part = (float *)(ws + L.gw_part);
+    float *gu_part = (float *)(ws + L.gu_part), *gw_part = (float *)(ws + L.gw_part), *e0 = (float *)(ws + L.e0);
 
     // 1. chunk-start states (unless the forward call handed them over)
     if (!a->state_ckpt) {
@@ -790,12 +781,12 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.T = T; p.H = H; p.nchunk = n; p.layout = a->state_layout; p.w_kind = a->w_kind;
         p.wvec = per_token_w ? nullptr : (const float *)a->w;
         p.gstate_out = a->gstate_out; p.gstate_in = a->gstate_in;
-        p.dck = (__nv_bfloat16 *)dck; p.status = (int *)ws;
+        p.dck = (__nv_bfloat16 *)dck; p.e0 = e0; p.status = (int *)ws;
         const size_t smem = sizeof(DscanSmem) + 1024;
         auto kern = per_token_w ? k_chunk_dscan<true> : k_chunk_dscan<false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return WKV_ERR_LAUNCH;
-        kern<<<B * H, 128, smem, stream>>>(mr, mgy, mw, p);
+        kern<<<B * H, 128, smem, stream>>>(mr, mgy, mw, ms, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 3. per-chunk gradients
@@ -804,7 +795,7 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.T = T; p.H = H; p.nchunk = n; p.w_kind = a->w_kind;
         p.u = (const __nv_bfloat16 *)a->u;
         p.wvec = per_token_w ? nullptr : (const float *)a->w;
-        p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
+        p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
         // bytes [64,256) of the status block take the optional phase timeline (debug aid)
         p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)(ws + 64) : nullptr;
         const size_t smem = sizeof(BwdSmem);
