@@ -39,9 +39,9 @@ METRIC = "wkv_fwd_bwd_tokens_per_s"
 # bytes each tensor element is touched, once: fwd r,k,v,w -> y ; bwd r,k,v,w,gy -> gr,gk,gv,gw
 FWD_ELEMS, BWD_ELEMS = 5, 9
 # DRAM bytes per head-token of the backward launch group, from the ncu captures of the B=1,
-# T=4096, H=64 case: (100.7 + 13.1 MB dS scan) + (235.0 + 100.8 MB per-chunk kernel) over
+# T=4096, H=64 case: (134.3 + 19.0 MB dS scan) + (236.0 + 101.4 MB per-chunk kernel) over
 # 64 * 4096 head-tokens.  Traffic grows in proportion to head-tokens.
-NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN = (100.74e6 + 13.05e6 + 234.99e6 + 100.82e6) / (64 * 4096)
+NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN = (134.26e6 + 19.03e6 + 236.03e6 + 101.43e6) / (64 * 4096)
 
 
 def peaks():
@@ -425,6 +425,91 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_side_config(args):
+    """Configs 1 (v4, fp32 I/O) and 2 (v5, bf16) of the benchmark list: forward over the BPTT
+    segments with state carried, backward in reverse with the state gradient carried.  Not the
+    headline line -- prints a JSON line of its own with ``"config_index"``."""
+    import rwkv_infctx_trainer_b200 as W
+    from rwkv_infctx_trainer_b200 import wkv56, _lib as L
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    hbm, which = peaks()
+    if args.config == 1:
+        B, T, seg, C, dt = 8, 4096, 2048, 2048, torch.float32
+        k, v, gy = (torch.randn((B, T, C), generator=g).to(dt).to(device) for _ in range(3))
+        w = (-torch.exp(torch.rand(C, generator=g) * 6 - 5)).to(device)
+        u = (torch.rand(C, generator=g) * 2 - 1).to(dt).to(device)
+        segs = [(a, a + seg) for a in range(0, T, seg)]
+        kk = [k[:, a:b].contiguous() for a, b in segs]
+        vv = [v[:, a:b].contiguous() for a, b in segs]
+        gg = [gy[:, a:b].contiguous() for a, b in segs]
+        lib, code = L.load(), L.DTYPE_CODE[dt]
+        st = torch.cuda.current_stream().cuda_stream
+        nws = lib.wkv4_backward_workspace(B, seg, C)
+        ws = torch.empty(nws, dtype=torch.uint8, device=device)
+        ys = [torch.empty_like(x) for x in kk]
+        gk = [torch.empty_like(x) for x in kk]
+        gv = [torch.empty_like(x) for x in kk]
+        gw = torch.empty((B, C), device=device); gu = torch.empty((B, C), device=device)
+        states = [torch.zeros((B, C, 3), device=device) for _ in range(len(segs) + 1)]
+        states[0][..., 2] = -1e38
+        gst = [torch.empty((B, C, 3), device=device) for _ in range(len(segs) + 1)]
+
+        def step():
+            for i in range(len(segs)):
+                L.check(lib.wkv4_forward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
+                                         vv[i].data_ptr(), states[i].data_ptr(), ys[i].data_ptr(),
+                                         states[i + 1].data_ptr(), st), "wkv4_forward")
+            for i in reversed(range(len(segs))):
+                gin = None if i == len(segs) - 1 else gst[i + 1].data_ptr()
+                L.check(lib.wkv4_backward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
+                                          vv[i].data_ptr(), states[i].data_ptr(), gg[i].data_ptr(), gin,
+                                          gw.data_ptr(), gu.data_ptr(), gk[i].data_ptr(), gv[i].data_ptr(),
+                                          gst[i].data_ptr(), ws.data_ptr(), nws, st), "wkv4_backward")
+        bytes_step = 8 * 4 * B * T * C
+        name = "rwkv4_wkv_fwd_bwd_fp32"
+    else:
+        B, T, seg, C, H = 8, 4096, 2048, 2048, 32
+        dt = torch.bfloat16
+        r, k, v, gy = (torch.randn((B, T, C), generator=g).to(dt).to(device) for _ in range(4))
+        w = (torch.rand((H, 64), generator=g) * 5 - 6).to(device)
+        u = (torch.rand((H, 64), generator=g) * 2 - 1).to(dt).to(device)
+        segs = [(a, a + seg) for a in range(0, T, seg)]
+        cs = lambda t: [t[:, a:b].contiguous() for a, b in segs]
+        rr, kk, vv, gg = cs(r), cs(k), cs(v), cs(gy)
+        s0 = torch.zeros((B, H, 64, 64), device=device)
+
+        def step():
+            states, cks = [s0], []
+            for i in range(len(segs)):
+                y, s, ck = wkv56.forward("wkv5", rr[i], kk[i], vv[i], w, u, states[-1], w_kind=W.WKV_W_RAW,
+                                         save_ckpt=True)
+                states.append(s); cks.append(ck)
+            gs = None
+            for i in reversed(range(len(segs))):
+                out = wkv56.backward("wkv5", rr[i], kk[i], vv[i], w, u, states[i], gg[i], gs,
+                                     w_kind=W.WKV_W_RAW, ckpt=cks[i])
+                gs = out[5]
+        bytes_step = 11 * 2 * B * T * C
+        name = "rwkv5_1b5_wkv_fwd_bwd_bf16"
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"config_index": args.config, "workload": name, "metric": METRIC,
+                      "value": B * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                      "algorithmic_bytes_per_step": bytes_step,
+                      "roofline_frac": bytes_step / (ms * 1e-3) / 1e9 / hbm, "peak_source": which,
+                      "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -434,6 +519,9 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU runs the whole workload; strong: the workload's heads "
                          "are split across the GPUs (needs H divisible by N)")
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3],
+                    help="3 (default): the headline v6 7B-shape workload; 1: v4 fp32 B=8 T=4096 C=2048; "
+                         "2: v5 bf16 1.5B shape (side measurements, one GPU)")
     ap.add_argument("--small", action="store_true",
                     help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
                          "still larger than L2) instead of the benchmark workload")
@@ -442,6 +530,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config != 3:
+        run_side_config(args)
     else:
         run_ours(args)
 
