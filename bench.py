@@ -448,6 +448,8 @@ def run_side_config(args):
         st = torch.cuda.current_stream().cuda_stream
         nws = lib.wkv4_backward_workspace(B, seg, C)
         ws = torch.empty(nws, dtype=torch.uint8, device=device)
+        nwf = lib.wkv4_forward_workspace(B, seg, C)
+        wsf = torch.empty(max(nwf, 16), dtype=torch.uint8, device=device)
         ys = [torch.empty_like(x) for x in kk]
         gk = [torch.empty_like(x) for x in kk]
         gv = [torch.empty_like(x) for x in kk]
@@ -460,7 +462,7 @@ def run_side_config(args):
             for i in range(len(segs)):
                 L.check(lib.wkv4_forward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
                                          vv[i].data_ptr(), states[i].data_ptr(), ys[i].data_ptr(),
-                                         states[i + 1].data_ptr(), st), "wkv4_forward")
+                                         states[i + 1].data_ptr(), wsf.data_ptr(), nwf, st), "wkv4_forward")
             for i in reversed(range(len(segs))):
                 gin = None if i == len(segs) - 1 else gst[i + 1].data_ptr()
                 L.check(lib.wkv4_backward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),

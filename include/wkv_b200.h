@@ -75,11 +75,15 @@ const char *wkv_error_string(int code);
  *              multiplied by w (wkv_cuda_bf16.cu:156)
  *   gstate_*   fp32 [B,C,3] = (gp,gq,go) in the exponent-scaled convention of
  *              wkv_cuda_bf16.cu:116-152; gstate_out may be NULL (= none)
- * No compile-time limit on T (the project needs T <= Tmax).
+ * No compile-time limit on T (the project needs T <= Tmax).  Segments of 128 tokens or
+ * more are cut into 64-token pieces that run in parallel (piece summaries are folded per
+ * channel); that needs the scratch memory wkv4_*_workspace() sizes.
  */
+size_t wkv4_forward_workspace(int B, int T, int C);
+
 int wkv4_forward(int B, int T, int C, int dtype, const float *w, const void *u,
                  const void *k, const void *v, const float *state_in, void *y,
-                 float *state_out, void *stream);
+                 float *state_out, void *workspace, size_t workspace_bytes, void *stream);
 
 size_t wkv4_backward_workspace(int B, int T, int C);
 

@@ -38,7 +38,7 @@ class WkvArgs(ctypes.Structure):
 
 EXPORTS = [
     "wkv_error_string", "wkv_version", "wkv56_uses_chunked", "wkv56_state_ckpt_bytes",
-    "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
+    "wkv4_forward_workspace", "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
     "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
@@ -67,8 +67,10 @@ def load() -> ctypes.CDLL:
     lib.wkv_error_string.argtypes = [ctypes.c_int]
     lib.wkv_version.restype = ctypes.c_char_p
     i, f = ctypes.c_int, _vp
+    lib.wkv4_forward_workspace.restype = ctypes.c_size_t
+    lib.wkv4_forward_workspace.argtypes = [i, i, i]
     lib.wkv4_forward.restype = i
-    lib.wkv4_forward.argtypes = [i, i, i, i, f, f, f, f, f, f, f, _vp]
+    lib.wkv4_forward.argtypes = [i, i, i, i, f, f, f, f, f, f, f, _vp, ctypes.c_size_t, _vp]
     lib.wkv4_backward_workspace.restype = ctypes.c_size_t
     lib.wkv4_backward_workspace.argtypes = [i, i, i]
     lib.wkv4_backward.restype = i

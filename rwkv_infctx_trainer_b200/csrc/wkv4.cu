@@ -153,19 +153,47 @@ int bwd(int B, int T, int C, const float *w, const void *u, const void *k, const
     return launch_status();
 }
 
+// segments shorter than this run on the one-thread-per-chain kernels above
+constexpr int PAR_MIN_T = 128;
+
+size_t serial_backward_workspace(int B, int T, int C) {
+    if (B <= 0 || T <= 0 || C <= 0) return 0;
+    const size_t ntile = (size_t)(T + TILE - 1) / TILE;
+    return (size_t)B * ntile * 3 * C * sizeof(float);
+}
+
 }  // namespace
+
+// time-parallel kernels, wkv4_par.cu
+size_t v4_par_forward_workspace(int B, int T, int C);
+size_t v4_par_backward_workspace(int B, int T, int C);
+int v4_par_forward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
+                   const float *si, void *y, float *so, float *ws, cudaStream_t s);
+int v4_par_backward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
+                    const float *si, const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv,
+                    float *gsi, float *ws, cudaStream_t s);
 }  // namespace wkv
 
 using namespace wkv;
 
+extern "C" size_t wkv4_forward_workspace(int B, int T, int C) {
+    if (B <= 0 || C <= 0 || T < PAR_MIN_T) return 0;
+    return v4_par_forward_workspace(B, T, C);
+}
+
 extern "C" int wkv4_forward(int B, int T, int C, int dtype, const float *w, const void *u,
                             const void *k, const void *v, const float *state_in, void *y,
-                            float *state_out, void *stream) {
+                            float *state_out, void *workspace, size_t workspace_bytes, void *stream) {
     if (B < 0 || T < 0 || C < 0) return WKV_ERR_SHAPE;
     if (B == 0 || C == 0) return WKV_OK;
     if (!w || !u) return WKV_ERR_NULL;
     if (T > 0 && (!k || !v || !y)) return WKV_ERR_NULL;
+    if (dtype != WKV_F32 && dtype != WKV_BF16 && dtype != WKV_F16) return WKV_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (T >= PAR_MIN_T) {
+        if (!workspace || workspace_bytes < wkv4_forward_workspace(B, T, C)) return WKV_ERR_WORKSPACE;
+        return v4_par_forward(B, T, C, dtype, w, u, k, v, state_in, y, state_out, (float *)workspace, s);
+    }
     switch (dtype) {
         case WKV_F32: return fwd<float>(B, T, C, w, u, k, v, state_in, y, state_out, s);
         case WKV_BF16: return fwd<__nv_bfloat16>(B, T, C, w, u, k, v, state_in, y, state_out, s);
@@ -176,8 +204,9 @@ extern "C" int wkv4_forward(int B, int T, int C, int dtype, const float *w, cons
 
 extern "C" size_t wkv4_backward_workspace(int B, int T, int C) {
     if (B <= 0 || T <= 0 || C <= 0) return 0;
-    const size_t ntile = (size_t)(T + TILE - 1) / TILE;
-    return (size_t)B * ntile * 3 * C * sizeof(float);
+    const size_t a = serial_backward_workspace(B, T, C);
+    const size_t b = T >= PAR_MIN_T ? v4_par_backward_workspace(B, T, C) : 0;
+    return a > b ? a : b;
 }
 
 extern "C" int wkv4_backward(int B, int T, int C, int dtype, const float *w, const void *u,
@@ -191,8 +220,11 @@ extern "C" int wkv4_backward(int B, int T, int C, int dtype, const float *w, con
     if (T > 0 && (!k || !v || !gy || !gk || !gv)) return WKV_ERR_NULL;
     const size_t need = wkv4_backward_workspace(B, T, C);
     if (need && (!workspace || workspace_bytes < need)) return WKV_ERR_WORKSPACE;
+    if (dtype != WKV_F32 && dtype != WKV_BF16 && dtype != WKV_F16) return WKV_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
     float *ws = (float *)workspace;
+    if (T >= PAR_MIN_T)
+        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
     switch (dtype) {
         case WKV_F32:
             return bwd<float>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);

@@ -1,0 +1,344 @@
+// v4 WKV, parallel over time.
+//
+// One thread per (batch, channel) chain leaves a B200 mostly idle (B*C chains, each a
+// dependent chain over T).  The state recurrence is linear in (p, q) with a constant decay
+// per step, so T is cut into segments of SEG tokens that are processed independently:
+//
+//   forward   1. k_seg_summary   each segment's (p,q,o) from an empty state
+//             2. k_seg_scan      per chain, fold the summaries: state at every segment start
+//             3. k_seg_forward   each segment from its true start state -> y
+//   backward  1-2 as above (segment-start states)
+//             3. k_seg_rsummary  each segment's reverse accumulation (gp,gq,go) from an empty
+//                                incoming gradient (needs the forward quantities of the segment)
+//             4. k_seg_rscan     per chain, fold them in reverse: (gp,gq,go) at every segment end
+//             5. k_seg_backward  each segment with its start state and end gradient -> gk, gv and
+//                                per-segment partial gw, gu
+//             6. k_seg_reduce    sum the partials over the segments in a fixed order
+//
+// Per-segment arithmetic is the math of RWKV-v4neo/cuda/wkv_cuda_bf16.cu:7-158; folding two
+// pieces a (earlier, n tokens after it) and b:  o' = o_a + n*w;  m = max(o', o_b);
+// (p,q) = e^{o'-m}(p_a,q_a) + e^{o_b-m}(p_b,q_b);  o = m  -- the same max-shift the kernel uses
+// token by token.  Threads of a warp hold consecutive channels: every access is coalesced.
+#include "wkv_common.cuh"
+
+namespace wkv {
+namespace {
+
+constexpr float MIN_VALUE = -1e38f;
+constexpr int SEG = 64;     // tokens per segment
+constexpr int TILE = 16;    // tokens recomputed at a time inside a segment (register stash)
+constexpr int THREADS = 128;
+
+__device__ __forceinline__ void exp_pair(float a, float b, float &A, float &Bv, float &m) {
+    const float d = a - b;
+    const float e = __expf(-fabsf(d));
+    const bool ge = d >= 0.f;
+    A = ge ? 1.f : e;
+    Bv = ge ? e : 1.f;
+    m = ge ? a : b;
+}
+
+struct Dims {
+    int B, T, C, nseg;
+};
+
+// thread -> (b, seg, c); c fastest so that a warp reads consecutive channels
+__device__ __forceinline__ bool locate(const Dims &d, int &b, int &seg, int &c, int &t0, int &len) {
+    const long long idx = (long long)blockIdx.x * THREADS + threadIdx.x;
+    if (idx >= (long long)d.B * d.nseg * d.C) return false;
+    c = (int)(idx % d.C);
+    seg = (int)((idx / d.C) % d.nseg);
+    b = (int)(idx / ((long long)d.C * d.nseg));
+    t0 = seg * SEG;
+    len = min(SEG, d.T - t0);
+    return true;
+}
+// summaries / segment states: [B][nseg][3][C]
+__device__ __forceinline__ size_t sidx(const Dims &d, int b, int seg, int c) {
+    return ((size_t)(b * d.nseg + seg) * 3) * d.C + c;
+}
+
+template <typename F>
+__global__ void __launch_bounds__(THREADS)
+k_seg_summary(Dims d, const float *__restrict__ w_, const F *__restrict__ k_, const F *__restrict__ v_,
+              float *__restrict__ loc) {
+    int b, seg, c, t0, len;
+    if (!locate(d, b, seg, c, t0, len)) return;
+    const float w = w_[c];
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    float p = 0.f, q = 0.f, o = MIN_VALUE;
+    // loads of 8 tokens go out together, then the dependent chain runs over them
+    for (int t8 = 0; t8 < len; t8 += 8) {
+        float kk[8], vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = t8 + j < len;
+            kk[j] = in ? Elem<F>::ld(k_ + off + (size_t)(t8 + j) * d.C) : 0.f;
+            vv[j] = in ? Elem<F>::ld(v_ + off + (size_t)(t8 + j) * d.C) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (t8 + j < len) {
+                float A, E, m;
+                exp_pair(w + o, kk[j], A, E, m);
+                p = A * p + E * vv[j]; q = A * q + E; o = m;
+            }
+        }
+    }
+    const size_t s = sidx(d, b, seg, c);
+    loc[s] = p; loc[s + d.C] = q; loc[s + 2 * (size_t)d.C] = o;
+}
+
+// per chain: state at the start of every segment, and the final state
+__global__ void __launch_bounds__(THREADS)
+k_seg_scan(Dims d, const float *__restrict__ w_, const float *__restrict__ state_in,
+           const float *__restrict__ loc, float *__restrict__ st, float *__restrict__ state_out) {
+    const int idx = blockIdx.x * THREADS + threadIdx.x;
+    if (idx >= d.B * d.C) return;
+    const int b = idx / d.C, c = idx % d.C;
+    const float w = w_[c];
+    float p = 0.f, q = 0.f, o = MIN_VALUE;
+    if (state_in) { p = state_in[(size_t)idx * 3]; q = state_in[(size_t)idx * 3 + 1]; o = state_in[(size_t)idx * 3 + 2]; }
+    for (int seg = 0; seg < d.nseg; seg++) {
+        const size_t s = sidx(d, b, seg, c);
+        st[s] = p; st[s + d.C] = q; st[s + 2 * (size_t)d.C] = o;
+        const int len = min(SEG, d.T - seg * SEG);
+        float A, E, m;
+        exp_pair(o + len * w, loc[s + 2 * (size_t)d.C], A, E, m);
+        p = A * p + E * loc[s]; q = A * q + E * loc[s + d.C]; o = m;
+    }
+    if (state_out) { state_out[(size_t)idx * 3] = p; state_out[(size_t)idx * 3 + 1] = q; state_out[(size_t)idx * 3 + 2] = o; }
+}
+
+template <typename F>
+__global__ void __launch_bounds__(THREADS)
+k_seg_forward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
+              const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_) {
+    int b, seg, c, t0, len;
+    if (!locate(d, b, seg, c, t0, len)) return;
+    const float w = w_[c], u = Elem<F>::ld(u_ + c);
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    const size_t s = sidx(d, b, seg, c);
+    float p = st[s], q = st[s + d.C], o = st[s + 2 * (size_t)d.C];
+    for (int t8 = 0; t8 < len; t8 += 8) {
+        float kk[8], vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = t8 + j < len;
+            kk[j] = in ? Elem<F>::ld(k_ + off + (size_t)(t8 + j) * d.C) : 0.f;
+            vv[j] = in ? Elem<F>::ld(v_ + off + (size_t)(t8 + j) * d.C) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (t8 + j < len) {
+                float A, E, m;
+                exp_pair(o, u + kk[j], A, E, m);
+                Elem<F>::st(y_ + off + (size_t)(t8 + j) * d.C, __fdividef(A * p + E * vv[j], A * q + E));
+                exp_pair(w + o, kk[j], A, E, m);
+                p = A * p + E * vv[j]; q = A * q + E; o = m;
+            }
+        }
+    }
+}
+
+// One segment backward.  FINAL = false: only the reverse accumulation from an empty incoming
+// gradient (the segment's reverse summary).  FINAL = true: with the true incoming gradient,
+// writing gk, gv and the segment's gw, gu.
+template <typename F, bool FINAL>
+__global__ void __launch_bounds__(THREADS)
+k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
+               const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ st,
+               const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
+               F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    int b, seg, c, t0, len;
+    if (!locate(d, b, seg, c, t0, len)) return;
+    const float w = w_[c], u = Elem<F>::ld(u_ + c);
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    const size_t s = sidx(d, b, seg, c);
+    constexpr int NT = SEG / TILE;
+    float cp[NT], cq[NT], co[NT];   // state at the start of every tile of the segment
+    float p = st[s], q = st[s + d.C], o = st[s + 2 * (size_t)d.C];
+    float gw = 0.f, gu = 0.f, dpdw = 0.f, dqdw = 0.f;
+#pragma unroll
+    for (int tile = 0; tile < NT; tile++) {
+        cp[tile] = p; cq[tile] = q; co[tile] = o;
+#pragma unroll
+        for (int j = 0; j < TILE; j++) {
+            const int t = tile * TILE + j;
+            if (t < len) {
+                const float kk = Elem<F>::ld(k_ + off + (size_t)t * d.C), vv = Elem<F>::ld(v_ + off + (size_t)t * d.C);
+                float A, E, m;
+                if (FINAL) {
+                    const float g = Elem<F>::ld(gy_ + off + (size_t)t * d.C);
+                    exp_pair(o, u + kk, A, E, m);
+                    const float iden = __fdividef(1.f, A * q + E);
+                    const float y = (A * p + E * vv) * iden;
+                    gw += g * (dpdw - dqdw * y) * iden * A;
+                    gu += g * (vv - y) * E * iden;
+                }
+                exp_pair(w + o, kk, A, E, m);
+                if (FINAL) { dpdw = A * (p + dpdw); dqdw = A * (q + dqdw); }
+                p = A * p + E * vv; q = A * q + E; o = m;
+            }
+        }
+    }
+    float gp = 0.f, gq = 0.f, go = MIN_VALUE;
+    if (FINAL) {
+        gp = gend[s]; gq = gend[s + d.C]; go = gend[s + 2 * (size_t)d.C];
+        gw += (gp * dpdw + gq * dqdw) * __expf(o + go);
+    }
+#pragma unroll
+    for (int tile = NT - 1; tile >= 0; tile--) {
+        if (tile * TILE < len) {
+            p = cp[tile]; q = cq[tile]; o = co[tile];
+            float ys[TILE], zs[TILE], ze[TILE];
+#pragma unroll
+            for (int j = 0; j < TILE; j++) {
+                const int t = tile * TILE + j;
+                if (t < len) {
+                    const float kk = Elem<F>::ld(k_ + off + (size_t)t * d.C), vv = Elem<F>::ld(v_ + off + (size_t)t * d.C);
+                    float A, E, m;
+                    exp_pair(o, u + kk, A, E, m);
+                    const float iden = __fdividef(1.f, A * q + E);
+                    ys[j] = (A * p + E * vv) * iden; zs[j] = iden; ze[j] = kk + u - m;
+                    exp_pair(w + o, kk, A, E, m);
+                    p = A * p + E * vv; q = A * q + E; o = m;
+                }
+            }
+#pragma unroll
+            for (int j = TILE - 1; j >= 0; j--) {
+                const int t = tile * TILE + j;
+                if (t < len) {
+                    const size_t ii = off + (size_t)t * d.C;
+                    const float kk = Elem<F>::ld(k_ + ii), g = Elem<F>::ld(gy_ + ii);
+                    const float gz = g * zs[j];
+                    float A, E, m;
+                    if (FINAL) {
+                        const float vv = Elem<F>::ld(v_ + ii);
+                        A = gz * __expf(ze[j]);
+                        E = __expf(kk + go);
+                        Elem<F>::st(gk_ + ii, A * (vv - ys[j]) + E * (gp * vv + gq));
+                        Elem<F>::st(gv_ + ii, A + E * gp);
+                    }
+                    exp_pair(w + go, ze[j] - kk - u, A, E, m);
+                    E *= gz;
+                    gp = A * gp + E; gq = A * gq - E * ys[j]; go = m;
+                }
+            }
+        }
+    }
+    if (FINAL) {
+        gw_part[(size_t)(b * d.nseg + seg) * d.C + c] = gw * w;
+        gu_part[(size_t)(b * d.nseg + seg) * d.C + c] = gu;
+    } else {
+        rloc[s] = gp; rloc[s + d.C] = gq; rloc[s + 2 * (size_t)d.C] = go;
+    }
+}
+
+// per chain, in reverse: incoming gradient at the end of every segment, and the chain's glast_state
+__global__ void __launch_bounds__(THREADS)
+k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gstate_out,
+            const float *__restrict__ rloc, float *__restrict__ gend, float *__restrict__ gstate_in) {
+    const int idx = blockIdx.x * THREADS + threadIdx.x;
+    if (idx >= d.B * d.C) return;
+    const int b = idx / d.C, c = idx % d.C;
+    const float w = w_[c];
+    float gp = 0.f, gq = 0.f, go = MIN_VALUE;
+    if (gstate_out) {
+        gp = gstate_out[(size_t)idx * 3]; gq = gstate_out[(size_t)idx * 3 + 1]; go = gstate_out[(size_t)idx * 3 + 2];
+        if (gp == 0.f && gq == 0.f) go = MIN_VALUE;
+    }
+    for (int seg = d.nseg - 1; seg >= 0; seg--) {
+        const size_t s = sidx(d, b, seg, c);
+        gend[s] = gp; gend[s + d.C] = gq; gend[s + 2 * (size_t)d.C] = go;
+        const int len = min(SEG, d.T - seg * SEG);
+        float A, E, m;
+        exp_pair(go + len * w, rloc[s + 2 * (size_t)d.C], A, E, m);
+        gp = A * gp + E * rloc[s]; gq = A * gq + E * rloc[s + d.C]; go = m;
+    }
+    if (gstate_in) { gstate_in[(size_t)idx * 3] = gp; gstate_in[(size_t)idx * 3 + 1] = gq; gstate_in[(size_t)idx * 3 + 2] = go; }
+}
+
+__global__ void __launch_bounds__(THREADS)
+k_seg_reduce(Dims d, const float *__restrict__ gw_part, const float *__restrict__ gu_part,
+             float *__restrict__ gw, float *__restrict__ gu) {
+    const int idx = blockIdx.x * THREADS + threadIdx.x;
+    if (idx >= d.B * d.C) return;
+    const int b = idx / d.C, c = idx % d.C;
+    float a = 0.f, e = 0.f;
+    for (int seg = 0; seg < d.nseg; seg++) {
+        a += gw_part[(size_t)(b * d.nseg + seg) * d.C + c];
+        e += gu_part[(size_t)(b * d.nseg + seg) * d.C + c];
+    }
+    gw[idx] = a;
+    gu[idx] = e;
+}
+
+inline unsigned blocks(long long n) { return (unsigned)((n + THREADS - 1) / THREADS); }
+
+template <typename F>
+int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v, const float *si, void *y,
+            float *so, float *ws, cudaStream_t s) {
+    const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C;
+    float *loc = ws, *st = ws + n3;
+    const long long nthr = (long long)d.B * d.nseg * d.C;
+    k_seg_summary<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
+    k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
+    k_seg_forward<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st, (F *)y);
+    return launch_status();
+}
+
+template <typename F>
+int par_bwd(Dims d, const float *w, const void *u, const void *k, const void *v, const float *si,
+            const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv, float *gsi, float *ws,
+            cudaStream_t s) {
+    const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C, n1 = (size_t)d.B * d.nseg * d.C;
+    float *loc = ws, *st = loc + n3, *rloc = st + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
+    const long long nthr = (long long)d.B * d.nseg * d.C;
+    const unsigned nb = blocks(nthr), nc = blocks((long long)d.B * d.C);
+    k_seg_summary<F><<<nb, THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
+    k_seg_scan<<<nc, THREADS, 0, s>>>(d, w, si, loc, st, nullptr);
+    k_seg_backward<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy, st,
+                                                    nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
+    k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
+    k_seg_backward<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy, st,
+                                                   gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
+    k_seg_reduce<<<nc, THREADS, 0, s>>>(d, gwp, gup, gw, gu);
+    return launch_status();
+}
+
+}  // namespace
+
+size_t v4_par_forward_workspace(int B, int T, int C) {
+    const size_t nseg = (size_t)(T + SEG - 1) / SEG;
+    return 2 * (size_t)B * nseg * 3 * C * sizeof(float);
+}
+size_t v4_par_backward_workspace(int B, int T, int C) {
+    const size_t nseg = (size_t)(T + SEG - 1) / SEG;
+    return (4 * 3 + 2) * (size_t)B * nseg * C * sizeof(float);
+}
+
+int v4_par_forward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
+                   const float *si, void *y, float *so, float *ws, cudaStream_t s) {
+    const Dims d{B, T, C, (T + SEG - 1) / SEG};
+    switch (dtype) {
+        case WKV_F32: return par_fwd<float>(d, w, u, k, v, si, y, so, ws, s);
+        case WKV_BF16: return par_fwd<__nv_bfloat16>(d, w, u, k, v, si, y, so, ws, s);
+        case WKV_F16: return par_fwd<__half>(d, w, u, k, v, si, y, so, ws, s);
+    }
+    return WKV_ERR_DTYPE;
+}
+
+int v4_par_backward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
+                    const float *si, const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv,
+                    float *gsi, float *ws, cudaStream_t s) {
+    const Dims d{B, T, C, (T + SEG - 1) / SEG};
+    switch (dtype) {
+        case WKV_F32: return par_bwd<float>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
+        case WKV_BF16: return par_bwd<__nv_bfloat16>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
+        case WKV_F16: return par_bwd<__half>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
+    }
+    return WKV_ERR_DTYPE;
+}
+
+}  // namespace wkv

@@ -42,10 +42,13 @@ class WKVFunction(torch.autograd.Function):
         last_state = raw_last_state.float().contiguous()
         y = torch.empty_like(k)
         new_state = torch.empty_like(last_state)
+        lib = L.load()
         with torch.cuda.device(dev):
-            L.check(L.load().wkv4_forward(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
-                                          L.ptr(v), L.ptr(last_state), L.ptr(y), L.ptr(new_state),
-                                          L.stream_handle(dev)), "wkv4_forward")
+            nbytes = lib.wkv4_forward_workspace(B, T, C)
+            ws = _ws(nbytes, dev)
+            L.check(lib.wkv4_forward(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
+                                     L.ptr(v), L.ptr(last_state), L.ptr(y), L.ptr(new_state),
+                                     L.ptr(ws), nbytes, L.stream_handle(dev)), "wkv4_forward")
         ctx.save_for_backward(w, u, k, v, last_state)
         ctx.u_dtype = raw_u.dtype
         return y, new_state

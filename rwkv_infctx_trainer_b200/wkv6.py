@@ -114,7 +114,11 @@ wkv6state_cuda_kernel = _Wkv6StateKernel()
 
 class WKV6STATE_CUDA(torch.autograd.Function):
     """RWKV-v6/src/module/TimeMix.py:19-109: ``apply(B,T,C,H,r,k,v,w,u,s) -> y`` with
-    ``s`` updated in place; backward returns (gr,gk,gv,gw,gu,gs)."""
+    ``s`` updated in place ([value,key] layout, any float dtype, indexed per batch row);
+    backward returns (gr,gk,gv,gw,gu,gs).  The raw decay activation ``w`` goes to the
+    kernels as it is (they apply exp(-exp(w)) themselves), so bf16 calls run on the
+    chunked tensor-core path; ``wkv6state_cuda_kernel`` keeps the project's lower-level
+    signature with the precomputed ``ew`` for callers that use it directly."""
 
     @staticmethod
     def forward(ctx, B, T, C, H, r, k, v, w, u, s):
@@ -128,11 +132,15 @@ class WKV6STATE_CUDA(torch.autograd.Function):
                 raise TypeError("r,k,v,u must share one dtype")
             if dtype not in L.DTYPE_CODE:
                 raise ValueError(f"Unsupported dtype {dtype} for WKV6_CUDA")
-            ew = (-torch.exp(w.float())).contiguous()
-            ctx.save_for_backward(r, k, v, ew, u, s.clone())
-            y = torch.empty((B, T, C), device=r.device, dtype=dtype)
-            name = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}[dtype]
-            getattr(wkv6state_cuda_kernel, "forward_" + name)(B, T, C, H, r, k, v, ew, u, s, y)
+            wx = w.to(dtype).contiguous()
+            s32 = s.float().contiguous()
+            s_in = s32.clone()
+            y, _, ckpt = wkv56.forward("wkv6", r, k, v, wx, u, s32, w_kind=L.WKV_W_RAW,
+                                       layout=L.WKV_STATE_VK, state_out=s32, save_ckpt=True)
+            if s32.data_ptr() != s.data_ptr():
+                s.copy_(s32.view_as(s))
+            ctx.save_for_backward(r, k, v, wx, u, s_in)
+            ctx.ckpt, ctx.s_dtype, ctx.w_dtype = ckpt, s.dtype, w.dtype
             return y
 
     @staticmethod
@@ -140,15 +148,13 @@ class WKV6STATE_CUDA(torch.autograd.Function):
         with torch.no_grad():
             B, T, C, H, dtype = ctx.B, ctx.T, ctx.C, ctx.H, ctx.dtype
             gy = gy.to(dtype).contiguous()
-            r, k, v, ew, u, s = ctx.saved_tensors
-            mk = lambda *shape: torch.empty(shape, device=gy.device, dtype=dtype)
-            gr, gk, gv, gw = mk(B, T, C), mk(B, T, C), mk(B, T, C), mk(B, T, C)
-            gu, gs = mk(B, C), torch.empty((B, H, C // H, C // H), device=gy.device, dtype=s.dtype)
-            name = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}[dtype]
-            getattr(wkv6state_cuda_kernel, "backward_" + name)(B, T, C, H, r, k, v, ew, u, s, gy,
-                                                               gr, gk, gv, gw, gu, gs)
-            gu = torch.sum(gu, 0).view(H, C // H)
-            return (None, None, None, None, gr, gk, gv, gw, gu, gs)
+            r, k, v, wx, u, s_in = ctx.saved_tensors
+            gr, gk, gv, gw, gu, gs = wkv56.backward("wkv6", r, k, v, wx, u, s_in, gy, None,
+                                                    w_kind=L.WKV_W_RAW, layout=L.WKV_STATE_VK,
+                                                    ckpt=ctx.ckpt)
+            gu = torch.sum(gu, 0).view(H, C // H).to(dtype)
+            return (None, None, None, None, gr, gk, gv, gw.to(ctx.w_dtype), gu,
+                    gs.view(B, H, C // H, C // H).to(ctx.s_dtype))
 
 
 def RUN_WKV6STATE_CUDA(B, T, C, H, r, k, v, w, u, s):

@@ -43,9 +43,11 @@ def test_error_codes_without_gpu():
         setattr(a, f, base)
     a.r = base + 2
     assert lib.wkv6_forward(ctypes.byref(a), None) == 4  # misaligned
-    assert lib.wkv4_forward(-1, 1, 1, 0, None, None, None, None, None, None, None, None) == 2
-    assert lib.wkv4_forward(1, 1, 1, 0, None, None, None, None, None, None, None, None) == 1
-    assert lib.wkv4_backward_workspace(2, 100, 8) == 2 * 7 * 3 * 8 * 4
+    assert lib.wkv4_forward(-1, 1, 1, 0, None, None, None, None, None, None, None, None, 0, None) == 2
+    assert lib.wkv4_forward(1, 1, 1, 0, None, None, None, None, None, None, None, None, 0, None) == 1
+    assert lib.wkv4_backward_workspace(2, 100, 8) == 2 * 7 * 3 * 8 * 4      # short: one thread per chain
+    assert lib.wkv4_forward_workspace(2, 100, 8) == 0
+    assert lib.wkv4_forward_workspace(2, 256, 8) == 2 * 2 * 4 * 3 * 8 * 4   # 64-token pieces
     assert b"workspace" in lib.wkv_error_string(5)
     # empty batch is a no-op, not an error
     a = L.WkvArgs()

@@ -1,9 +1,12 @@
 """wkv4_backward_static: the v4 backward for callers that cannot provide scratch memory
 (a binding with no device allocator of its own, or a loop that must not cudaMalloc
 between steps).  It keeps the tile-start states in an array inside the library instead of
-a caller workspace, so its results must equal wkv4_backward's bit for bit -- on a first
-call and on a second call that reuses the same array with other sizes and inputs.  Runs
-last (file name) so that a failure here cannot hide any other test."""
+a caller workspace, so its results must agree with wkv4_backward's -- on a first call and
+on a second call that reuses the same array with other sizes and inputs.  For segments
+under 128 tokens both entry points run the same kernel and the results are identical bit
+for bit; longer segments take the time-parallel kernels in wkv4_backward, and the two are
+held to the parity tolerance of the other v4 tests (1e-3 fp32, 2e-2 bf16, max|a-b|/max|b|).
+Runs last (file name) so that a failure here cannot hide any other test."""
 import numpy as np
 import pytest
 import torch
@@ -26,8 +29,11 @@ def _run_both(B, T, C, dtype, seed):
     y = torch.empty_like(k); s1 = torch.empty_like(s0)
     stream = torch.cuda.current_stream().cuda_stream
     code = L.DTYPE_CODE[dtype]
+    nf = lib.wkv4_forward_workspace(B, T, C)
+    wsf = torch.empty(max(nf, 16), dtype=torch.uint8, device=dev)
     L.check(lib.wkv4_forward(B, T, C, code, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
-                             s0.data_ptr(), y.data_ptr(), s1.data_ptr(), stream), "wkv4_forward")
+                             s0.data_ptr(), y.data_ptr(), s1.data_ptr(), wsf.data_ptr(), nf, stream),
+            "wkv4_forward")
     gso = mk(np.stack([inputs.normal((B, C), seed, stream=30), inputs.normal((B, C), seed, stream=31),
                        inputs.uniform((B, C), seed, -1, 1, stream=32)], -1), torch.float32)
 
@@ -51,13 +57,29 @@ def _run_both(B, T, C, dtype, seed):
     return a, b
 
 
+def _rel(x, y):
+    x, y = x.double(), y.double()
+    return float((x - y).abs().max() / y.abs().max().clamp_min(1e-30))
+
+
 def test_static_scratch_backward_equals_workspace_backward_twice_in_a_row():
-    # same kernel, same arithmetic, only the scratch location differs: results are identical
     for B, T, C, dtype, seed in ((2, 200, 256, torch.bfloat16, 1), (3, 77, 128, torch.float32, 2)):
         a, b = _run_both(B, T, C, dtype, seed)
         for name in a:
             assert torch.isfinite(b[name].float()).all(), name
-            assert torch.equal(a[name], b[name]), f"{name} differs (B={B},T={T},C={C})"
+        if T < 128:
+            # same kernel, same arithmetic, only the scratch location differs
+            for name in a:
+                assert torch.equal(a[name], b[name]), f"{name} differs (B={B},T={T},C={C})"
+        else:
+            tol = 2e-2 if dtype == torch.bfloat16 else 1e-3
+            for name in ("gw", "gu", "gk", "gv"):
+                assert _rel(b[name].float(), a[name].float()) <= tol, name
+            # (gp,gq,go) stands for (gp,gq)*e^go: compare what it represents
+            for i in (0, 1):
+                x = b["gsi"][..., i].double() * torch.exp(b["gsi"][..., 2].double())
+                y = a["gsi"][..., i].double() * torch.exp(a["gsi"][..., 2].double())
+                assert _rel(x, y) <= tol, ("gstate_in", i)
 
 
 def test_static_scratch_rejects_oversized_problem_without_launching():
