@@ -159,26 +159,37 @@ k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, c
     float cp[NT], cq[NT], co[NT];   // state at the start of every tile of the segment
     float p = st[s], q = st[s + d.C], o = st[s + 2 * (size_t)d.C];
     float gw = 0.f, gu = 0.f, dpdw = 0.f, dqdw = 0.f;
-#pragma unroll
+    // every tile: its loads go out together (independent of the recurrence), then the chain runs.
+    // The tile loops stay rolled: unrolled, the compiler hoists the loads of all four tiles and
+    // runs out of registers; the 12 tile-start values then live in (L1-resident) local memory.
+#pragma unroll 1
     for (int tile = 0; tile < NT; tile++) {
         cp[tile] = p; cq[tile] = q; co[tile] = o;
+        if (tile * TILE < len) {
+            float kk[TILE], vv[TILE], gg[TILE];
 #pragma unroll
-        for (int j = 0; j < TILE; j++) {
-            const int t = tile * TILE + j;
-            if (t < len) {
-                const float kk = Elem<F>::ld(k_ + off + (size_t)t * d.C), vv = Elem<F>::ld(v_ + off + (size_t)t * d.C);
-                float A, E, m;
-                if (FINAL) {
-                    const float g = Elem<F>::ld(gy_ + off + (size_t)t * d.C);
-                    exp_pair(o, u + kk, A, E, m);
-                    const float iden = __fdividef(1.f, A * q + E);
-                    const float y = (A * p + E * vv) * iden;
-                    gw += g * (dpdw - dqdw * y) * iden * A;
-                    gu += g * (vv - y) * E * iden;
+            for (int j = 0; j < TILE; j++) {
+                const int t = tile * TILE + j;
+                const bool in = t < len;
+                kk[j] = in ? Elem<F>::ld(k_ + off + (size_t)t * d.C) : 0.f;
+                vv[j] = in ? Elem<F>::ld(v_ + off + (size_t)t * d.C) : 0.f;
+                gg[j] = (FINAL && in) ? Elem<F>::ld(gy_ + off + (size_t)t * d.C) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < TILE; j++) {
+                if (tile * TILE + j < len) {
+                    float A, E, m;
+                    if (FINAL) {
+                        exp_pair(o, u + kk[j], A, E, m);
+                        const float iden = __fdividef(1.f, A * q + E);
+                        const float y = (A * p + E * vv[j]) * iden;
+                        gw += gg[j] * (dpdw - dqdw * y) * iden * A;
+                        gu += gg[j] * (vv[j] - y) * E * iden;
+                    }
+                    exp_pair(w + o, kk[j], A, E, m);
+                    if (FINAL) { dpdw = A * (p + dpdw); dqdw = A * (q + dqdw); }
+                    p = A * p + E * vv[j]; q = A * q + E; o = m;
                 }
-                exp_pair(w + o, kk, A, E, m);
-                if (FINAL) { dpdw = A * (p + dpdw); dqdw = A * (q + dqdw); }
-                p = A * p + E * vv; q = A * q + E; o = m;
             }
         }
     }
@@ -187,22 +198,29 @@ k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, c
         gp = gend[s]; gq = gend[s + d.C]; go = gend[s + 2 * (size_t)d.C];
         gw += (gp * dpdw + gq * dqdw) * __expf(o + go);
     }
-#pragma unroll
+#pragma unroll 1
     for (int tile = NT - 1; tile >= 0; tile--) {
         if (tile * TILE < len) {
             p = cp[tile]; q = cq[tile]; o = co[tile];
-            float ys[TILE], zs[TILE], ze[TILE];
+            float kk[TILE], vv[TILE], gg[TILE];
 #pragma unroll
             for (int j = 0; j < TILE; j++) {
                 const int t = tile * TILE + j;
-                if (t < len) {
-                    const float kk = Elem<F>::ld(k_ + off + (size_t)t * d.C), vv = Elem<F>::ld(v_ + off + (size_t)t * d.C);
+                const bool in = t < len;
+                kk[j] = in ? Elem<F>::ld(k_ + off + (size_t)t * d.C) : 0.f;
+                vv[j] = in ? Elem<F>::ld(v_ + off + (size_t)t * d.C) : 0.f;
+                gg[j] = in ? Elem<F>::ld(gy_ + off + (size_t)t * d.C) : 0.f;
+            }
+            float ys[TILE], zs[TILE], ze[TILE];
+#pragma unroll
+            for (int j = 0; j < TILE; j++) {
+                if (tile * TILE + j < len) {
                     float A, E, m;
-                    exp_pair(o, u + kk, A, E, m);
+                    exp_pair(o, u + kk[j], A, E, m);
                     const float iden = __fdividef(1.f, A * q + E);
-                    ys[j] = (A * p + E * vv) * iden; zs[j] = iden; ze[j] = kk + u - m;
-                    exp_pair(w + o, kk, A, E, m);
-                    p = A * p + E * vv; q = A * q + E; o = m;
+                    ys[j] = (A * p + E * vv[j]) * iden; zs[j] = iden; ze[j] = kk[j] + u - m;
+                    exp_pair(w + o, kk[j], A, E, m);
+                    p = A * p + E * vv[j]; q = A * q + E; o = m;
                 }
             }
 #pragma unroll
@@ -210,17 +228,15 @@ k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, c
                 const int t = tile * TILE + j;
                 if (t < len) {
                     const size_t ii = off + (size_t)t * d.C;
-                    const float kk = Elem<F>::ld(k_ + ii), g = Elem<F>::ld(gy_ + ii);
-                    const float gz = g * zs[j];
+                    const float gz = gg[j] * zs[j];
                     float A, E, m;
                     if (FINAL) {
-                        const float vv = Elem<F>::ld(v_ + ii);
                         A = gz * __expf(ze[j]);
-                        E = __expf(kk + go);
-                        Elem<F>::st(gk_ + ii, A * (vv - ys[j]) + E * (gp * vv + gq));
+                        E = __expf(kk[j] + go);
+                        Elem<F>::st(gk_ + ii, A * (vv[j] - ys[j]) + E * (gp * vv[j] + gq));
                         Elem<F>::st(gv_ + ii, A + E * gp);
                     }
-                    exp_pair(w + go, ze[j] - kk - u, A, E, m);
+                    exp_pair(w + go, ze[j] - kk[j] - u, A, E, m);
                     E *= gz;
                     gp = A * gp + E; gq = A * gq - E * ys[j]; go = m;
                 }
