@@ -53,13 +53,14 @@ struct DscanParams {
     const float *gstate_out;
     float *gstate_in;
     __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
-    float *e0;           // [B*H, nchunk, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at the START of chunk j
+    float *e0;           // [B*H, nchunk+1, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at chunk boundary j
     int *status;
 };
 
 // Step i = 0..n-1 handles chunk j = n-1-i: with D_{j+1} in tensor memory it writes the D_{j+1}
-// checkpoint and E_{j+1} = rowsum(S_{j+1} * D_{j+1}) (the decay-gradient constant of chunk j+1),
-// then forms D_j = d_j D_{j+1} + (r e^{cp})^T gy.  A last step i = n only writes E_0 and D_0.
+// checkpoint and E_{j+1} = rowsum(S_{j+1} * D_{j+1}) (the decay-gradient constant at chunk
+// boundary j+1), then forms D_j = d_j D_{j+1} + (r e^{cp})^T gy.  A closing step i = n writes
+// E_0 and D_0.
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(128)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_gy,
@@ -89,14 +90,14 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
 
     auto issue_load = [&](int i) {
         const int st = i & 1, j = n - 1 - i;
-        const int tiles = (i < n ? (PER_TOKEN ? 3 : 2) : 0) + (i >= 1 ? 1 : 0);
+        const int tiles = (i < n ? (PER_TOKEN ? 3 : 2) : 0) + 1;
         mbar_expect_tx(&s.load_bar[st], tiles * TILE_BYTES);
         if (i < n) {
             tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
             tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
             if (PER_TOKEN) tma_load_3d(&s.in[st][2], &map_w, &s.load_bar[st], h * 64, j * CH, b);
         }
-        if (i >= 1) tma_load_3d(&s.in[st][3], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
+        tma_load_3d(&s.in[st][3], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
     };
     if (tid == 0) issue_load(0);
 
@@ -123,78 +124,81 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
         }
     }
 
-    uint32_t mma_phase = 0;
-    int fail = 0, aborted = 0, issued = 0, landed = -1;
-    tc_fence_before();
-    __syncthreads();
-
-    for (int i = 0; i <= n; i++) {
-        const int st = i & 1, j = n - 1 - i;
-        Tile *in = s.in[st];
-        if (i + 1 <= n) {
-            if (tid == 0) issue_load(i + 1);
-            issued = i + 1;
-        }
-        if (mbar_wait(&s.load_bar[st], (uint32_t)((i >> 1) & 1))) landed = i; else fail = 1;
-
-        if (i < n) {   // r e^{cp}, chunk decay
-            float c[4][8];
-            Decay D;
+    // operand pass of step i (chunk j = n-1-i): r e^{cp} in place, the chunk decay
+    auto prep = [&](int i) {
+        const int j = n - 1 - i;
+        Tile *in = s.in[i & 1];
+        float c[4][8];
+        Decay D;
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int t = tok0 + q;
-                const bool valid = j * CH + t < P.T;
-                if (PER_TOKEN) {
-                    float x[8];
-                    unpack8(ld_tile(in[2], t, cc), x);
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) {
-                        bool live;
-                        const float l2 = log2_decay(x[ch], P.w_kind, live);
-                        c[q][ch] = valid ? l2 : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) c[q][ch] = valid ? lwc[ch] : 0.f;
-                }
-            }
-            decay_scan(c, lane, D);
-            if (tgl == 7) {
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
-            }
-            __syncthreads();
-            float f[8];      // 2^{cp} counted from the chunk start
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                const float other = s.btot[blk ^ 1][cc * 8 + ch];
-                f[ch] = exp2f(blk ? D.cp0[ch] + other : D.cp0[ch]);
-                if (blk == 0 && tgl == 7) s.dvec[cc * 8 + ch] = exp2f(D.e[ch] + other);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int t = tok0 + q;
-                float rr[8];
-                unpack8(ld_tile(in[0], t, cc), rr);
+        for (int q = 0; q < 4; q++) {
+            const int t = tok0 + q;
+            const bool valid = j * CH + t < P.T;
+            if (PER_TOKEN) {
+                float x[8];
+                unpack8(ld_tile(in[2], t, cc), x);
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++) {
-                    rr[ch] *= f[ch];
-                    f[ch] *= D.w[q][ch];
+                    bool live;
+                    const float l2 = log2_decay(x[ch], P.w_kind, live);
+                    c[q][ch] = valid ? l2 : 0.f;
                 }
-                st_tile(in[0], t, cc, pack8(rr));
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) c[q][ch] = valid ? lwc[ch] : 0.f;
             }
         }
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(fail)) { aborted = 1; break; }
-        tc_fence_after();
+        decay_scan(c, lane, D);
+        if (tgl == 7) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
+        }
+        __syncthreads();
+        float f[8];      // 2^{cp} counted from the chunk start
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            const float other = s.btot[blk ^ 1][cc * 8 + ch];
+            f[ch] = exp2f(blk ? D.cp0[ch] + other : D.cp0[ch]);
+            if (blk == 0 && tgl == 7) s.dvec[cc * 8 + ch] = exp2f(D.e[ch] + other);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int t = tok0 + q;
+            float rr[8];
+            unpack8(ld_tile(in[0], t, cc), rr);
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                rr[ch] *= f[ch];
+                f[ch] *= D.w[q][ch];
+            }
+            st_tile(in[0], t, cc, pack8(rr));
+        }
+    };
 
+    uint32_t mma_phase = 0;
+    int fail = 0, aborted = 0, issued = 0, landed = -1;
+
+    // prologue: operands of step 0, load of step 1
+    if (mbar_wait(&s.load_bar[0], 0)) landed = 0; else fail = 1;
+    prep(0);
+    if (tid == 0) issue_load(1);      // n >= 1, so step 1 exists (it may be the closing step)
+    issued = 1;
+    fence_async_smem();
+    tc_fence_before();
+    if (__syncthreads_or(fail)) aborted = 1;
+    tc_fence_after();
+
+    // Software pipeline: while the tensor core forms D_j, the CUDA cores prepare step i+1.
+    for (int i = 0; i <= n && !aborted; i++) {
+        const int st = i & 1, j = n - 1 - i;
+        Tile *in = s.in[st];
+        float dnext = 0.f;
         {   // with D_{j+1} in hand: its checkpoint, E_{j+1}, then the decay
             float v[32];
             tmem_ld16(tmem_addr(tm, lane_base, 0), v);
             tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
             tmem_ld_wait();
-            if (i >= 1) {
+            {
                 float dot = 0.f;
 #pragma unroll
                 for (int c8 = 0; c8 < 4; c8++) {
@@ -204,7 +208,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                     for (int q = 0; q < 8; q++) dot += sv[q] * v[8 * c8 + q];
                 }
                 dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-                if (active) P.e0[((size_t)bh * n + (j + 1)) * 64 + row] = dot;
+                if (active) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + row] = dot;
             }
             if (i < n) {
                 const float d = s.dvec[row];
@@ -215,7 +219,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                 for (int c = 0; c < 32; c++) v[c] *= d;
                 tmem_st16(tmem_addr(tm, lane_base, 0), v);
                 tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
-            } else if (P.gstate_in) {   // last step: D_0 is the state gradient
+            } else if (P.gstate_in) {   // closing step: D_0 is the state gradient
 #pragma unroll
                 for (int q = 0; q < 32; q++) {
                     const int vc = vcol0 + q;
@@ -223,6 +227,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                     P.gstate_in[sbase + idx] = v[q];
                 }
             }
+            (void)dnext;
         }
         if (i == n) break;
         tmem_st_wait();
@@ -238,11 +243,21 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__
                 mma_ss(d, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k) + off, id, true);
             mma_commit(&s.mma_bar);
         }
+        // operands of the next step while the tensor core works
+        if (mbar_wait(&s.load_bar[(i + 1) & 1], (uint32_t)(((i + 1) >> 1) & 1))) landed = i + 1; else fail = 1;
+        if (i + 1 < n) prep(i + 1);
         if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
         mma_phase ^= 1;
         tc_fence_after();
+        fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
+        tc_fence_after();
+        // stage i&1 is free now
+        if (i + 2 <= n) {
+            if (tid == 0) issue_load(i + 2);
+            issued = i + 2;
+        }
     }
     if (aborted) {
         for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
@@ -277,7 +292,7 @@ struct BwdParams {
     int T, H, nchunk, w_kind;
     const __nv_bfloat16 *u;
     const float *wvec;
-    const float *e0;  // [B*H, nchunk, 64]: sum_v S_j[k,v] D_j[k,v] at the start of chunk j (from the dS scan)
+    const float *e0;  // [B*H, nchunk+1, 64]: sum_v S_j[k,v] D_j[k,v] at chunk boundary j (from the dS scan)
     float *gu_part;   // [B*H, nchunk, 64]
     float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
@@ -599,7 +614,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const float m0 = *ctab_ptr(ct_lo, ct_hi, 15, kch), e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch);
     const float m1 = *ctab_ptr(ct_lo, ct_hi, 47, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
     // decay-gradient constant of the chunk: sum_v S_j[k,v] D_j[k,v]
-    const float K0 = P.e0[((size_t)bh * n + j) * 64 + kch];
+    const float K0 = P.e0[((size_t)bh * (n + 1) + j) * 64 + kch];
     const float uk = __bfloat162float(P.u[h * 64 + kch]);
     float lw_static = 0.f;
     bool static_live = true;
@@ -739,7 +754,7 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     L.sck = 256;
     L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
-    L.gu_part = L.e0 + align256(bh * n * 64 * 4);
+    L.gu_part = L.e0 + align256(bh * (n + 1) * 64 * 4);
     L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
     L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
     return L;
