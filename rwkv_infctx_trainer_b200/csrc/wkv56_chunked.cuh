@@ -68,20 +68,23 @@ __device__ __forceinline__ float log2_decay(float x, int w_kind, bool &live) {
     return fmaxf(l2, L2_FLOOR);
 }
 
-struct Decay {
-    float w[4][8];   // decay of each of the thread's 4 tokens (1 past the segment end)
-    float cp0[8];    // log2-decay accumulated from the block start to before the thread's first token
-    float c3[8];     // ... up to and including its last token
-    float m[8];      // ... up to and including token 15 of the block (the block midpoint reference)
-    float e[8];      // the whole block
+template <int NCH>
+struct DecayT {
+    float w[4][NCH];   // decay of each of the thread's 4 tokens (1 past the segment end)
+    float cp0[NCH];    // log2-decay accumulated from the block start to before the thread's first token
+    float c3[NCH];     // ... up to and including its last token
+    float m[NCH];      // ... up to and including token 15 of the block (the block midpoint reference)
+    float e[NCH];      // the whole block
 };
+using Decay = DecayT<8>;
 
 // In: l2[i][ch] per-token log2-decay.  Out: l2 holds the block-local inclusive sums c
 // (local scan + scan over the 8 threads that share a column, which sit 4 lanes apart).
-__device__ __forceinline__ void decay_scan(float (&l2)[4][8], int lane, Decay &D) {
+template <int NCH>
+__device__ __forceinline__ void decay_scan(float (&l2)[4][NCH], int lane, DecayT<NCH> &D) {
     const int tgl = lane >> 2, ccl = lane & 3;
 #pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
+    for (int ch = 0; ch < NCH; ch++) {
 #pragma unroll
         for (int i = 0; i < 4; i++) D.w[i][ch] = exp2f(l2[i][ch]);
         const float first = l2[0][ch];
@@ -101,6 +104,19 @@ __device__ __forceinline__ void decay_scan(float (&l2)[4][8], int lane, Decay &D
         D.m[ch] = __shfl_sync(0xffffffffu, l2[3][ch], ccl + 12);   // tgl = 3: token 15 of the block
         D.e[ch] = __shfl_sync(0xffffffffu, l2[3][ch], ccl + 28);   // tgl = 7: token 31
     }
+}
+
+// 8-byte halves of a 16-byte tile chunk (4 bf16)
+__device__ __forceinline__ void unpack4(const uint2 &q, float *f) {
+    f[0] = __uint_as_float(q.x << 16); f[1] = __uint_as_float(q.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(q.y << 16); f[3] = __uint_as_float(q.y & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint2 pack4(const float *f) { return make_uint2(pack2(f[0], f[1]), pack2(f[2], f[3])); }
+__device__ __forceinline__ uint2 ld_tile4(const Tile &t, int row, int chunk, int half) {
+    return *reinterpret_cast<const uint2 *>(t.b + tile_off(row, chunk) + 8 * half);
+}
+__device__ __forceinline__ void st_tile4(Tile &t, int row, int chunk, int half, const uint2 &v) {
+    *reinterpret_cast<uint2 *>(t.b + tile_off(row, chunk) + 8 * half) = v;
 }
 
 }  // namespace chunked

@@ -26,6 +26,7 @@
 // Math reference: RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:70-293 (what the
 // gradients are), RWKV-v6/src/module/rwkv_inner.py:48-113 (the chunked form).
 #include <cstdlib>
+#include <type_traits>
 
 #include "wkv56_chunked.cuh"
 
@@ -293,8 +294,8 @@ struct BwdParams {
     const __nv_bfloat16 *u;
     const float *wvec;
     const float *e0;  // [B*H, nchunk+1, 64]: sum_v S_j[k,v] D_j[k,v] at chunk boundary j (from the dS scan)
-    float *gu_part;   // [B*H, nchunk, 64]
-    float *gw_part;   // v5 only: [B*H, nchunk, 64]
+    float *gu_part;   // [B*H, nchunk, 2, 64]  (one partial per token half of a chunk)
+    float *gw_part;   // v5 only: [B*H, nchunk, 2, 64]
     int *status;
     long long *timeline;  // optional: clock stamps of one CTA (phase boundaries), or NULL
 };
@@ -316,8 +317,17 @@ __device__ __forceinline__ float *ctab_ptr(Tile &a, Tile &b, int t, int k) {
     return reinterpret_cast<float *>((t < 32 ? a.b : b.b) + (t & 31) * 256) + k;
 }
 
+// Eight warps: warps 0..3 and 4..7 share the four 32-lane quarters of tensor memory (warp & 3).
+// The two groups split every CUDA-core phase: the operand pass by channels (4 of the 8 channels
+// of a tile chunk each), the
+// mask pass by score columns, the epilogue by tokens.  The decay-gradient recurrence runs forward
+// in both groups; group 1 (tokens 32..63) starts from zero, parks its fp32 values in tensor-memory
+// columns it has already consumed and adds the per-channel offset that group 0 publishes when it
+// reaches token 31.  (Walking group 1 backward from the chunk-end constant would need no offset,
+// but that constant comes from a separately rounded bf16 state and the small residuals of
+// strongly decaying channels do not survive the mismatch.)
 template <bool PER_TOKEN>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(256, 2)
 k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
             const __grid_constant__ CUtensorMap map_gy, const __grid_constant__ CUtensorMap map_s,
@@ -327,12 +337,13 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     BwdSmem &s = *reinterpret_cast<BwdSmem *>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wg = warp >> 2, w4 = warp & 3;
     const int n = P.nchunk;
     const int bh = blockIdx.x / n, j = blockIdx.x % n, b = bh / P.H, h = bh % P.H;
     const bool lo = (lane & 16) == 0;
-    const int row = warp * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
-    const uint32_t lane_base = (uint32_t)(warp * 32);
-    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
+    const int row = w4 * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
+    const uint32_t lane_base = (uint32_t)(w4 * 32);
+    const int blk = w4 >> 1, cc = 4 * (w4 & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
 
     // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise
     if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -343,7 +354,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
         mbar_init(&s.load_bar, 1);
-        mbar_init(&s.mma_bar, 4);   // lane 0 of every warp issues a share of each MMA group and commits
+        mbar_init(&s.mma_bar, 8);   // lane 0 of every warp issues a share of each MMA group and commits
         fence_mbar_init();
         mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
         tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
@@ -361,23 +372,23 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const uint32_t tm = s.tmem_base;
     const uint32_t tm_lo = tm, tm_hi = tm + (16u << 16);
 
-    float lwc[8];
-    bool livec[8];
+    // operand pass: this thread's 4 channels are 8*cc + 4*wg .. +3 (one 8-byte half of a tile chunk)
+    const int ch0 = cc * 8 + 4 * wg;
+    float lwc[4];
+    bool livec[4];
     if (!PER_TOKEN) {
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, livec[ch]);
-        }
+        for (int ch = 0; ch < 4; ch++) lwc[ch] = log2_decay(P.wvec[h * 64 + ch0 + ch], P.w_kind, livec[ch]);
     }
     int fail = 0;
     if (stamp) P.timeline[1] = clock64();
     if (!mbar_wait(&s.load_bar, 0)) fail = 1;
     if (stamp) P.timeline[2] = clock64();
 
-    // ---------------------------------------------------------------- prep
+    // ---------------------------------------------------------------- operand pass
     {
-        float c[4][8];
-        Decay D;
+        float c[4][4];
+        DecayT<4> D;
         unsigned livebits[4];
         // per-block totals are exchanged through the first bytes of the A~ tile (unused until the mask pass)
         float (*btot)[CH] = reinterpret_cast<float (*)[CH]>(s.atil.b);
@@ -387,10 +398,10 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             const bool valid = j * CH + t < P.T;
             livebits[i] = 0;
             if (PER_TOKEN) {
-                float x[8];
-                unpack8(ld_tile(s.in[T_W], t, cc), x);
+                float x[4];
+                unpack4(ld_tile4(s.in[T_W], t, cc, wg), x);
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
+                for (int ch = 0; ch < 4; ch++) {
                     bool live;
                     const float l2 = log2_decay(x[ch], P.w_kind, live);
                     livebits[i] |= (live ? 1u : 0u) << ch;
@@ -398,7 +409,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             } else {
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
+                for (int ch = 0; ch < 4; ch++) {
                     livebits[i] |= (livec[ch] ? 1u : 0u) << ch;
                     c[i][ch] = valid ? lwc[ch] : 0.f;
                 }
@@ -407,74 +418,72 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         decay_scan(c, lane, D);
         if (tgl == 7) {
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) btot[blk][cc * 8 + ch] = D.e[ch];
+            for (int ch = 0; ch < 4; ch++) btot[blk][ch0 + ch] = D.e[ch];
         }
         __syncthreads();   // block totals visible; every w value has been read, so its slot may take the table
-        float other_l2[8], other[8];
+        float other_l2[4], other[4];
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            other_l2[ch] = btot[blk ^ 1][cc * 8 + ch];
+        for (int ch = 0; ch < 4; ch++) {
+            other_l2[ch] = btot[blk ^ 1][ch0 + ch];
             other[ch] = exp2f(other_l2[ch]);
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = tok0 + i;
-            float cv[8];      // cumulative log2-decay counted from the chunk start; its lowest mantissa
+            float cv[4];      // cumulative log2-decay counted from the chunk start; its lowest mantissa
                               // bit is replaced by the "decay above the floor" flag of the token
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
+            for (int ch = 0; ch < 4; ch++) {
                 const float cabs = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
                 cv[ch] = __uint_as_float((__float_as_uint(cabs) & ~1u) | ((livebits[i] >> ch) & 1u));
             }
-            float4 *cdst = reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, cc * 8));
-            cdst[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
-            cdst[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
+            *reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, ch0)) = make_float4(cv[0], cv[1], cv[2], cv[3]);
         }
         // r-side operands, walking forward:  fa = 2^{cp - m};  block 1 also x = r 2^{cp}  (block-local cp)
-        float fa[8], fb[8];
+        float fa[4], fb[4];
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
+        for (int ch = 0; ch < 4; ch++) {
             fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
             fb[ch] = exp2f(D.cp0[ch]);
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int t = tok0 + i;
-            float r[8], rt[8], xx[8];
-            unpack8(ld_tile(s.in[T_R], t, cc), r);
+            float r[4], rt[4], xx[4];
+            unpack4(ld_tile4(s.in[T_R], t, cc, wg), r);
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
+            for (int ch = 0; ch < 4; ch++) {
                 rt[ch] = r[ch] * fa[ch];
                 xx[ch] = r[ch] * fb[ch];
                 fa[ch] *= D.w[i][ch];
                 fb[ch] *= D.w[i][ch];
             }
-            st_tile(s.rt, t, cc, pack8(rt));
-            if (blk) st_tile(s.x, t, cc, pack8(xx));
+            st_tile4(s.rt, t, cc, wg, pack4(rt));
+            if (blk) st_tile4(s.x, t, cc, wg, pack4(xx));
         }
         // k-side operands, walking backward:  fa = 2^{m - c};  fb = 2^{e - c}
         //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
+        for (int ch = 0; ch < 4; ch++) {
             fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
             fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
         }
 #pragma unroll
         for (int i = 3; i >= 0; i--) {
             const int t = tok0 + i;
-            float k[8], kt[8], kh[8], xx[8];
-            unpack8(ld_tile(s.in[T_K], t, cc), k);
+            float k[4], kt[4], kh[4], xx[4];
+            unpack4(ld_tile4(s.in[T_K], t, cc, wg), k);
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
+            for (int ch = 0; ch < 4; ch++) {
                 kt[ch] = k[ch] * fa[ch];
                 xx[ch] = k[ch] * fb[ch];
                 kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
                 fa[ch] *= D.w[i][ch];
                 fb[ch] *= D.w[i][ch];
             }
-            st_tile(s.kt, t, cc, pack8(kt));
-            if (!blk) st_tile(s.x, t, cc, pack8(xx));
-            st_tile(s.khat, t, cc, pack8(kh));
+            st_tile4(s.kt, t, cc, wg, pack4(kt));
+            if (!blk) st_tile4(s.x, t, cc, wg, pack4(xx));
+            st_tile4(s.khat, t, cc, wg, pack4(kh));
         }
     }
     fence_async_smem();
@@ -503,9 +512,12 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
         mma_commit(&s.mma_bar);
     }
-    // meanwhile (lo lanes): the bonus term of the score diagonal, sum_k r_t u k_t
+    // meanwhile: the bonus term of the score diagonal, sum_k r_t u k_t, in the thread that will
+    // own column t of row t in the mask pass
+    const int col0 = 32 * wg;                       // score columns this group masks
+    const bool own_diag = lo && ((row >= HB) == (wg == 1));
     float diag = 0.f;
-    if (lo) {
+    if (own_diag) {
 #pragma unroll
         for (int c8 = 0; c8 < 8; c8++) {
             float a[8], d[8], uq[8];
@@ -520,37 +532,40 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     tc_fence_after();
     if (stamp) P.timeline[4] = clock64();
 
-    // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t)
+    // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t); this group's 32 columns
     {
         const int t = row;
-        float a[64], a2[32];
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_A1 + c0), a + c0);
-        tmem_ld16(tmem_addr(tm, lane_base, C_A2), a2);
-        tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
+        float a[32], a2[32];
+        // columns col0..+31 of A1 (lo lanes) and of P (hi lanes) share their tensor-memory columns
+        tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0), a);
+        tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0 + 16), a + 16);
+        if (wg == 0 && w4 >= 2) {   // rows 32..63, columns 0..31: the cross-block scores
+            tmem_ld16(tmem_addr(tm, lane_base, C_A2), a2);
+            tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
+        }
         tmem_ld_wait();
         if (lo) {
+            const bool cross = wg == 0 && t >= HB;      // every entry kept
+            const bool empty = wg == 1 && t < HB;       // upper-right block
 #pragma unroll
-            for (int sx = 0; sx < 64; sx++) {
-                float val;
-                if (sx == t) val = diag;
-                else if (sx > t) val = 0.f;
-                else if (t >= HB && sx < HB) val = a2[sx & 31];
-                else val = a[sx];
-                a[sx] = val;
+            for (int q = 0; q < 32; q++) {
+                const int sx = col0 + q;
+                float val = cross ? a2[q] : a[q];
+                if (!cross) val = sx < t ? val : (sx == t ? diag : 0.f);
+                if (empty) val = 0.f;
+                a[q] = val;
             }
 #pragma unroll
-            for (int c8 = 0; c8 < 8; c8++) st_tile(s.atil, t, c8, pack8(a + 8 * c8));
+            for (int c8 = 0; c8 < 4; c8++) st_tile(s.atil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
         } else {
-            float pd = 0.f;
 #pragma unroll
-            for (int sx = 0; sx < 64; sx++) {
-                if (sx == t) pd = a[sx];
-                a[sx] = sx < t ? a[sx] : 0.f;
+            for (int q = 0; q < 32; q++) {
+                const int sx = col0 + q;
+                if (sx == t) s.ptt[t] = a[q];
+                a[q] = sx < t ? a[q] : 0.f;
             }
-            s.ptt[t] = pd;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; c8++) st_tile(s.ptil, t, c8, pack8(a + 8 * c8));
+            for (int c8 = 0; c8 < 4; c8++) st_tile(s.ptil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
         }
     }
     fence_async_smem();
@@ -596,11 +611,13 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int kk = 0; kk < 2; kk++)
                 mma_ss(tm_hi + C_G2, desc_mnmajor(&s.x, 32, kk), desc_mnmajor(&s.ptil, 32, kk), id_mm32, kk > 0);
-        } else {
-            // state parts: GS[k,t] = sum_v S[k,v] gy[t,v] (gr side), GS[k,s] = sum_v D[k,v] v[s,v] (gk side)
+        } else if (warp == 3) {
+            // gr state part: GS[k,t] = sum_v S[k,v] gy[t,v]
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm_lo + C_GS, desc_kmajor(&s.in[T_S], 0, k), desc_kmajor(&s.in[T_GY], 0, k), id_kk64, k > 0);
+        } else if (warp == 4) {
+            // gk state part: GS[k,s] = sum_v D[k,v] v[s,v]
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm_hi + C_GS, desc_kmajor(&s.in[T_D], 0, k), desc_kmajor(&s.in[T_V], 0, k), id_kk64, k > 0);
@@ -611,16 +628,14 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     // while the tensor core works: per-channel constants
     const int kch = row;   // channel owned in the epilogue
     Tile &ct_lo = s.in[T_W], &ct_hi = s.ctab_hi;
-    const float m0 = *ctab_ptr(ct_lo, ct_hi, 15, kch), e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch);
-    const float m1 = *ctab_ptr(ct_lo, ct_hi, 47, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
-    // decay-gradient constant of the chunk: sum_v S_j[k,v] D_j[k,v]
-    const float K0 = P.e0[((size_t)bh * (n + 1) + j) * 64 + kch];
+    const float e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
+    const float mb = *ctab_ptr(ct_lo, ct_hi, wg ? 47 : 15, kch);   // midpoint reference of this group's block
+    // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (group 1 starts from zero)
+    const float Kb = wg ? 0.f : P.e0[((size_t)bh * (n + 1) + j) * 64 + kch];
     const float uk = __bfloat162float(P.u[h * 64 + kch]);
     float lw_static = 0.f;
     bool static_live = true;
-    if (!PER_TOKEN) {
-        lw_static = log2_decay(P.wvec[h * 64 + kch], P.w_kind, static_live) * LN2;
-    }
+    if (!PER_TOKEN) lw_static = log2_decay(P.wvec[h * 64 + kch], P.w_kind, static_live) * LN2;
 
     if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
     tc_fence_after();
@@ -631,39 +646,41 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
     {
         const Tile &t_own = lo ? s.rt : s.kt;          // the scaled operand whose product with G1 is qI
-        float prefS = 0.f, preD = 0.f, C = 0.f, prev_qkI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
-        float c_prev = 0.f;   // c_{t-1}
+        // the cross-block accumulator G2 exists for tokens 32..63 on the gr side and 0..31 on the gk side
+        const bool has2 = lo ? (wg == 1) : (wg == 0);
+        // exponents: gr side  cp - mb, cp, cp - e0 ;  gk side  mb - c, e1 - c, e0 - c
+        const float sg = lo ? 1.f : -1.f;
+        const float o1 = lo ? -mb : mb, o2 = lo ? 0.f : e1, o3 = lo ? -e0 : e0;
+        // running sums of the decay-gradient recurrence (see the file header):
+        //   glw_t = K_j - sum_{t'<=t} qrS + sum_{s<t} qkD + C_t,      C_t = C_{t-1} + qkI_{t-1} - qrI_t
+        float accS = 0.f, accD = 0.f, C = 0.f, carryI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
+        int nvalid = 0;
 #pragma unroll 1
-        for (int t0 = 0; t0 < 64; t0 += 16) {
-            float g1[16], g2[16], gs[16];
-            tmem_ld16(tmem_addr(tm, lane_base, C_G1 + t0), g1);
-            tmem_ld16(tmem_addr(tm, lane_base, C_GS + t0), gs);
-            // G2 exists for tokens 32..63 on the gr side (columns t-32) and 0..31 on the gk side
-            tmem_ld16(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
-            const bool has2 = lo ? (t0 >= HB) : (t0 < HB);
-            const float mb = t0 >= HB ? m1 : m0;
-            // exponents: gr side  cp - mb, cp, cp - e0 ;  gk side  mb - c, e1 - c, e0 - c
-            const float sg = lo ? 1.f : -1.f;
-            const float o1 = lo ? -mb : mb, o2 = lo ? 0.f : e1, o3 = lo ? -e0 : e0;
+        for (int bt = 0; bt < 4; bt++) {
+            const int t0 = 32 * wg + 8 * bt;
+            float g1[8], g2[8], gs[8];
+            tmem_ld8(tmem_addr(tm, lane_base, C_G1 + t0), g1);
+            tmem_ld8(tmem_addr(tm, lane_base, C_GS + t0), gs);
+            tmem_ld8(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
             // stage 1: every shared-memory read of this batch
-            float vown[16], vx[16], vr[16], vk[16], vc[16], vpt[16];
+            float vown[8], vx[8], vr[8], vk[8], vc[9], vpt[8];
+            vc[0] = t0 > 0 ? *ctab_ptr(ct_lo, ct_hi, t0 - 1, kch) : 0.f;
 #pragma unroll
-            for (int q = 0; q < 16; q++) {
+            for (int q = 0; q < 8; q++) {
                 const int t = t0 + q;
                 vown[q] = ld_bf(t_own, t, kch);
                 vx[q] = ld_bf(s.x, t, kch);
                 vr[q] = ld_bf(s.in[T_R], t, kch);
                 vk[q] = ld_bf(s.in[T_K], t, kch);
-                vc[q] = *ctab_ptr(ct_lo, ct_hi, t, kch);
+                vc[q + 1] = *ctab_ptr(ct_lo, ct_hi, t, kch);
                 vpt[q] = s.ptt[t];
             }
             tmem_ld_wait();
             // stage 2: arithmetic, the lane exchange, and the running sums
-            float out[16], gwv[16];
+            float out[8], glwv[8], lmv[8];
 #pragma unroll
-            for (int q = 0; q < 16; q++) {
-                const float c = vc[q], cp = c_prev;
-                c_prev = c;
+            for (int q = 0; q < 8; q++) {
+                const float c = vc[q + 1], cp = vc[q];
                 const float b2 = has2 ? g2[q] : 0.f;
                 const float z = lo ? cp : c;
                 const float f1 = exp2f(fmaf(sg, z, o1)), fS = exp2f(fmaf(sg, z, o2));
@@ -674,44 +691,78 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 out[q] = f1 * g1[q] + f3 * b2 + fS * gs[q] + vpt[q] * uk * raw_other;
                 if (!lo) gu_acc += vpt[q] * vr[q] * vk[q];
                 // the gk lane hands its two terms to the gr lane of the same channel
-                const float o_qI = __shfl_xor_sync(0xffffffffu, qI, 16);
-                const float o_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
-                C += prev_qkI - qI;
-                prefS += qS;
-                const float glw = K0 - prefS + preD + C;
-                preD += o_qS;
-                prev_qkI = o_qI;
+                const float k_qI = __shfl_xor_sync(0xffffffffu, qI, 16);
+                const float k_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
+                C += carryI - qI;        // carryI = qkI of the previous token
+                accS += qS;
+                glwv[q] = Kb - accS + accD + C;
+                accD += k_qS;
+                carryI = k_qI;
                 if (PER_TOKEN) {
-                    const float l = (c - cp) * LN2;   // floored log-decay of this token
-                    gwv[q] = (__float_as_uint(c) & 1u) ? glw * l : 0.f;
+                    // floored log-decay of this token, zero where the floor was hit (no gradient)
+                    lmv[q] = (__float_as_uint(c) & 1u) ? (c - cp) * LN2 : 0.f;
                 } else if (j * CH + t0 + q < P.T) {
-                    gw_acc += glw;
+                    gw_acc += glwv[q];
+                    nvalid++;
                 }
             }
             // stage 3: stores
             if (lo) {
 #pragma unroll
-                for (int q = 0; q < 16; q++) {
+                for (int q = 0; q < 8; q++) {
                     st_bf(o_gr, t0 + q, kch, out[q]);
-                    if (PER_TOKEN) st_bf(o_gw, t0 + q, kch, gwv[q]);
+                    if (PER_TOKEN && wg == 0) st_bf(o_gw, t0 + q, kch, glwv[q] * lmv[q]);
                 }
             } else {
 #pragma unroll
-                for (int q = 0; q < 16; q++) st_bf(o_gk, t0 + q, kch, out[q]);
+                for (int q = 0; q < 8; q++) st_bf(o_gk, t0 + q, kch, out[q]);
+            }
+            if (PER_TOKEN && wg == 1) {
+                // park the offset-free values in the accumulator columns this batch has consumed
+                tmem_st8(tmem_addr(tm, lane_base, C_G1 + t0), glwv);
+                tmem_st8(tmem_addr(tm, lane_base, C_GS + t0), lmv);
             }
         }
-        if (!lo) P.gu_part[((size_t)bh * n + j) * 64 + kch] = gu_acc;
-        if (!PER_TOKEN && lo) P.gw_part[((size_t)bh * n + j) * 64 + kch] = static_live ? gw_acc * lw_static : 0.f;
-    }
-    // gv: accumulator [v, s]; lo lanes own value channel v
-    {
-        float gv[64];
+        // group 0 publishes what group 1's recurrence was missing: with the sums after token 31,
+        // glw_t (t >= 32) = parked value + K_j - accS + accD + C + qkI_31
+        float *off = reinterpret_cast<float *>(s.khat.b);     // khat's last reader was phase 2
+        if (wg == 0 && lo) off[kch] = Kb - accS + accD + C + carryI;
+        if (PER_TOKEN && wg == 1) tmem_st_wait();
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        if (wg == 1) {
+            const float offk = off[kch];
+            if (PER_TOKEN) {
+#pragma unroll 1
+                for (int bt = 0; bt < 4; bt++) {
+                    const int t0 = 32 + 8 * bt;
+                    float glwv[8], lmv[8];
+                    tmem_ld8(tmem_addr(tm, lane_base, C_G1 + t0), glwv);
+                    tmem_ld8(tmem_addr(tm, lane_base, C_GS + t0), lmv);
+                    tmem_ld_wait();
+                    if (lo) {
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem_addr(tm, lane_base, C_GV + c0), gv + c0);
+                        for (int q = 0; q < 8; q++) st_bf(o_gw, t0 + q, kch, (glwv[q] + offk) * lmv[q]);
+                    }
+                }
+            } else {
+                gw_acc += nvalid * offk;
+            }
+        }
+        // per-(chunk, token-half) partials, folded later in a fixed order
+        if (!lo) P.gu_part[(((size_t)bh * n + j) * 2 + wg) * 64 + kch] = gu_acc;
+        if (!PER_TOKEN && lo) P.gw_part[(((size_t)bh * n + j) * 2 + wg) * 64 + kch] = static_live ? gw_acc * lw_static : 0.f;
+    }
+    // gv: accumulator [v, s]; lo lanes own value channel v, this group's 32 tokens
+    {
+        float gv[32];
+        tmem_ld16(tmem_addr(tm, lane_base, C_GV + col0), gv);
+        tmem_ld16(tmem_addr(tm, lane_base, C_GV + col0 + 16), gv + 16);
         tmem_ld_wait();
         if (lo) {
 #pragma unroll
-            for (int t = 0; t < 64; t++) st_bf(o_gv, t, kch, gv[t]);
+            for (int t = 0; t < 32; t++) st_bf(o_gv, col0 + t, kch, gv[t]);
         }
     }
     fence_async_smem();
@@ -755,8 +806,8 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.gu_part = L.e0 + align256(bh * (n + 1) * 64 * 4);
-    L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
-    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
+    L.gw_part = L.gu_part + align256(bh * n * 2 * 64 * 4);
+    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 2 * 64 * 4));
     return L;
 }
 
@@ -817,14 +868,14 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return WKV_ERR_LAUNCH;
-        kern<<<B * H * n, 128, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
+        kern<<<B * H * n, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 4. fold the per-chunk partial sums
     {
         const int total = B * H * 64;
-        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, n, total);
-        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, n, total);
+        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, 2 * n, total);
+        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, 2 * n, total);
     }
     return launch_status();
 }
