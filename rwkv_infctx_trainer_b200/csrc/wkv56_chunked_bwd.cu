@@ -282,6 +282,7 @@ struct BwdSmem {
     Tile atil, ptil;           // masked scores A (with diagonal), P~
     Tile ctab_hi;              // rows 32..63 of the cumulative-decay table
     float ptt[CH];
+    float kb[CH];              // decay-gradient constant of the chunk start, per channel
     uint64_t load_bar;
     uint64_t mma_bar;
     uint32_t tmem_base;
@@ -294,27 +295,52 @@ struct BwdParams {
     const __nv_bfloat16 *u;
     const float *wvec;
     const float *e0;  // [B*H, nchunk+1, 64]: sum_v S_j[k,v] D_j[k,v] at chunk boundary j (from the dS scan)
-    float *gu_part;   // [B*H, nchunk, 2, 64]  (one partial per token half of a chunk)
-    float *gw_part;   // v5 only: [B*H, nchunk, 2, 64]
+    float *gu_part;   // [B*H, nchunk, 64]
+    float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
     long long *timeline;  // optional: clock stamps of one CTA (phase boundaries), or NULL
+    int stop;  // TEMP profiling aid
 };
 
-// tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31
-enum { C_A1 = 0, C_A2 = 64, C_P = 0,                                  // phase 1 (P in hi)
-       C_G1 = 0, C_G2 = 64, C_GS = 96, C_GV = 160, BWD_TMEM_COLS = 256 };  // phase 2
+// tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31.
+// Phase 1: A1 and A2 in lo, P in hi (full 64-column score rows).  The state products of phase 1
+// and everything of phase 2 are [token, 32 channels] with channels 0..31 in lo and 32..63 in hi.
+enum { C_GSR = 0, C_GSK = 32,                                          // phase 1, read by the epilogue
+       C_A1 = 64, C_P = 64, C_A2 = 128,                                // phase 1, read by the mask pass
+       C_G1R = 64, C_G2R = 96, C_G1K = 128, C_G2K = 160, C_GV = 192,   // phase 2
+       BWD_TMEM_COLS = 256 };
 
-__device__ __forceinline__ float ld_bf(const Tile &t, int row, int col) {
-    const unsigned short h =
-        *reinterpret_cast<const unsigned short *>(t.b + tile_off(row, col >> 3) + ((col & 7) << 1));
-    return __uint_as_float((uint32_t)h << 16);
+// fp32 cumulative log-decay table c[t][k]: rows 0..31 in `a`, rows 32..63 in `b`, 256 bytes per row;
+// the 16-byte column index is XORed with (t & 7) so that 8 consecutive rows of one column fall into
+// 8 different bank groups
+__device__ __forceinline__ float4 *ctab_ptr4(Tile &a, Tile &b, int t, int col4) {
+    return reinterpret_cast<float4 *>((t < 32 ? a.b : b.b) + (t & 31) * 256 + ((col4 ^ (t & 7)) << 4));
 }
-__device__ __forceinline__ void st_bf(Tile &t, int row, int col, float v) {
-    *reinterpret_cast<__nv_bfloat16 *>(t.b + tile_off(row, col >> 3) + ((col & 7) << 1)) = __float2bfloat16_rn(v);
+// channels 8*c8 .. +7 of row t
+__device__ __forceinline__ void ld_ctab8(Tile &a, Tile &b, int t, int c8, float *v) {
+    const float4 p = *ctab_ptr4(a, b, t, 2 * c8), q = *ctab_ptr4(a, b, t, 2 * c8 + 1);
+    v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w;
+    v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
 }
-// fp32 cumulative log-decay table c[t][k]: rows 0..31 in `a`, rows 32..63 in `b`
-__device__ __forceinline__ float *ctab_ptr(Tile &a, Tile &b, int t, int k) {
-    return reinterpret_cast<float *>((t < 32 ? a.b : b.b) + (t & 31) * 256) + k;
+// Sum of each of 8 values over the 16 lanes of a half-warp.  The lanes exchange halves of the
+// vector (8 -> 4 -> 2 -> 1 values); lanes 2i and 2i+1 both end with the total of value i.
+__device__ __forceinline__ float halving_sum8(const float *v, int l16) {
+    float a4[4], a2[2];
+    const bool b3 = l16 & 8, b2 = l16 & 4, b1 = l16 & 2;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float send = b3 ? v[i] : v[4 + i];
+        a4[i] = (b3 ? v[4 + i] : v[i]) + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float send = b2 ? a4[i] : a4[2 + i];
+        a2[i] = (b2 ? a4[2 + i] : a4[i]) + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    const float send = b1 ? a2[0] : a2[1];
+    float r = (b1 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, send, 2);
+    r += __shfl_xor_sync(0xffffffffu, r, 1);
+    return r;
 }
 
 // Eight warps: warps 0..3 and 4..7 share the four 32-lane quarters of tensor memory (warp & 3).
@@ -351,6 +377,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         return;
     }
     const bool stamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && tid == 0;
+    const bool stamp2 = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && (tid & 127) == 0;
     if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
         mbar_init(&s.load_bar, 1);
@@ -437,7 +464,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const float cabs = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
                 cv[ch] = __uint_as_float((__float_as_uint(cabs) & ~1u) | ((livebits[i] >> ch) & 1u));
             }
-            *reinterpret_cast<float4 *>(ctab_ptr(s.in[T_W], s.ctab_hi, t, ch0)) = make_float4(cv[0], cv[1], cv[2], cv[3]);
+            *ctab_ptr4(s.in[T_W], s.ctab_hi, t, ch0 >> 2) = make_float4(cv[0], cv[1], cv[2], cv[3]);
         }
         // r-side operands, walking forward:  fa = 2^{cp - m};  block 1 also x = r 2^{cp}  (block-local cp)
         float fa[4], fb[4];
@@ -490,8 +517,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     tc_fence_before();
     const int abort1 = __syncthreads_or(fail);
     if (stamp) P.timeline[3] = clock64();
+    if (P.stop == 1) { if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
 
-    // ------------------------------------------------- phase 1: A1, A2, P
+    // ------------------------------------------------- phase 1: A1, A2, P and the state products
     // (a tcgen05.mma is issued by one thread and costs it ~100 cycles of descriptor
     // arithmetic: the accumulators of a group go out from different warps at once)
     if (!abort1 && lane == 0) {
@@ -509,17 +537,30 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
+        } else if (warp < 5) {
+            // gr state part: GSr[t, k] = sum_v gy[t,v] S[k,v]; channels 0..31 in lo, 32..63 in hi lanes
+            const int hf = warp - 3;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss((hf ? tm_hi : tm_lo) + C_GSR, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_S], 32 * hf, k), id32, k > 0);
+        } else if (warp < 7) {
+            // gk state part: GSk[s, k] = sum_v v[s,v] D[k,v]
+            const int hf = warp - 5;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss((hf ? tm_hi : tm_lo) + C_GSK, desc_kmajor(&s.in[T_V], 0, k), desc_kmajor(&s.in[T_D], 32 * hf, k), id32, k > 0);
         }
         mma_commit(&s.mma_bar);
     }
-    // meanwhile: the bonus term of the score diagonal, sum_k r_t u k_t, in the thread that will
-    // own column t of row t in the mask pass
+    // meanwhile: the bonus term of the score diagonal, sum_k r_t u k_t, in the warps whose 16 rows x
+    // 32 columns straddle the diagonal; the lo lane takes channels 0..31 of the row, the hi lane 32..63
     const int col0 = 32 * wg;                       // score columns this group masks
-    const bool own_diag = lo && ((row >= HB) == (wg == 1));
+    const bool diag_warp = (w4 >= 2) == (wg == 1), cross_warp = wg == 0 && w4 >= 2;
     float diag = 0.f;
-    if (own_diag) {
+    if (diag_warp) {
 #pragma unroll
-        for (int c8 = 0; c8 < 8; c8++) {
+        for (int c = 0; c < 4; c++) {
+            const int c8 = (lo ? 0 : 4) + c;
             float a[8], d[8], uq[8];
             unpack8(ld_tile(s.in[T_R], row, c8), a);
             unpack8(ld_tile(s.in[T_K], row, c8), d);
@@ -527,244 +568,309 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 8; q++) diag += a[q] * uq[q] * d[q];
         }
+        diag += __shfl_xor_sync(0xffffffffu, diag, 16);
     }
     if (!abort1 && !mbar_wait(&s.mma_bar, 0)) fail = 1;
     tc_fence_after();
     if (stamp) P.timeline[4] = clock64();
 
-    // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t); this group's 32 columns
+    // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t); this group's 32 columns.
+    // P~ is split: its two same-block triangles go to the P~ tile (cross block zero), the
+    // cross block (t >= 32, s < 32) to the same rows of the v tile, whose readers are done.
     {
         const int t = row;
-        float a[32], a2[32];
+        float a[32];
         // columns col0..+31 of A1 (lo lanes) and of P (hi lanes) share their tensor-memory columns
-        tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0), a);
-        tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0 + 16), a + 16);
-        if (wg == 0 && w4 >= 2) {   // rows 32..63, columns 0..31: the cross-block scores
+        if (diag_warp || cross_warp) {
+            tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0), a);
+            tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0 + 16), a + 16);
+        }
+        if (cross_warp) {           // rows 32..63, columns 0..31: every entry kept; A~ takes the cross-block scores
+            float a2[32];
             tmem_ld16(tmem_addr(tm, lane_base, C_A2), a2);
             tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 32; q++) a[q] = lo ? a2[q] : a[q];
+        } else if (diag_warp) {
+            tmem_ld_wait();
+            // local row lim = t - col0: columns below it are kept, column lim is the diagonal (the bonus
+            // term in A~, p_tt set aside and zero in P~).  Rows 0..15 of the block cannot reach columns
+            // 16..31, rows 16..31 keep all of columns 0..15.
+            const float dval = lo ? diag : 0.f;
+            float pt = 0.f;
+            if ((w4 & 1) == 0) {
+                const int lim = t - col0;
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    if (q == lim) pt = a[q];
+                    a[q] = q < lim ? a[q] : (q == lim ? dval : 0.f);
+                    a[16 + q] = 0.f;
+                }
+            } else {
+                const int lim = t - col0 - 16;
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    if (q == lim) pt = a[16 + q];
+                    a[16 + q] = q < lim ? a[16 + q] : (q == lim ? dval : 0.f);
+                }
+            }
+            if (!lo) s.ptt[t] = pt;
+        } else {                    // upper-right block: nothing survives
+#pragma unroll
+            for (int q = 0; q < 32; q++) a[q] = 0.f;
         }
-        tmem_ld_wait();
-        if (lo) {
-            const bool cross = wg == 0 && t >= HB;      // every entry kept
-            const bool empty = wg == 1 && t < HB;       // upper-right block
+        Tile &dst = lo ? s.atil : (cross_warp ? s.in[T_V] : s.ptil);
 #pragma unroll
-            for (int q = 0; q < 32; q++) {
-                const int sx = col0 + q;
-                float val = cross ? a2[q] : a[q];
-                if (!cross) val = sx < t ? val : (sx == t ? diag : 0.f);
-                if (empty) val = 0.f;
-                a[q] = val;
-            }
+        for (int c8 = 0; c8 < 4; c8++) st_tile(dst, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
+        if (cross_warp && !lo) {
 #pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) st_tile(s.atil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
-        } else {
-#pragma unroll
-            for (int q = 0; q < 32; q++) {
-                const int sx = col0 + q;
-                if (sx == t) s.ptt[t] = a[q];
-                a[q] = sx < t ? a[q] : 0.f;
-            }
-#pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) st_tile(s.ptil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
+            for (int c8 = 0; c8 < 4; c8++) st_tile(s.ptil, t, c8, make_uint4(0u, 0u, 0u, 0u));
         }
     }
     fence_async_smem();
     tc_fence_before();
     const int abort2 = __syncthreads_or(fail) | abort1;
     if (stamp) P.timeline[5] = clock64();
+    if (P.stop == 2) { if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
 
-    // ------------------------------------------------- phase 2
+    // ------------------------------------------------- phase 2: token-major accumulators
+    // every accumulator is [token, 32 channels]: channels 0..31 in the lo lanes, 32..63 in the hi lanes
     if (!abort2 && lane == 0) {
         tc_fence_after();
-        const uint32_t id_mk32 = make_idesc(64, 32, true, false), id_mm32 = make_idesc(64, 32, true, true);
-        const uint32_t id_kk64 = make_idesc(64, 64, false, false);
-        if (warp == 0) {
-            // gv^T[v,s] = gy^T A~ + D^T khat^T
-            const uint32_t id_mm = make_idesc(64, 64, true, true), id_mk = make_idesc(64, 64, true, false);
+        const uint32_t id_kn = make_idesc(64, 32, false, true), id_nn = make_idesc(64, 32, true, true);
+        const int hf = warp & 1;
+        const uint32_t tmh = hf ? tm_hi : tm_lo;
+        const uint64_t boff = hf ? 4 : 0;     // +64 bytes: the upper 32 of the 64 contiguous elements
+        if (warp < 2) {
+            // gv[s, v] = sum_t A~[t,s] gy[t,v] + sum_k khat[s,k] D[k,v]
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm_lo + C_GV, desc_mnmajor(&s.in[T_GY], 0, k), desc_mnmajor(&s.atil, 0, k), id_mm, k > 0);
+                mma_ss(tmh + C_GV, desc_mnmajor(&s.atil, 0, k), desc_mnmajor(&s.in[T_GY], 0, k) + boff, id_nn, k > 0);
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm_lo + C_GV, desc_mnmajor(&s.in[T_D], 0, k), desc_kmajor(&s.khat, 0, k), id_mk, true);
-        } else if (warp == 1) {
-            // gr intra, same block: G1[k,t] = sum_{s in blk} Kt[s,k] P~[t,s]
-#pragma unroll
-            for (int bl = 0; bl < 2; bl++)
-#pragma unroll
-                for (int kk = 0; kk < 2; kk++)
-                    mma_ss(tm_lo + C_G1 + 32 * bl, desc_mnmajor(&s.kt, 32 * bl, kk),
-                           desc_kmajor(&s.ptil, 32 * bl, 2 * bl + kk), id_mk32, kk > 0);
-            // gr intra, across blocks: G2[k, t in blk1] = sum_{s<32} X[s,k] P~[t,s]
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-                mma_ss(tm_lo + C_G2, desc_mnmajor(&s.x, 0, kk), desc_kmajor(&s.ptil, 32, kk), id_mk32, kk > 0);
-        } else if (warp == 2) {
-            // gk intra, same block: G1[k,s] = sum_{t in blk} Rt[t,k] P~[t,s]
-#pragma unroll
-            for (int bl = 0; bl < 2; bl++)
-#pragma unroll
-                for (int kk = 0; kk < 2; kk++)
-                    mma_ss(tm_hi + C_G1 + 32 * bl, desc_mnmajor(&s.rt, 32 * bl, kk),
-                           desc_mnmajor(&s.ptil, 32 * bl, kk) + (bl ? 4 : 0), id_mm32, kk > 0);
-            // gk intra, across blocks: G2[k, s<32] = sum_{t>=32} X[t,k] P~[t,s]
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-                mma_ss(tm_hi + C_G2, desc_mnmajor(&s.x, 32, kk), desc_mnmajor(&s.ptil, 32, kk), id_mm32, kk > 0);
-        } else if (warp == 3) {
-            // gr state part: GS[k,t] = sum_v S[k,v] gy[t,v]
+                mma_ss(tmh + C_GV, desc_kmajor(&s.khat, 0, k), desc_mnmajor(&s.in[T_D], 0, k) + boff, id_kn, true);
+        } else if (warp < 4) {
+            // gr intra, same block: G1r[t,k] = sum_s P~d[t,s] Kt[s,k]
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm_lo + C_GS, desc_kmajor(&s.in[T_S], 0, k), desc_kmajor(&s.in[T_GY], 0, k), id_kk64, k > 0);
-        } else if (warp == 4) {
-            // gk state part: GS[k,s] = sum_v D[k,v] v[s,v]
+                mma_ss(tmh + C_G1R, desc_kmajor(&s.ptil, 0, k), desc_mnmajor(&s.kt, 0, k) + boff, id_kn, k > 0);
+        } else if (warp < 6) {
+            // gk intra, same block: G1k[s,k] = sum_t P~d[t,s] Rt[t,k]
 #pragma unroll
             for (int k = 0; k < 4; k++)
-                mma_ss(tm_hi + C_GS, desc_kmajor(&s.in[T_D], 0, k), desc_kmajor(&s.in[T_V], 0, k), id_kk64, k > 0);
+                mma_ss(tmh + C_G1K, desc_mnmajor(&s.ptil, 0, k), desc_mnmajor(&s.rt, 0, k) + boff, id_nn, k > 0);
+        } else if (warp == 6) {
+            // gr intra, across blocks: G2r[t >= 32, k] = sum_{s<32} P~x[t,s] X[s,k]   (rows t < 32 are not read)
+#pragma unroll
+            for (int hq = 0; hq < 2; hq++)
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+                    mma_ss((hq ? tm_hi : tm_lo) + C_G2R, desc_kmajor(&s.in[T_V], 0, k),
+                           desc_mnmajor(&s.x, 0, k) + (hq ? 4 : 0), id_kn, k > 0);
+        } else {
+            // gk intra, across blocks: G2k[s < 32, k] = sum_{t>=32} P~x[t,s] X[t,k]   (rows s >= 32 are not read)
+#pragma unroll
+            for (int hq = 0; hq < 2; hq++)
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+                    mma_ss((hq ? tm_hi : tm_lo) + C_G2K, desc_mnmajor(&s.in[T_V], 32, k),
+                           desc_mnmajor(&s.x, 32, k) + (hq ? 4 : 0), id_nn, k > 0);
         }
         mma_commit(&s.mma_bar);
     }
 
-    // while the tensor core works: per-channel constants
-    const int kch = row;   // channel owned in the epilogue
+    // ------------------------------------------------- epilogue
+    // A thread owns token t = row and the 32 channels of its lane half; group 0 is the gr side,
+    // group 1 the gk side.  Output staging reuses tiles whose last reader was phase 2:
+    // gr->atil, gk->ptil, gw->v, gv->gy; S, D and khat serve as scratch.
+    Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
     Tile &ct_lo = s.in[T_W], &ct_hi = s.ctab_hi;
-    const float e0 = *ctab_ptr(ct_lo, ct_hi, 31, kch), e1 = *ctab_ptr(ct_lo, ct_hi, 63, kch);
-    const float mb = *ctab_ptr(ct_lo, ct_hi, wg ? 47 : 15, kch);   // midpoint reference of this group's block
-    // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (group 1 starts from zero)
-    const float Kb = wg ? 0.f : P.e0[((size_t)bh * (n + 1) + j) * 64 + kch];
-    const float uk = __bfloat162float(P.u[h * 64 + kch]);
-    float lw_static = 0.f;
-    bool static_live = true;
-    if (!PER_TOKEN) lw_static = log2_decay(P.wvec[h * 64 + kch], P.w_kind, static_live) * LN2;
+    const int t = row, hh = lane >> 4, l16 = lane & 15;
+    const float ptt_t = s.ptt[t];
+    const bool tvalid = j * CH + t < P.T;
+    float *wtot = reinterpret_cast<float *>(s.khat.b);           // [4][64] per-warp totals of the token scan
+    float *gup = wtot + 4 * CH, *gwp = gup + 4 * CH;             // [4][64] per-warp sums for gu / the static gw
+    float keep[16];   // group 0: a_t of its first 16 channels; group 1: b_t of its last 16 channels
 
+    // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (consumed after two more barriers)
+    if (tid < CH) s.kb[tid] = P.e0[((size_t)bh * (n + 1) + j) * 64 + tid];
     if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
     tc_fence_after();
     if (stamp) P.timeline[6] = clock64();
 
-    // ------------------------------------------------- epilogue: gr (lo lanes), gk (hi lanes), gw
-    // output staging reuses tiles whose last reader was phase 2: gr->atil, gk->ptil, gw->v, gv->gy
-    Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
-    {
-        const Tile &t_own = lo ? s.rt : s.kt;          // the scaled operand whose product with G1 is qI
-        // the cross-block accumulator G2 exists for tokens 32..63 on the gr side and 0..31 on the gk side
-        const bool has2 = lo ? (wg == 1) : (wg == 0);
-        // exponents: gr side  cp - mb, cp, cp - e0 ;  gk side  mb - c, e1 - c, e0 - c
-        const float sg = lo ? 1.f : -1.f;
-        const float o1 = lo ? -mb : mb, o2 = lo ? 0.f : e1, o3 = lo ? -e0 : e0;
-        // running sums of the decay-gradient recurrence (see the file header):
-        //   glw_t = K_j - sum_{t'<=t} qrS + sum_{s<t} qkD + C_t,      C_t = C_{t-1} + qkI_{t-1} - qrI_t
-        float accS = 0.f, accD = 0.f, C = 0.f, carryI = 0.f, gu_acc = 0.f, gw_acc = 0.f;
-        int nvalid = 0;
+    // The decay gradient of token t is  glw_t = K_j + sum_{t'<=t} (a_t' + b_t') - b_t  with
+    //   a_t = -(qrS_t + qrI_t)   (gr side),     b_t = qkD_t + qkI_t   (gk side),
+    // qrS/qkD the state parts of r*gr and k*gk and qrI/qkI their intra-chunk parts (file header).
+    auto side_pass = [&](auto side_tag) {
+        constexpr bool GR = decltype(side_tag)::value;
+        const bool has2 = GR ? (w4 >= 2) : (w4 < 2);         // the cross-block accumulator covers this token
+        const Tile &t_own = GR ? s.rt : s.kt;
+        const Tile &t_raw = GR ? s.in[T_R] : s.in[T_K], &t_oth = GR ? s.in[T_K] : s.in[T_R];
+        constexpr int cGS = GR ? C_GSR : C_GSK, cG1 = GR ? C_G1R : C_G1K, cG2 = GR ? C_G2R : C_G2K;
+        Tile &o_main = GR ? o_gr : o_gk;
+        Tile &exch = GR ? s.in[T_S] : s.in[T_D];              // what the other group needs from this one
+        const int zrow = GR ? t - 1 : t;                      // gr factors use c_{t-1}, gk factors c_t
+        const int mrow = t < HB ? 15 : 47;
 #pragma unroll 1
         for (int bt = 0; bt < 4; bt++) {
-            const int t0 = 32 * wg + 8 * bt;
-            float g1[8], g2[8], gs[8];
-            tmem_ld8(tmem_addr(tm, lane_base, C_G1 + t0), g1);
-            tmem_ld8(tmem_addr(tm, lane_base, C_GS + t0), gs);
-            tmem_ld8(tmem_addr(tm, lane_base, C_G2 + (t0 & 31)), g2);
-            // stage 1: every shared-memory read of this batch
-            float vown[8], vx[8], vr[8], vk[8], vc[9], vpt[8];
-            vc[0] = t0 > 0 ? *ctab_ptr(ct_lo, ct_hi, t0 - 1, kch) : 0.f;
+            const int c8 = 4 * hh + bt;       // 16-byte column of the bf16 tiles; channels 8*c8 .. +7
+            float g1[8], gs[8], g2[8];
+            tmem_ld8(tmem_addr(tm, lane_base, cG1 + 8 * bt), g1);
+            tmem_ld8(tmem_addr(tm, lane_base, cGS + 8 * bt), gs);
+            if (has2) tmem_ld8(tmem_addr(tm, lane_base, cG2 + 8 * bt), g2);
+            float own[8], raw[8], oth[8], xx[8], uu[8], z[8], mb[8], e0r[8], e1r[8];
+            unpack8(ld_tile(t_own, t, c8), own);
+            unpack8(ld_tile(t_raw, t, c8), raw);
+            unpack8(ld_tile(t_oth, t, c8), oth);
+            unpack8(__ldg(reinterpret_cast<const uint4 *>(P.u + h * 64) + c8), uu);
+            ld_ctab8(ct_lo, ct_hi, mrow, c8, mb);
+            if (zrow >= 0) {
+                ld_ctab8(ct_lo, ct_hi, zrow, c8, z);
+            } else {
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const int t = t0 + q;
-                vown[q] = ld_bf(t_own, t, kch);
-                vx[q] = ld_bf(s.x, t, kch);
-                vr[q] = ld_bf(s.in[T_R], t, kch);
-                vk[q] = ld_bf(s.in[T_K], t, kch);
-                vc[q + 1] = *ctab_ptr(ct_lo, ct_hi, t, kch);
-                vpt[q] = s.ptt[t];
+                for (int q = 0; q < 8; q++) z[q] = 0.f;
+            }
+            if (!GR) ld_ctab8(ct_lo, ct_hi, 63, c8, e1r);
+            if (has2) {
+                unpack8(ld_tile(s.x, t, c8), xx);
+                ld_ctab8(ct_lo, ct_hi, 31, c8, e0r);
             }
             tmem_ld_wait();
-            // stage 2: arithmetic, the lane exchange, and the running sums
-            float out[8], glwv[8], lmv[8];
+            float out[8], ab[8], gue[8];
 #pragma unroll
             for (int q = 0; q < 8; q++) {
-                const float c = vc[q + 1], cp = vc[q];
-                const float b2 = has2 ? g2[q] : 0.f;
-                const float z = lo ? cp : c;
-                const float f1 = exp2f(fmaf(sg, z, o1)), fS = exp2f(fmaf(sg, z, o2));
-                const float f3 = has2 ? exp2f(fmaf(sg, z, o3)) : 0.f;
-                const float raw_own = lo ? vr[q] : vk[q], raw_other = lo ? vk[q] : vr[q];
-                const float qI = vown[q] * g1[q] + vx[q] * b2;
-                const float qS = raw_own * fS * gs[q];
-                out[q] = f1 * g1[q] + f3 * b2 + fS * gs[q] + vpt[q] * uk * raw_other;
-                if (!lo) gu_acc += vpt[q] * vr[q] * vk[q];
-                // the gk lane hands its two terms to the gr lane of the same channel
-                const float k_qI = __shfl_xor_sync(0xffffffffu, qI, 16);
-                const float k_qS = __shfl_xor_sync(0xffffffffu, qS, 16);
-                C += carryI - qI;        // carryI = qkI of the previous token
-                accS += qS;
-                glwv[q] = Kb - accS + accD + C;
-                accD += k_qS;
-                carryI = k_qI;
-                if (PER_TOKEN) {
-                    // floored log-decay of this token, zero where the floor was hit (no gradient)
-                    lmv[q] = (__float_as_uint(c) & 1u) ? (c - cp) * LN2 : 0.f;
-                } else if (j * CH + t0 + q < P.T) {
-                    gw_acc += glwv[q];
-                    nvalid++;
+                const float f1 = GR ? exp2f(z[q] - mb[q]) : exp2f(mb[q] - z[q]);
+                const float fS = GR ? exp2f(z[q]) : exp2f(e1r[q] - z[q]);
+                const float sgs = fS * gs[q];
+                float o = f1 * g1[q] + sgs + ptt_t * uu[q] * oth[q];
+                float qq = own[q] * g1[q] + raw[q] * sgs;
+                if (has2) {
+                    const float f3 = GR ? exp2f(z[q] - e0r[q]) : exp2f(e0r[q] - z[q]);
+                    o += f3 * g2[q];
+                    qq += xx[q] * g2[q];
                 }
+                out[q] = o;
+                ab[q] = GR ? -qq : qq;
+                if (!GR) gue[q] = ptt_t * raw[q] * oth[q];
             }
-            // stage 3: stores
-            if (lo) {
+            st_tile(o_main, t, c8, pack8(out));
+            const bool mine = GR ? (bt < 2) : (bt >= 2);
+            if (mine) {
+                if (bt & 1) {
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    st_bf(o_gr, t0 + q, kch, out[q]);
-                    if (PER_TOKEN && wg == 0) st_bf(o_gw, t0 + q, kch, glwv[q] * lmv[q]);
+                    for (int q = 0; q < 8; q++) keep[8 + q] = ab[q];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) keep[q] = ab[q];
                 }
             } else {
-#pragma unroll
-                for (int q = 0; q < 8; q++) st_bf(o_gk, t0 + q, kch, out[q]);
+                float4 *dst = reinterpret_cast<float4 *>(exch.b + tile_off(t, 4 * hh + 2 * (bt & 1)));
+                dst[0] = make_float4(ab[0], ab[1], ab[2], ab[3]);
+                *reinterpret_cast<float4 *>(exch.b + tile_off(t, 4 * hh + 2 * (bt & 1) + 1)) =
+                    make_float4(ab[4], ab[5], ab[6], ab[7]);
             }
-            if (PER_TOKEN && wg == 1) {
-                // park the offset-free values in the accumulator columns this batch has consumed
-                tmem_st8(tmem_addr(tm, lane_base, C_G1 + t0), glwv);
-                tmem_st8(tmem_addr(tm, lane_base, C_GS + t0), lmv);
-            }
-        }
-        // group 0 publishes what group 1's recurrence was missing: with the sums after token 31,
-        // glw_t (t >= 32) = parked value + K_j - accS + accD + C + qkI_31
-        float *off = reinterpret_cast<float *>(s.khat.b);     // khat's last reader was phase 2
-        if (wg == 0 && lo) off[kch] = Kb - accS + accD + C + carryI;
-        if (PER_TOKEN && wg == 1) tmem_st_wait();
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-        if (wg == 1) {
-            const float offk = off[kch];
-            if (PER_TOKEN) {
-#pragma unroll 1
-                for (int bt = 0; bt < 4; bt++) {
-                    const int t0 = 32 + 8 * bt;
-                    float glwv[8], lmv[8];
-                    tmem_ld8(tmem_addr(tm, lane_base, C_G1 + t0), glwv);
-                    tmem_ld8(tmem_addr(tm, lane_base, C_GS + t0), lmv);
-                    tmem_ld_wait();
-                    if (lo) {
-#pragma unroll
-                        for (int q = 0; q < 8; q++) st_bf(o_gw, t0 + q, kch, (glwv[q] + offk) * lmv[q]);
-                    }
-                }
-            } else {
-                gw_acc += nvalid * offk;
+            if (!GR) {
+                // gu: sum over this warp's 16 tokens of p_tt r k, by a halving exchange
+                const float tot = halving_sum8(gue, l16);
+                if ((l16 & 1) == 0) gup[w4 * CH + 8 * c8 + (l16 >> 1)] = tot;
             }
         }
-        // per-(chunk, token-half) partials, folded later in a fixed order
-        if (!lo) P.gu_part[(((size_t)bh * n + j) * 2 + wg) * 64 + kch] = gu_acc;
-        if (!PER_TOKEN && lo) P.gw_part[(((size_t)bh * n + j) * 2 + wg) * 64 + kch] = static_live ? gw_acc * lw_static : 0.f;
-    }
-    // gv: accumulator [v, s]; lo lanes own value channel v, this group's 32 tokens
-    {
+    };
+    if (wg == 0) side_pass(std::true_type{}); else side_pass(std::false_type{});
+    if (P.stop == 3) { tc_fence_before(); __syncthreads(); if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
+    if (stamp2) P.timeline[9 + 5 * wg] = clock64();
+    if (wg == 0) {
+        // gv: accumulator [s, v]
         float gv[32];
-        tmem_ld16(tmem_addr(tm, lane_base, C_GV + col0), gv);
-        tmem_ld16(tmem_addr(tm, lane_base, C_GV + col0 + 16), gv + 16);
+        tmem_ld16(tmem_addr(tm, lane_base, C_GV), gv);
+        tmem_ld16(tmem_addr(tm, lane_base, C_GV + 16), gv + 16);
         tmem_ld_wait();
-        if (lo) {
 #pragma unroll
-            for (int t = 0; t < 32; t++) st_bf(o_gv, col0 + t, kch, gv[t]);
+        for (int c8 = 0; c8 < 4; c8++) st_tile(o_gv, t, 4 * hh + c8, pack8(gv + 8 * c8));
+    }
+    if (stamp2) P.timeline[10 + 5 * wg] = clock64();
+    __syncthreads();
+    if (stamp2) P.timeline[11 + 5 * wg] = clock64();
+    // the token scan of z = a + b for this thread's 16 channels: 32*hh + 16*wg .. +15
+    float bsub[16];
+    {
+        const Tile &got = wg ? s.in[T_S] : s.in[T_D];      // what the other group left for this one
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+            const float4 o = *reinterpret_cast<const float4 *>(got.b + tile_off(t, 4 * hh + c4));
+            const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int i = 4 * c4 + q;
+                bsub[i] = wg ? keep[i] : ov[q];            // b_t
+                keep[i] += ov[q];                          // z_t
+            }
+        }
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const float o = __shfl_up_sync(0xffffffffu, keep[i], off, 16);
+                if (l16 >= off) keep[i] += o;
+            }
+        }
+        if (l16 == 15) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++)
+                *reinterpret_cast<float4 *>(wtot + w4 * CH + 32 * hh + 16 * wg + 4 * c4) =
+                    make_float4(keep[4 * c4], keep[4 * c4 + 1], keep[4 * c4 + 2], keep[4 * c4 + 3]);
         }
     }
+    if (stamp2) P.timeline[12 + 5 * wg] = clock64();
+    __syncthreads();
+    {
+        const int kb0 = 32 * hh + 16 * wg;                 // first of the 16 channels
+        float glw[16];
+        // the constant of the chunk start plus the earlier warps' totals
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+            float4 o = *reinterpret_cast<const float4 *>(s.kb + kb0 + 4 * c4);
+            for (int w = 0; w < w4; w++) {
+                const float4 p = *reinterpret_cast<const float4 *>(wtot + w * CH + kb0 + 4 * c4);
+                o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+            }
+            glw[4 * c4] = o.x + keep[4 * c4] - bsub[4 * c4];
+            glw[4 * c4 + 1] = o.y + keep[4 * c4 + 1] - bsub[4 * c4 + 1];
+            glw[4 * c4 + 2] = o.z + keep[4 * c4 + 2] - bsub[4 * c4 + 2];
+            glw[4 * c4 + 3] = o.w + keep[4 * c4 + 3] - bsub[4 * c4 + 3];
+        }
+        if (PER_TOKEN) {
+            // times the floored log-decay of the token, zero where the floor was hit (no gradient)
+#pragma unroll
+            for (int c2 = 0; c2 < 2; c2++) {
+                const int c8 = (kb0 >> 3) + c2;
+                float c[8], cp[8];
+                ld_ctab8(ct_lo, ct_hi, t, c8, c);
+                if (t > 0) {
+                    ld_ctab8(ct_lo, ct_hi, t - 1, c8, cp);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) cp[q] = 0.f;
+                }
+                float o[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    o[q] = (__float_as_uint(c[q]) & 1u) ? glw[8 * c2 + q] * (c[q] - cp[q]) * LN2 : 0.f;
+                st_tile(o_gw, t, c8, pack8(o));
+            }
+        } else {
+#pragma unroll
+            for (int c2 = 0; c2 < 2; c2++) {
+                float e[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) e[q] = tvalid ? glw[8 * c2 + q] : 0.f;
+                const float tot = halving_sum8(e, l16);
+                if ((l16 & 1) == 0) gwp[w4 * CH + kb0 + 8 * c2 + (l16 >> 1)] = tot;
+            }
+        }
+    }
+    if (stamp2) P.timeline[13 + 5 * wg] = clock64();
     fence_async_smem();
     tc_fence_before();
     const int abort3 = __syncthreads_or(fail) | abort2;
@@ -775,8 +881,19 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tma_store_3d(&map_gv, &o_gv, h * 64, j * CH, b);
         if (PER_TOKEN) tma_store_3d(&map_gw, &o_gw, h * 64, j * CH, b);
         tma_store_commit();
-        tma_store_wait_all();
     }
+    // per-chunk partials, folded later in a fixed order
+    if (tid >= 64 && tid < 128) {
+        const int k = tid - 64;
+        P.gu_part[((size_t)bh * n + j) * 64 + k] = gup[k] + gup[CH + k] + gup[2 * CH + k] + gup[3 * CH + k];
+    } else if (!PER_TOKEN && tid >= 128 && tid < 192) {
+        const int k = tid - 128;
+        bool live;
+        const float lw = log2_decay(P.wvec[h * 64 + k], P.w_kind, live) * LN2;
+        const float tot = gwp[k] + gwp[CH + k] + gwp[2 * CH + k] + gwp[3 * CH + k];
+        P.gw_part[((size_t)bh * n + j) * 64 + k] = live ? tot * lw : 0.f;
+    }
+    if (!abort3 && tid == 0) tma_store_wait_all();
     if (abort3 && P.status && tid == 0) atomicOr(P.status, 4);
     if (stamp) P.timeline[8] = clock64();
     __syncthreads();
@@ -806,8 +923,8 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.gu_part = L.e0 + align256(bh * (n + 1) * 64 * 4);
-    L.gw_part = L.gu_part + align256(bh * n * 2 * 64 * 4);
-    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 2 * 64 * 4));
+    L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
+    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
     return L;
 }
 
@@ -864,6 +981,7 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
         // bytes [64,256) of the status block take the optional phase timeline (debug aid)
         p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)(ws + 64) : nullptr;
+        p.stop = getenv("WKV_B200_STOP") ? atoi(getenv("WKV_B200_STOP")) : 0;
         const size_t smem = sizeof(BwdSmem);
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -874,8 +992,8 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     // 4. fold the per-chunk partial sums
     {
         const int total = B * H * 64;
-        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, 2 * n, total);
-        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, 2 * n, total);
+        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, n, total);
+        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, n, total);
     }
     return launch_status();
 }
