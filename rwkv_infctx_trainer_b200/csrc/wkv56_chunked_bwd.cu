@@ -284,7 +284,10 @@ struct BwdSmem {
     float ptt[CH];
     float kb[CH];              // decay-gradient constant of the chunk start, per channel
     uint64_t load_bar;
-    uint64_t mma_bar;
+    uint64_t bar_early;        // P and the state products (need the raw tiles only)
+    uint64_t bar_score;        // A1, A2
+    uint64_t bar_grad;         // phase 2 except gv
+    uint64_t bar_gv;           // gv
     uint32_t tmem_base;
 };
 
@@ -299,7 +302,6 @@ struct BwdParams {
     float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
     long long *timeline;  // optional: clock stamps of one CTA (phase boundaries), or NULL
-    int stop;  // TEMP profiling aid
 };
 
 // tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31.
@@ -381,7 +383,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
         mbar_init(&s.load_bar, 1);
-        mbar_init(&s.mma_bar, 8);   // lane 0 of every warp issues a share of each MMA group and commits
+        // lane 0 of every warp commits to every barrier, whether or not it issued a share of the group
+        mbar_init(&s.bar_early, 8); mbar_init(&s.bar_score, 8); mbar_init(&s.bar_grad, 8); mbar_init(&s.bar_gv, 8);
         fence_mbar_init();
         mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
         tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
@@ -411,6 +414,34 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (stamp) P.timeline[1] = clock64();
     if (!mbar_wait(&s.load_bar, 0)) fail = 1;
     if (stamp) P.timeline[2] = clock64();
+
+    // The products that need only the raw tiles go to the tensor core before the operand pass
+    // (a tcgen05.mma is issued by one thread and costs it ~100 cycles of descriptor arithmetic:
+    // the accumulators of a group go out from different warps at once).
+    if (lane == 0) {
+        const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
+        if (!fail) {
+            if (warp == 0) {
+                // P[t,s] = sum_v gy[t,v] v[s,v]
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
+            } else if (warp < 3) {
+                // gr state part: GSr[t, k] = sum_v gy[t,v] S[k,v]; channels 0..31 in lo, 32..63 in hi lanes
+                const int hf = warp - 1;
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    mma_ss((hf ? tm_hi : tm_lo) + C_GSR, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_S], 32 * hf, k), id32, k > 0);
+            } else if (warp < 5) {
+                // gk state part: GSk[s, k] = sum_v v[s,v] D[k,v]
+                const int hf = warp - 3;
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    mma_ss((hf ? tm_hi : tm_lo) + C_GSK, desc_kmajor(&s.in[T_V], 0, k), desc_kmajor(&s.in[T_D], 32 * hf, k), id32, k > 0);
+            }
+        }
+        mma_commit(&s.bar_early);
+    }
 
     // ---------------------------------------------------------------- operand pass
     {
@@ -517,40 +548,24 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     tc_fence_before();
     const int abort1 = __syncthreads_or(fail);
     if (stamp) P.timeline[3] = clock64();
-    if (P.stop == 1) { if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
 
-    // ------------------------------------------------- phase 1: A1, A2, P and the state products
-    // (a tcgen05.mma is issued by one thread and costs it ~100 cycles of descriptor
-    // arithmetic: the accumulators of a group go out from different warps at once)
-    if (!abort1 && lane == 0) {
-        tc_fence_after();
-        const uint32_t id64 = make_idesc(64, 64, false, false), id32 = make_idesc(64, 32, false, false);
-        if (warp == 0) {
+    // ------------------------------------------------- phase 1: the scores A1, A2
+    if (lane == 0) {
+        if (!abort1) {
+            tc_fence_after();
+            if (warp == 0) {
+                const uint32_t id64 = make_idesc(64, 64, false, false);
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
-        } else if (warp == 1) {
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
+            } else if (warp == 1) {
+                const uint32_t id32 = make_idesc(64, 32, false, false);
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm_lo + C_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
-        } else if (warp == 2) {
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tm_hi + C_P, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_V], 0, k), id64, k > 0);
-        } else if (warp < 5) {
-            // gr state part: GSr[t, k] = sum_v gy[t,v] S[k,v]; channels 0..31 in lo, 32..63 in hi lanes
-            const int hf = warp - 3;
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss((hf ? tm_hi : tm_lo) + C_GSR, desc_kmajor(&s.in[T_GY], 0, k), desc_kmajor(&s.in[T_S], 32 * hf, k), id32, k > 0);
-        } else if (warp < 7) {
-            // gk state part: GSk[s, k] = sum_v v[s,v] D[k,v]
-            const int hf = warp - 5;
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss((hf ? tm_hi : tm_lo) + C_GSK, desc_kmajor(&s.in[T_V], 0, k), desc_kmajor(&s.in[T_D], 32 * hf, k), id32, k > 0);
+                for (int k = 0; k < 4; k++)
+                    mma_ss(tm_lo + C_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
+            }
         }
-        mma_commit(&s.mma_bar);
+        mma_commit(&s.bar_score);
     }
     // meanwhile: the bonus term of the score diagonal, sum_k r_t u k_t, in the warps whose 16 rows x
     // 32 columns straddle the diagonal; the lo lane takes channels 0..31 of the row, the hi lane 32..63
@@ -570,7 +585,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
         diag += __shfl_xor_sync(0xffffffffu, diag, 16);
     }
-    if (!abort1 && !mbar_wait(&s.mma_bar, 0)) fail = 1;
+    if (!abort1 && !(mbar_wait(&s.bar_early, 0) && mbar_wait(&s.bar_score, 0))) fail = 1;
     tc_fence_after();
     if (stamp) P.timeline[4] = clock64();
 
@@ -632,17 +647,21 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     tc_fence_before();
     const int abort2 = __syncthreads_or(fail) | abort1;
     if (stamp) P.timeline[5] = clock64();
-    if (P.stop == 2) { if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
 
     // ------------------------------------------------- phase 2: token-major accumulators
     // every accumulator is [token, 32 channels]: channels 0..31 in the lo lanes, 32..63 in the hi lanes
-    if (!abort2 && lane == 0) {
+    // gv is needed last and goes to a barrier of its own.  (A commit covers everything its thread has
+    // issued before, so the gv warps arrive on the gradient barrier first.)
+    if (lane == 0) {
         tc_fence_after();
         const uint32_t id_kn = make_idesc(64, 32, false, true), id_nn = make_idesc(64, 32, true, true);
         const int hf = warp & 1;
         const uint32_t tmh = hf ? tm_hi : tm_lo;
         const uint64_t boff = hf ? 4 : 0;     // +64 bytes: the upper 32 of the 64 contiguous elements
-        if (warp < 2) {
+        if (warp < 2) mma_commit(&s.bar_grad);
+        if (abort2) {
+            // nothing is issued
+        } else if (warp < 2) {
             // gv[s, v] = sum_t A~[t,s] gy[t,v] + sum_k khat[s,k] D[k,v]
 #pragma unroll
             for (int k = 0; k < 4; k++)
@@ -677,25 +696,28 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     mma_ss((hq ? tm_hi : tm_lo) + C_G2K, desc_mnmajor(&s.in[T_V], 32, k),
                            desc_mnmajor(&s.x, 32, k) + (hq ? 4 : 0), id_nn, k > 0);
         }
-        mma_commit(&s.mma_bar);
+        if (warp >= 2) mma_commit(&s.bar_grad);
+        mma_commit(&s.bar_gv);
     }
 
     // ------------------------------------------------- epilogue
     // A thread owns token t = row and the 32 channels of its lane half; group 0 is the gr side,
-    // group 1 the gk side.  Output staging reuses tiles whose last reader was phase 2:
-    // gr->atil, gk->ptil, gw->v, gv->gy; S, D and khat serve as scratch.
-    Tile &o_gr = s.atil, &o_gk = s.ptil, &o_gw = s.in[T_V], &o_gv = s.in[T_GY];
+    // group 1 the gk side.  While gv is still being accumulated (from A~, gy, khat, D) only tiles
+    // outside that product are touched: gr and gk are staged in place of the scaled operands each
+    // thread has just consumed (gr->rt, gk->kt), S and the P~ tile carry the exchange between the
+    // groups, the v tile the per-warp sums.  Once gv is done: gv->gy, gw->D.
+    Tile &o_gr = s.rt, &o_gk = s.kt, &o_gw = s.in[T_D], &o_gv = s.in[T_GY];
     Tile &ct_lo = s.in[T_W], &ct_hi = s.ctab_hi;
     const int t = row, hh = lane >> 4, l16 = lane & 15;
     const float ptt_t = s.ptt[t];
     const bool tvalid = j * CH + t < P.T;
-    float *wtot = reinterpret_cast<float *>(s.khat.b);           // [4][64] per-warp totals of the token scan
+    float *wtot = reinterpret_cast<float *>(s.in[T_V].b);        // [4][64] per-warp totals of the token scan
     float *gup = wtot + 4 * CH, *gwp = gup + 4 * CH;             // [4][64] per-warp sums for gu / the static gw
     float keep[16];   // group 0: a_t of its first 16 channels; group 1: b_t of its last 16 channels
 
     // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (consumed after two more barriers)
     if (tid < CH) s.kb[tid] = P.e0[((size_t)bh * (n + 1) + j) * 64 + tid];
-    if (!abort2 && !mbar_wait(&s.mma_bar, 1)) fail = 1;
+    if (!abort2 && !mbar_wait(&s.bar_grad, 0)) fail = 1;
     tc_fence_after();
     if (stamp) P.timeline[6] = clock64();
 
@@ -709,7 +731,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         const Tile &t_raw = GR ? s.in[T_R] : s.in[T_K], &t_oth = GR ? s.in[T_K] : s.in[T_R];
         constexpr int cGS = GR ? C_GSR : C_GSK, cG1 = GR ? C_G1R : C_G1K, cG2 = GR ? C_G2R : C_G2K;
         Tile &o_main = GR ? o_gr : o_gk;
-        Tile &exch = GR ? s.in[T_S] : s.in[T_D];              // what the other group needs from this one
+        Tile &exch = GR ? s.in[T_S] : s.ptil;                 // what the other group needs from this one
         const int zrow = GR ? t - 1 : t;                      // gr factors use c_{t-1}, gk factors c_t
         const int mrow = t < HB ? 15 : 47;
 #pragma unroll 1
@@ -778,10 +800,11 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
     };
     if (wg == 0) side_pass(std::true_type{}); else side_pass(std::false_type{});
-    if (P.stop == 3) { tc_fence_before(); __syncthreads(); if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS); return; }
     if (stamp2) P.timeline[9 + 5 * wg] = clock64();
     if (wg == 0) {
         // gv: accumulator [s, v]
+        if (!abort2 && !mbar_wait(&s.bar_gv, 0)) fail = 1;
+        tc_fence_after();
         float gv[32];
         tmem_ld16(tmem_addr(tm, lane_base, C_GV), gv);
         tmem_ld16(tmem_addr(tm, lane_base, C_GV + 16), gv + 16);
@@ -795,7 +818,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     // the token scan of z = a + b for this thread's 16 channels: 32*hh + 16*wg .. +15
     float bsub[16];
     {
-        const Tile &got = wg ? s.in[T_S] : s.in[T_D];      // what the other group left for this one
+        const Tile &got = wg ? s.in[T_S] : s.ptil;         // what the other group left for this one
 #pragma unroll
         for (int c4 = 0; c4 < 4; c4++) {
             const float4 o = *reinterpret_cast<const float4 *>(got.b + tile_off(t, 4 * hh + c4));
@@ -893,8 +916,12 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         const float tot = gwp[k] + gwp[CH + k] + gwp[2 * CH + k] + gwp[3 * CH + k];
         P.gw_part[((size_t)bh * n + j) * 64 + k] = live ? tot * lw : 0.f;
     }
-    if (!abort3 && tid == 0) tma_store_wait_all();
-    if (abort3 && P.status && tid == 0) atomicOr(P.status, 4);
+    if (!abort3 && tid == 0) tma_store_wait_read();   // the tiles must outlive the reads of the bulk stores
+    if (abort3 && tid == 0) {
+        // every warp has arrived on every barrier: whatever was issued is done once they complete
+        mbar_wait(&s.bar_early, 0); mbar_wait(&s.bar_score, 0); mbar_wait(&s.bar_grad, 0); mbar_wait(&s.bar_gv, 0);
+        if (P.status) atomicOr(P.status, 4);
+    }
     if (stamp) P.timeline[8] = clock64();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
@@ -981,7 +1008,6 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
         // bytes [64,256) of the status block take the optional phase timeline (debug aid)
         p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)(ws + 64) : nullptr;
-        p.stop = getenv("WKV_B200_STOP") ? atoi(getenv("WKV_B200_STOP")) : 0;
         const size_t smem = sizeof(BwdSmem);
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
