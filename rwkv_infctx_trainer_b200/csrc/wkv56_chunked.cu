@@ -48,6 +48,8 @@ struct FwdParams {
     float *state_out;
     __nv_bfloat16 *y;
     __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
+    float *dchunk;            // [B*H,nchunk,64] decay of each whole chunk, or NULL; with it the
+                              // kernel also stores r e^{cp} of every chunk through map_rh
     int *status;
     long long *timeline;      // optional debug aid: clock stamps of one mid-sequence step of one CTA
 };
@@ -66,7 +68,7 @@ template <bool PER_TOKEN>
 __global__ void __launch_bounds__(128, 2)
 k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
-            const FwdParams P) {
+            const __grid_constant__ CUtensorMap map_rh, const FwdParams P) {
     extern __shared__ unsigned char smem_raw[];
     FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -170,7 +172,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         for (int ch = 0; ch < 8; ch++) other[ch] = exp2f(s.btot[blk ^ 1][cc * 8 + ch]);
         if (blk == 0 && tgl == 7) {
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) s.dvec[cc * 8 + ch] = exp2f(D.e[ch]) * other[ch];
+            for (int ch = 0; ch < 8; ch++) {
+                const float d = exp2f(D.e[ch]) * other[ch];
+                s.dvec[cc * 8 + ch] = d;
+                if (P.dchunk) P.dchunk[((size_t)bh * n + j) * 64 + cc * 8 + ch] = d;
+            }
         }
         // r-side operands, walking forward over the thread's tokens:
         //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
@@ -202,6 +208,21 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 st_tile(in[3], t, cc, pack8(rh));
                 if (blk) st_tile(s.x, t, cc, pack8(xx));
                 s.dpart[cc][t] = dsum;
+            }
+        } else if (P.dchunk) {
+            // state-only pass on behalf of a backward call: r e^{cp} alone
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int t = tok0 + i;
+                float r[8], rh[8];
+                unpack8(ld_tile(in[0], t, cc), r);
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) {
+                    const float xx = r[ch] * fb[ch];
+                    rh[ch] = blk ? xx * other[ch] : xx;
+                    fb[ch] *= D.w[i][ch];
+                }
+                st_tile(in[3], t, cc, pack8(rh));
             }
         }
         // k-side operands, walking backward:
@@ -258,6 +279,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         Tile *in = s.in[st];
         const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
         if (stamp) P.timeline[0] = clock64();
+        // r e^{cp} of this chunk goes out for the backward pass (read again by the state product below)
+        if (tid == 0 && P.dchunk) {
+            tma_store_3d(&map_rh, &in[3], h * 64, j * CH, b);
+            tma_store_commit();
+        }
 
         // (A) scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T.  A tcgen05.mma is
         // issued by one thread and costs it ~100 cycles of descriptor arithmetic, so the three
@@ -395,7 +421,10 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (__syncthreads_or(fail)) { aborted = 1; break; }
         // stage j&1 is free now (its last reader was the MMA group that just completed)
         if (j + 2 < n) {
-            if (tid == 0) issue_load(j + 2);
+            if (tid == 0) {
+                tma_store_wait_read();     // the store above has read its tile of this stage
+                issue_load(j + 2);
+            }
             issued = j + 2;
         }
         if (stamp) P.timeline[7] = clock64();
@@ -427,6 +456,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
     }
     if (aborted && P.status && tid == 0) atomicOr(P.status, 1);
+    if (tid == 0) tma_store_wait_read();
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tm, FWD_TMEM_COLS);
@@ -466,14 +496,22 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     p.wvec = per_token_w ? nullptr : (const float *)a->w;
     p.state_in = a->state_in; p.state_out = a->state_out;
     p.y = (__nv_bfloat16 *)a->y;
-    p.ckpt = (__nv_bfloat16 *)state_ckpt;
+    const CkptLayout CL = ckpt_layout(B, T, H);
+    CUtensorMap mrh = mr;
+    p.ckpt = nullptr; p.dchunk = nullptr;
+    if (state_ckpt) {
+        char *ck = (char *)state_ckpt;
+        p.ckpt = (__nv_bfloat16 *)(ck + CL.sck);
+        p.dchunk = (float *)(ck + CL.dchunk);
+        if (!make_btc_map(&mrh, ck + CL.rhat, B, T, C)) return WKV_ERR_LAUNCH;
+    }
     p.status = (int *)a->workspace;
     p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)((char *)a->workspace + 64) : nullptr;
     const size_t smem = sizeof(FwdSmem) + 1024;
     auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return WKV_ERR_LAUNCH;
-    kern<<<B * H, 128, smem, stream>>>(mr, mk, mv, mw, p);
+    kern<<<B * H, 128, smem, stream>>>(mr, mk, mv, mw, mrh, p);
     return launch_status();
 }
 

@@ -119,10 +119,28 @@ __device__ __forceinline__ void st_tile4(Tile &t, int row, int chunk, int half, 
     *reinterpret_cast<uint2 *>(t.b + tile_off(row, chunk) + 8 * half) = v;
 }
 
+// What the forward kernel hands to the backward kernels (wkv_args_t.state_ckpt):
+//   sck     bf16 [B*H, nchunk+1, 64, 64]  state at the start of every chunk (key rows, value columns)
+//   rhat    bf16 [B, T, C]                r_t * (decay accumulated from the chunk start to before t)
+//   dchunk  fp32 [B*H, nchunk, 64]        decay of each whole chunk per key channel
+struct CkptLayout {
+    size_t sck, rhat, dchunk, total;
+};
+inline CkptLayout ckpt_layout(int B, int T, int H) {
+    const size_t n = (size_t)(T + CH - 1) / CH, bh = (size_t)B * H;
+    auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    CkptLayout L;
+    L.sck = 0;
+    L.rhat = al(bh * (n + 1) * 64 * 64 * 2);
+    L.dchunk = L.rhat + al((size_t)B * T * H * 64 * 2);
+    L.total = L.dchunk + al(bh * n * 64 * 4);
+    return L;
+}
+
 }  // namespace chunked
 
-// chunk-start states of a segment as bf16 [B*H, nchunk+1, 64, 64] (key rows, value columns),
-// written by the forward kernel; y is not produced when `y` in `a` is NULL
+// `state_ckpt` (laid out as chunked::CkptLayout, or NULL) receives what the backward kernels
+// reuse from the forward pass; y is not produced when `y` in `a` is NULL
 int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, cudaStream_t s);
 
 }  // namespace wkv

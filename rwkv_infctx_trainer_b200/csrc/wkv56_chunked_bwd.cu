@@ -39,234 +39,193 @@ using namespace chunked;
 // ----------------------------------------------------------------------------
 // dS scan
 
+constexpr int DS_STAGES = 3;
+
 struct DscanSmem {
-    Tile in[2][4];  // r (overwritten by r e^{cp}), gy, w of the step's chunk; S at the chunk's end
-    float dvec[CH];
-    float btot[2][CH];
-    uint64_t load_bar[2];
-    uint64_t mma_bar;
+    Tile in[DS_STAGES][3];              // r e^{cp} and gy of the step's chunk; S at the chunk's end
+    __align__(16) float dvec[DS_STAGES][CH];   // decay of the whole chunk per key channel
+    float epart[2][2][CH];              // partial row sums of S * D by step parity and column half
+    uint64_t load_bar[DS_STAGES];
+    uint64_t mma_bar[2];
     uint32_t tmem_base;
 };
 
 struct DscanParams {
-    int T, H, nchunk, layout, w_kind;
-    const float *wvec;
+    int T, H, nchunk, layout;
+    const float *dchunk;  // [B*H, nchunk, 64] decay of each whole chunk (from the forward kernel)
     const float *gstate_out;
     float *gstate_in;
     __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
     float *e0;           // [B*H, nchunk+1, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at chunk boundary j
     int *status;
+    long long *timeline;  // optional: clock stamps of one step of one CTA, or NULL
 };
 
-// Step i = 0..n-1 handles chunk j = n-1-i: with D_{j+1} in tensor memory it writes the D_{j+1}
-// checkpoint and E_{j+1} = rowsum(S_{j+1} * D_{j+1}) (the decay-gradient constant at chunk
-// boundary j+1), then forms D_j = d_j D_{j+1} + (r e^{cp})^T gy.  A closing step i = n writes
-// E_0 and D_0.
-template <bool PER_TOKEN>
-__global__ void __launch_bounds__(128)
-k_chunk_dscan(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_gy,
-              const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
-              const DscanParams P) {
+// Reverse scan of the state gradient:  D_j = d_j D_{j+1} + (r e^{cp})^T gy  over the chunks j of a
+// segment, step i = 0..n-1 handling chunk j = n-1-i.  The scaled r tiles and the chunk decays
+// d_j come from the forward kernel, so a step has no operand pass.  The carried gradient D lives
+// in registers (thread = key row, 16 value columns); the tensor core only forms the chunk's own
+// contribution U_j = (r e^{cp})^T gy into one of two tensor-memory buffers, which does not depend
+// on D: the product of step i+1 is in flight while step i runs its part of the serial chain,
+//   write D_{j+1} (bf16) and E_{j+1} = rowsum(S_{j+1} * D_{j+1});   D_j = d_j D_{j+1} + U_j.
+// A closing step i = n writes E_0 and D_0.
+__global__ void __launch_bounds__(256, 2)
+k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant__ CUtensorMap map_gy,
+              const __grid_constant__ CUtensorMap map_s, const DscanParams P) {
     extern __shared__ unsigned char smem_raw[];
     DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H;
+    // eight warps: warps w and w+4 share a 32-lane quarter of tensor memory and split its columns
+    const int wg = warp >> 2, w4 = warp & 3;
     const bool active = (lane & 16) == 0;
-    const int row = warp * 16 + (lane & 15);
-    const uint32_t lane_base = (uint32_t)(warp * 32);
-    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
+    const int row = w4 * 16 + (lane & 15);
+    const uint32_t lane_base = (uint32_t)(w4 * 32);
     const int n = P.nchunk;
 
     if (tid == 0) {
-        mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1); mbar_init(&s.mma_bar, 2);
+        for (int q = 0; q < DS_STAGES; q++) mbar_init(&s.load_bar[q], 1);
+        mbar_init(&s.mma_bar[0], 2); mbar_init(&s.mma_bar[1], 2);
         fence_mbar_init();
     }
-    if (warp == 0) { tmem_alloc(&s.tmem_base, 32); tmem_relinquish(); }
+    if (warp == 0) { tmem_alloc(&s.tmem_base, 64); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = s.tmem_base;
-    // dS[key, value 0..31] sits in lanes 0..15 of each quarter, dS[key, value 32..63] in lanes 16..31
-    const int vcol0 = active ? 0 : 32;
+    // U[key, value 0..31] sits in lanes 0..15 of each quarter, U[key, value 32..63] in lanes 16..31;
+    // buffer q occupies columns 32q .. 32q+31.  This thread: 16 value columns from vcol0.
+    const int vcol0 = (active ? 0 : 32) + 16 * wg;
 
     auto issue_load = [&](int i) {
-        const int st = i & 1, j = n - 1 - i;
-        const int tiles = (i < n ? (PER_TOKEN ? 3 : 2) : 0) + 1;
-        mbar_expect_tx(&s.load_bar[st], tiles * TILE_BYTES);
+        const int st = i % DS_STAGES, j = n - 1 - i;
+        mbar_expect_tx(&s.load_bar[st], i < n ? 3 * TILE_BYTES + CH * 4 : TILE_BYTES);
         if (i < n) {
-            tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
+            tma_load_3d(&s.in[st][0], &map_rh, &s.load_bar[st], h * 64, j * CH, b);
             tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
-            if (PER_TOKEN) tma_load_3d(&s.in[st][2], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+            bulk_load_1d(s.dvec[st], P.dchunk + ((size_t)bh * n + j) * 64, CH * 4, &s.load_bar[st]);
         }
-        tma_load_3d(&s.in[st][3], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
+        tma_load_3d(&s.in[st][2], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
     };
-    if (tid == 0) issue_load(0);
+    int issued = -1;
+    if (tid == 0) {
+        for (int i = 0; i < DS_STAGES && i <= n; i++) issue_load(i);
+    }
+    issued = (n < DS_STAGES - 1 ? n : DS_STAGES - 1);
 
     const size_t sbase = (size_t)bh * 64 * 64;
-    {
-        float v[32];
+    float v[16];     // D, this thread's key row and a quarter of the value columns
 #pragma unroll
-        for (int q = 0; q < 32; q++) {
-            const int vc = vcol0 + q;
-            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-            v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
-        }
-        tmem_st16(tmem_addr(tm, lane_base, 0), v);
-        tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
-    }
-    tmem_st_wait();
-
-    float lwc[8];
-    if (!PER_TOKEN) {
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            bool live;
-            lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, live);
-        }
+    for (int q = 0; q < 16; q++) {
+        const int vc = vcol0 + q;
+        const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+        v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
     }
 
-    // operand pass of step i (chunk j = n-1-i): r e^{cp} in place, the chunk decay
-    auto prep = [&](int i) {
-        const int j = n - 1 - i;
-        Tile *in = s.in[i & 1];
-        float c[4][8];
-        Decay D;
+    // U of step i into buffer i&1: value columns 0..31 from warp 0, 32..63 from warp 1.  The
+    // operands arrive by TMA, so the issuing thread's own wait on the load barrier is all it needs.
+    auto issue_mma = [&](int i) {
+        if (lane == 0 && warp < 2) {
+            tc_fence_after();
+            Tile *in = s.in[i % DS_STAGES];
+            const uint32_t id = make_idesc(64, 32, true, true);
+            const uint32_t d = tm + (warp ? (16u << 16) : 0u) + 32u * (i & 1);
+            const uint64_t off = warp ? 4 : 0;
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int t = tok0 + q;
-            const bool valid = j * CH + t < P.T;
-            if (PER_TOKEN) {
-                float x[8];
-                unpack8(ld_tile(in[2], t, cc), x);
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
-                    bool live;
-                    const float l2 = log2_decay(x[ch], P.w_kind, live);
-                    c[q][ch] = valid ? l2 : 0.f;
-                }
-            } else {
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) c[q][ch] = valid ? lwc[ch] : 0.f;
-            }
-        }
-        decay_scan(c, lane, D);
-        if (tgl == 7) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
-        }
-        __syncthreads();
-        float f[8];      // 2^{cp} counted from the chunk start
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            const float other = s.btot[blk ^ 1][cc * 8 + ch];
-            f[ch] = exp2f(blk ? D.cp0[ch] + other : D.cp0[ch]);
-            if (blk == 0 && tgl == 7) s.dvec[cc * 8 + ch] = exp2f(D.e[ch] + other);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int t = tok0 + q;
-            float rr[8];
-            unpack8(ld_tile(in[0], t, cc), rr);
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                rr[ch] *= f[ch];
-                f[ch] *= D.w[q][ch];
-            }
-            st_tile(in[0], t, cc, pack8(rr));
+            for (int k = 0; k < 4; k++)
+                mma_ss(d, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k) + off, id, k > 0);
+            mma_commit(&s.mma_bar[i & 1]);
         }
     };
+    auto load_parity = [&](int i) { return (uint32_t)((i / DS_STAGES) & 1); };
 
-    uint32_t mma_phase = 0;
-    int fail = 0, aborted = 0, issued = 0, landed = -1;
+    int fail = 0, aborted = 0, landed = -1, mma_issued = -1, mma_done = -1;
 
-    // prologue: operands of step 0, load of step 1
+    // prologue: product of step 0 (n >= 1)
     if (mbar_wait(&s.load_bar[0], 0)) landed = 0; else fail = 1;
-    prep(0);
-    if (tid == 0) issue_load(1);      // n >= 1, so step 1 exists (it may be the closing step)
-    issued = 1;
-    fence_async_smem();
-    tc_fence_before();
-    if (__syncthreads_or(fail)) aborted = 1;
-    tc_fence_after();
+    if (!fail) issue_mma(0);
+    mma_issued = 0;     // (a thread whose wait failed issued nothing; the abort path's waits are bounded)
 
-    // Software pipeline: while the tensor core forms D_j, the CUDA cores prepare step i+1.
     for (int i = 0; i <= n && !aborted; i++) {
-        const int st = i & 1, j = n - 1 - i;
+        const int st = i % DS_STAGES, j = n - 1 - i;
         Tile *in = s.in[st];
-        float dnext = 0.f;
-        {   // with D_{j+1} in hand: its checkpoint, E_{j+1}, then the decay
-            float v[32];
-            tmem_ld16(tmem_addr(tm, lane_base, 0), v);
-            tmem_ld16(tmem_addr(tm, lane_base, 16), v + 16);
-            tmem_ld_wait();
-            {
-                float dot = 0.f;
-#pragma unroll
-                for (int c8 = 0; c8 < 4; c8++) {
-                    float sv[8];
-                    unpack8(ld_tile(in[3], row, (vcol0 >> 3) + c8), sv);
-#pragma unroll
-                    for (int q = 0; q < 8; q++) dot += sv[q] * v[8 * c8 + q];
-                }
-                dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-                if (active) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + row] = dot;
+        const bool stamp = P.timeline != nullptr && bh == (int)gridDim.x / 2 && tid == 0 && i == n / 2;
+        if (stamp) P.timeline[0] = clock64();
+        // the next step's product first: it does not depend on D.  (Its buffer was last read in
+        // step i-1, before that step's closing barrier.)
+        if (i + 1 <= n) {
+            if (mbar_wait(&s.load_bar[(i + 1) % DS_STAGES], load_parity(i + 1))) landed = i + 1; else fail = 1;
+            if (i + 1 < n) {
+                if (!fail) issue_mma(i + 1);
+                mma_issued = i + 1;
             }
-            if (i < n) {
-                const float d = s.dvec[row];
-                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+        }
+        if (stamp) P.timeline[1] = clock64();
+        // with D_{j+1} in hand: its checkpoint and E_{j+1} ...
+        {
+            float dot = 0.f;
 #pragma unroll
-                for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
+            for (int c8 = 0; c8 < 2; c8++) {
+                float sv[8];
+                unpack8(ld_tile(in[2], row, (vcol0 >> 3) + c8), sv);
 #pragma unroll
-                for (int c = 0; c < 32; c++) v[c] *= d;
-                tmem_st16(tmem_addr(tm, lane_base, 0), v);
-                tmem_st16(tmem_addr(tm, lane_base, 16), v + 16);
-            } else if (P.gstate_in) {   // closing step: D_0 is the state gradient
+                for (int q = 0; q < 8; q++) dot += sv[q] * v[8 * c8 + q];
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+            if (active) s.epart[i & 1][wg][row] = dot;     // the two column halves meet after the step's barrier
+        }
+        if (i == n) {   // closing step: D_0 is the state gradient
+            if (P.gstate_in) {
 #pragma unroll
-                for (int q = 0; q < 32; q++) {
+                for (int q = 0; q < 16; q++) {
                     const int vc = vcol0 + q;
                     const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
                     P.gstate_in[sbase + idx] = v[q];
                 }
             }
-            (void)dnext;
+            __syncthreads();
+            if (tid < CH) P.e0[(size_t)bh * (n + 1) * 64 + tid] = s.epart[i & 1][0][tid] + s.epart[i & 1][1][tid];
+            break;
         }
-        if (i == n) break;
-        tmem_st_wait();
-        tc_fence_before();
-        __syncthreads();
-        if (lane == 0 && warp < 2) {   // value columns 0..31 from warp 0, 32..63 from warp 1
-            tc_fence_after();
-            const uint32_t id = make_idesc(64, 32, true, true);
-            const uint32_t d = tm + (warp ? (16u << 16) : 0u);
-            const uint64_t off = warp ? 4 : 0;
+        {
+            uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(d, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k) + off, id, true);
-            mma_commit(&s.mma_bar);
+            for (int c8 = 0; c8 < 2; c8++) dst[c8] = pack8(v + 8 * c8);
         }
-        // operands of the next step while the tensor core works
-        if (mbar_wait(&s.load_bar[(i + 1) & 1], (uint32_t)(((i + 1) >> 1) & 1))) landed = i + 1; else fail = 1;
-        if (i + 1 < n) prep(i + 1);
-        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
-        mma_phase ^= 1;
+        if (stamp) P.timeline[2] = clock64();
+        // ... then D_j = d_j D_{j+1} + U_j
+        if (mbar_wait(&s.mma_bar[i & 1], (uint32_t)((i >> 1) & 1))) mma_done = i; else fail = 1;
         tc_fence_after();
-        fence_async_smem();
+        if (stamp) P.timeline[3] = clock64();
+        {
+            float u[16];
+            tmem_ld16(tmem_addr(tm, lane_base, 32 * (i & 1) + 16 * wg), u);
+            tmem_ld_wait();
+            const float d = s.dvec[st][row];
+#pragma unroll
+            for (int q = 0; q < 16; q++) v[q] = fmaf(d, v[q], u[q]);
+        }
+        if (stamp) P.timeline[4] = clock64();
+        // stage st and product buffer i&1 are free once every thread is here
         tc_fence_before();
         if (__syncthreads_or(fail)) { aborted = 1; break; }
-        tc_fence_after();
-        // stage i&1 is free now
-        if (i + 2 <= n) {
-            if (tid == 0) issue_load(i + 2);
-            issued = i + 2;
+        if (stamp) P.timeline[5] = clock64();
+        if (tid < CH) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + tid] = s.epart[i & 1][0][tid] + s.epart[i & 1][1][tid];
+        if (i + DS_STAGES <= n) {
+            if (tid == 128) issue_load(i + DS_STAGES);
+            issued = i + DS_STAGES;
         }
+        if (stamp) P.timeline[6] = clock64();
     }
     if (aborted) {
-        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
+        // let everything in flight land before the shared and tensor memory go away
+        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q % DS_STAGES], load_parity(q));
+        for (int q = mma_done + 1; q <= mma_issued; q++) mbar_wait(&s.mma_bar[q & 1], (uint32_t)((q >> 1) & 1), 100000u);
+        if (P.status && tid == 0) atomicOr(P.status, 2);
     }
-    if (aborted && P.status && tid == 0) atomicOr(P.status, 2);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tm, 32);
+    if (warp == 0) tmem_dealloc(tm, 64);
 }
 
 // ----------------------------------------------------------------------------
@@ -947,7 +906,7 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     BwdLayout L;
     L.status = 0;
     L.sck = 256;
-    L.dck = L.sck + align256(bh * (n + 1) * 64 * 64 * 2);
+    L.dck = L.sck + align256(ckpt_layout(a->B, a->T, a->H).total);
     L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.gu_part = L.e0 + align256(bh * (n + 1) * 64 * 4);
     L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
@@ -964,7 +923,10 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     const BwdLayout L = bwd_layout(a, per_token_w);
     char *ws = (char *)a->workspace;
     if (cudaMemsetAsync(ws, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
-    void *sck = a->state_ckpt ? a->state_ckpt : ws + L.sck, *dck = ws + L.dck;
+    // what the forward kernel leaves for this call: chunk-start states, r e^{cp}, chunk decays
+    char *fwd_ck = a->state_ckpt ? (char *)a->state_ckpt : ws + L.sck;
+    const CkptLayout CL = ckpt_layout(B, T, H);
+    void *sck = fwd_ck + CL.sck, *dck = ws + L.dck;
     float *gu_part = (float *)(ws + L.gu_part), *gw_part = (float *)(ws + L.gw_part), *e0 = (float *)(ws + L.e0);
 
     // 1. chunk-start states (unless the forward call handed them over)
@@ -972,15 +934,15 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         wkv_args_t f = *a;
         f.y = nullptr;
         f.state_out = nullptr;
-        const int err = chunked_forward_impl(&f, per_token_w, sck, stream);
+        const int err = chunked_forward_impl(&f, per_token_w, fwd_ck, stream);
         if (err != WKV_OK) return err;
     }
-    CUtensorMap mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw;
+    CUtensorMap mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, mrh;
     bool ok = make_btc_map(&mr, a->r, B, T, C) && make_btc_map(&mk, a->k, B, T, C) &&
               make_btc_map(&mv, a->v, B, T, C) && make_btc_map(&mgy, a->gy, B, T, C) &&
               make_btc_map(&mgr, a->gr, B, T, C) && make_btc_map(&mgk, a->gk, B, T, C) &&
               make_btc_map(&mgv, a->gv, B, T, C) && make_btc_map(&ms, sck, B * H * (n + 1), 64, 64) &&
-              make_btc_map(&md, dck, B * H * (n + 1), 64, 64);
+              make_btc_map(&md, dck, B * H * (n + 1), 64, 64) && make_btc_map(&mrh, fwd_ck + CL.rhat, B, T, C);
     if (per_token_w) ok = ok && make_btc_map(&mw, a->w, B, T, C) && make_btc_map(&mgw, a->gw, B, T, C);
     else { mw = mr; mgw = mgr; }
     if (!ok) return WKV_ERR_LAUNCH;
@@ -988,15 +950,15 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     // 2. dS scan
     {
         DscanParams p;
-        p.T = T; p.H = H; p.nchunk = n; p.layout = a->state_layout; p.w_kind = a->w_kind;
-        p.wvec = per_token_w ? nullptr : (const float *)a->w;
+        p.T = T; p.H = H; p.nchunk = n; p.layout = a->state_layout;
+        p.dchunk = (const float *)(fwd_ck + CL.dchunk);
         p.gstate_out = a->gstate_out; p.gstate_in = a->gstate_in;
         p.dck = (__nv_bfloat16 *)dck; p.e0 = e0; p.status = (int *)ws;
+        p.timeline = getenv("WKV_B200_TIMELINE_DSCAN") ? (long long *)(ws + 64) : nullptr;
         const size_t smem = sizeof(DscanSmem) + 1024;
-        auto kern = per_token_w ? k_chunk_dscan<true> : k_chunk_dscan<false>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_chunk_dscan, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return WKV_ERR_LAUNCH;
-        kern<<<B * H, 128, smem, stream>>>(mr, mgy, mw, ms, p);
+        k_chunk_dscan<<<B * H, 256, smem, stream>>>(mrh, mgy, ms, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 3. per-chunk gradients

@@ -1,5 +1,6 @@
 // C-ABI entry points for v5/v6: argument validation and dispatch between the
 // token-serial kernels and the chunked tensor-core kernels.
+#include "wkv56_chunked.cuh"
 #include "wkv_common.cuh"
 
 using namespace wkv;
@@ -106,8 +107,7 @@ const char *wkv_version(void) { return "wkv_b200 1 sm_100a"; }
 
 size_t wkv56_state_ckpt_bytes(const wkv_args_t *a, int per_token_w) {
     if (!wkv56_uses_chunked(a, per_token_w)) return 0;
-    const size_t n = (size_t)(a->T + 63) / 64;
-    return (size_t)a->B * a->H * (n + 1) * 64 * 64 * 2;
+    return chunked::ckpt_layout(a->B, a->T, a->H).total;
 }
 
 int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w) {
