@@ -44,9 +44,10 @@ constexpr int DS_STAGES = 3;
 struct DscanSmem {
     Tile in[DS_STAGES][3];              // r e^{cp} and gy of the step's chunk; S at the chunk's end
     __align__(16) float dvec[DS_STAGES][CH];   // decay of the whole chunk per key channel
-    float epart[2][2][CH];              // partial row sums of S * D by step parity and column half
-    uint64_t load_bar[DS_STAGES];
-    uint64_t mma_bar[2];
+    uint64_t load_bar[DS_STAGES];       // TMA: a stage has landed
+    uint64_t stage_free[DS_STAGES];     // the four scan warps are done with a stage
+    uint64_t mma_bar[2];                // tensor core: a product buffer is complete
+    uint64_t prod_free[2];              // the four scan warps have read a product buffer
     uint32_t tmem_base;
 };
 
@@ -58,34 +59,33 @@ struct DscanParams {
     __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
     float *e0;           // [B*H, nchunk+1, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at chunk boundary j
     int *status;
-    long long *timeline;  // optional: clock stamps of one step of one CTA, or NULL
 };
 
 // Reverse scan of the state gradient:  D_j = d_j D_{j+1} + (r e^{cp})^T gy  over the chunks j of a
 // segment, step i = 0..n-1 handling chunk j = n-1-i.  The scaled r tiles and the chunk decays
-// d_j come from the forward kernel, so a step has no operand pass.  The carried gradient D lives
-// in registers (thread = key row, 16 value columns); the tensor core only forms the chunk's own
-// contribution U_j = (r e^{cp})^T gy into one of two tensor-memory buffers, which does not depend
-// on D: the product of step i+1 is in flight while step i runs its part of the serial chain,
-//   write D_{j+1} (bf16) and E_{j+1} = rowsum(S_{j+1} * D_{j+1});   D_j = d_j D_{j+1} + U_j.
-// A closing step i = n writes E_0 and D_0.
-__global__ void __launch_bounds__(256, 2)
+// d_j come from the forward kernel, so a step has no operand pass.
+//
+// Five warps.  Warp 4 (one lane) feeds the machine: TMA loads three steps ahead, and for every
+// step the product U_j = (r e^{cp})^T gy into one of two tensor-memory buffers -- U_j does not
+// depend on the carried gradient, so it is ready before the scan gets there.  Warps 0..3 carry
+// D in registers (thread = key row, 32 value columns) and run the serial chain,
+//   write D_{j+1} (bf16) and E_{j+1} = rowsum(S_{j+1} * D_{j+1});   D_j = d_j D_{j+1} + U_j,
+// without ever synchronising with one another: each warp only waits on the barriers of the data
+// it consumes and releases buffers back to warp 4.  A closing step i = n writes E_0 and D_0.
+// Every wait is bounded; a warp whose wait runs out flags the status word and leaves the loop,
+// which makes the waits of the others run out in turn.
+__global__ void __launch_bounds__(160)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant__ CUtensorMap map_gy,
               const __grid_constant__ CUtensorMap map_s, const DscanParams P) {
     extern __shared__ unsigned char smem_raw[];
     DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H;
-    // eight warps: warps w and w+4 share a 32-lane quarter of tensor memory and split its columns
-    const int wg = warp >> 2, w4 = warp & 3;
-    const bool active = (lane & 16) == 0;
-    const int row = w4 * 16 + (lane & 15);
-    const uint32_t lane_base = (uint32_t)(w4 * 32);
     const int n = P.nchunk;
 
     if (tid == 0) {
-        for (int q = 0; q < DS_STAGES; q++) mbar_init(&s.load_bar[q], 1);
-        mbar_init(&s.mma_bar[0], 2); mbar_init(&s.mma_bar[1], 2);
+        for (int q = 0; q < DS_STAGES; q++) { mbar_init(&s.load_bar[q], 1); mbar_init(&s.stage_free[q], 4); }
+        for (int q = 0; q < 2; q++) { mbar_init(&s.mma_bar[q], 1); mbar_init(&s.prod_free[q], 4); }
         fence_mbar_init();
     }
     if (warp == 0) { tmem_alloc(&s.tmem_base, 64); tmem_relinquish(); }
@@ -93,135 +93,125 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = s.tmem_base;
-    // U[key, value 0..31] sits in lanes 0..15 of each quarter, U[key, value 32..63] in lanes 16..31;
-    // buffer q occupies columns 32q .. 32q+31.  This thread: 16 value columns from vcol0.
-    const int vcol0 = (active ? 0 : 32) + 16 * wg;
-
-    auto issue_load = [&](int i) {
-        const int st = i % DS_STAGES, j = n - 1 - i;
-        mbar_expect_tx(&s.load_bar[st], i < n ? 3 * TILE_BYTES + CH * 4 : TILE_BYTES);
-        if (i < n) {
-            tma_load_3d(&s.in[st][0], &map_rh, &s.load_bar[st], h * 64, j * CH, b);
-            tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
-            bulk_load_1d(s.dvec[st], P.dchunk + ((size_t)bh * n + j) * 64, CH * 4, &s.load_bar[st]);
-        }
-        tma_load_3d(&s.in[st][2], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
-    };
-    int issued = -1;
-    if (tid == 0) {
-        for (int i = 0; i < DS_STAGES && i <= n; i++) issue_load(i);
-    }
-    issued = (n < DS_STAGES - 1 ? n : DS_STAGES - 1);
-
-    const size_t sbase = (size_t)bh * 64 * 64;
-    float v[16];     // D, this thread's key row and a quarter of the value columns
-#pragma unroll
-    for (int q = 0; q < 16; q++) {
-        const int vc = vcol0 + q;
-        const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-        v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
-    }
-
-    // U of step i into buffer i&1: value columns 0..31 from warp 0, 32..63 from warp 1.  The
-    // operands arrive by TMA, so the issuing thread's own wait on the load barrier is all it needs.
-    auto issue_mma = [&](int i) {
-        if (lane == 0 && warp < 2) {
-            tc_fence_after();
-            Tile *in = s.in[i % DS_STAGES];
-            const uint32_t id = make_idesc(64, 32, true, true);
-            const uint32_t d = tm + (warp ? (16u << 16) : 0u) + 32u * (i & 1);
-            const uint64_t off = warp ? 4 : 0;
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(d, desc_mnmajor(&in[0], 0, k), desc_mnmajor(&in[1], 0, k) + off, id, k > 0);
-            mma_commit(&s.mma_bar[i & 1]);
-        }
-    };
     auto load_parity = [&](int i) { return (uint32_t)((i / DS_STAGES) & 1); };
+    auto prod_parity = [&](int i) { return (uint32_t)((i >> 1) & 1); };
+    int fail = 0;
 
-    int fail = 0, aborted = 0, landed = -1, mma_issued = -1, mma_done = -1;
-
-    // prologue: product of step 0 (n >= 1)
-    if (mbar_wait(&s.load_bar[0], 0)) landed = 0; else fail = 1;
-    if (!fail) issue_mma(0);
-    mma_issued = 0;     // (a thread whose wait failed issued nothing; the abort path's waits are bounded)
-
-    for (int i = 0; i <= n && !aborted; i++) {
-        const int st = i % DS_STAGES, j = n - 1 - i;
-        Tile *in = s.in[st];
-        const bool stamp = P.timeline != nullptr && bh == (int)gridDim.x / 2 && tid == 0 && i == n / 2;
-        if (stamp) P.timeline[0] = clock64();
-        // the next step's product first: it does not depend on D.  (Its buffer was last read in
-        // step i-1, before that step's closing barrier.)
-        if (i + 1 <= n) {
-            if (mbar_wait(&s.load_bar[(i + 1) % DS_STAGES], load_parity(i + 1))) landed = i + 1; else fail = 1;
-            if (i + 1 < n) {
-                if (!fail) issue_mma(i + 1);
-                mma_issued = i + 1;
-            }
-        }
-        if (stamp) P.timeline[1] = clock64();
-        // with D_{j+1} in hand: its checkpoint and E_{j+1} ...
-        {
-            float dot = 0.f;
+    if (warp == 4) {
+        if (lane == 0) {
+            auto issue_load = [&](int i) {
+                const int st = i % DS_STAGES, j = n - 1 - i;
+                mbar_expect_tx(&s.load_bar[st], i < n ? 3 * TILE_BYTES + CH * 4 : TILE_BYTES);
+                if (i < n) {
+                    tma_load_3d(&s.in[st][0], &map_rh, &s.load_bar[st], h * 64, j * CH, b);
+                    tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
+                    bulk_load_1d(s.dvec[st], P.dchunk + ((size_t)bh * n + j) * 64, CH * 4, &s.load_bar[st]);
+                }
+                tma_load_3d(&s.in[st][2], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
+            };
+            int issued = -1, landed = -1, mma_issued = -1;
+            for (int i = 0; i < DS_STAGES && i <= n; i++) { issue_load(i); issued = i; }
+            const uint32_t id = make_idesc(64, 32, true, true);
+            for (int i = 0; i <= n && !fail; i++) {
+                if (!mbar_wait(&s.load_bar[i % DS_STAGES], load_parity(i))) { fail = 1; break; }
+                landed = i;
+                if (i < n) {
+                    // buffer i&1 held the product of step i-2
+                    if (i >= 2 && !mbar_wait(&s.prod_free[i & 1], prod_parity(i - 2))) { fail = 1; break; }
+                    tc_fence_after();
+                    Tile *in = s.in[i % DS_STAGES];
+                    // value columns 0..31 into lanes 0..15 of each quarter, 32..63 into lanes 16..31
 #pragma unroll
-            for (int c8 = 0; c8 < 2; c8++) {
-                float sv[8];
-                unpack8(ld_tile(in[2], row, (vcol0 >> 3) + c8), sv);
+                    for (int hf = 0; hf < 2; hf++)
 #pragma unroll
-                for (int q = 0; q < 8; q++) dot += sv[q] * v[8 * c8 + q];
-            }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-            if (active) s.epart[i & 1][wg][row] = dot;     // the two column halves meet after the step's barrier
-        }
-        if (i == n) {   // closing step: D_0 is the state gradient
-            if (P.gstate_in) {
-#pragma unroll
-                for (int q = 0; q < 16; q++) {
-                    const int vc = vcol0 + q;
-                    const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-                    P.gstate_in[sbase + idx] = v[q];
+                        for (int k = 0; k < 4; k++)
+                            mma_ss(tm + (hf ? (16u << 16) : 0u) + 32u * (i & 1), desc_mnmajor(&in[0], 0, k),
+                                   desc_mnmajor(&in[1], 0, k) + (hf ? 4 : 0), id, k > 0);
+                    mma_commit(&s.mma_bar[i & 1]);
+                    mma_issued = i;
+                }
+                // the stage of step i-1 goes to step i+2 as soon as the scan warps are done with it
+                if (i >= 1 && i + 2 <= n) {
+                    if (!mbar_wait(&s.stage_free[(i - 1) % DS_STAGES], load_parity(i - 1))) { fail = 1; break; }
+                    issue_load(i + 2);
+                    issued = i + 2;
                 }
             }
-            __syncthreads();
-            if (tid < CH) P.e0[(size_t)bh * (n + 1) * 64 + tid] = s.epart[i & 1][0][tid] + s.epart[i & 1][1][tid];
-            break;
+            if (fail) {
+                // let everything in flight land before the shared and tensor memory go away
+                for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q % DS_STAGES], load_parity(q));
+                if (mma_issued >= 0) mbar_wait(&s.mma_bar[mma_issued & 1], prod_parity(mma_issued), 100000u);
+                if (mma_issued >= 1) mbar_wait(&s.mma_bar[(mma_issued - 1) & 1], prod_parity(mma_issued - 1), 100000u);
+                if (P.status) atomicOr(P.status, 2);
+            }
         }
-        {
-            uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+        __syncwarp();
+    } else {
+        const bool active = (lane & 16) == 0;
+        const int row = warp * 16 + (lane & 15);
+        const uint32_t lane_base = (uint32_t)(warp * 32);
+        // U[key, value 0..31] sits in lanes 0..15 of each quarter, U[key, value 32..63] in lanes 16..31
+        const int vcol0 = active ? 0 : 32;
+        const size_t sbase = (size_t)bh * 64 * 64;
+        float v[32];     // D, this thread's key row and half of the value columns
 #pragma unroll
-            for (int c8 = 0; c8 < 2; c8++) dst[c8] = pack8(v + 8 * c8);
+        for (int q = 0; q < 32; q++) {
+            const int vc = vcol0 + q;
+            const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+            v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
         }
-        if (stamp) P.timeline[2] = clock64();
-        // ... then D_j = d_j D_{j+1} + U_j
-        if (mbar_wait(&s.mma_bar[i & 1], (uint32_t)((i >> 1) & 1))) mma_done = i; else fail = 1;
-        tc_fence_after();
-        if (stamp) P.timeline[3] = clock64();
-        {
-            float u[16];
-            tmem_ld16(tmem_addr(tm, lane_base, 32 * (i & 1) + 16 * wg), u);
-            tmem_ld_wait();
-            const float d = s.dvec[st][row];
+        for (int i = 0; i <= n; i++) {
+            const int st = i % DS_STAGES, j = n - 1 - i;
+            Tile *in = s.in[st];
+            if (!mbar_wait(&s.load_bar[st], load_parity(i))) { fail = 1; break; }
+            // with D_{j+1} in hand: its checkpoint and E_{j+1} ...
+            {
+                float dot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int q = 0; q < 16; q++) v[q] = fmaf(d, v[q], u[q]);
+                for (int c8 = 0; c8 < 4; c8++) {
+                    float sv[8];
+                    unpack8(ld_tile(in[2], row, (vcol0 >> 3) + c8), sv);
+#pragma unroll
+                    for (int q = 0; q < 8; q++) dot[c8] += sv[q] * v[8 * c8 + q];
+                }
+                float e = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+                e += __shfl_xor_sync(0xffffffffu, e, 16);
+                if (active) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + row] = e;
+            }
+            if (i == n) {   // closing step: D_0 is the state gradient
+                if (P.gstate_in) {
+#pragma unroll
+                    for (int q = 0; q < 32; q++) {
+                        const int vc = vcol0 + q;
+                        const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
+                        P.gstate_in[sbase + idx] = v[q];
+                    }
+                }
+                break;
+            }
+            {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+#pragma unroll
+                for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
+            }
+            // ... then D_j = d_j D_{j+1} + U_j
+            if (!mbar_wait(&s.mma_bar[i & 1], prod_parity(i))) { fail = 1; break; }
+            tc_fence_after();
+            {
+                float u[32];
+                tmem_ld16(tmem_addr(tm, lane_base, 32 * (i & 1)), u);
+                tmem_ld16(tmem_addr(tm, lane_base, 32 * (i & 1) + 16), u + 16);
+                tmem_ld_wait();
+                const float d = s.dvec[st][row];
+#pragma unroll
+                for (int q = 0; q < 32; q++) v[q] = fmaf(d, v[q], u[q]);
+            }
+            // this warp is done with the product buffer and with the stage
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&s.prod_free[i & 1]); mbar_arrive(&s.stage_free[st]); }
         }
-        if (stamp) P.timeline[4] = clock64();
-        // stage st and product buffer i&1 are free once every thread is here
-        tc_fence_before();
-        if (__syncthreads_or(fail)) { aborted = 1; break; }
-        if (stamp) P.timeline[5] = clock64();
-        if (tid < CH) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + tid] = s.epart[i & 1][0][tid] + s.epart[i & 1][1][tid];
-        if (i + DS_STAGES <= n) {
-            if (tid == 128) issue_load(i + DS_STAGES);
-            issued = i + DS_STAGES;
-        }
-        if (stamp) P.timeline[6] = clock64();
-    }
-    if (aborted) {
-        // let everything in flight land before the shared and tensor memory go away
-        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q % DS_STAGES], load_parity(q));
-        for (int q = mma_done + 1; q <= mma_issued; q++) mbar_wait(&s.mma_bar[q & 1], (uint32_t)((q >> 1) & 1), 100000u);
-        if (P.status && tid == 0) atomicOr(P.status, 2);
+        if (fail && lane == 0 && P.status) atomicOr(P.status, 2);
     }
     tc_fence_before();
     __syncthreads();
@@ -954,11 +944,10 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         p.dchunk = (const float *)(fwd_ck + CL.dchunk);
         p.gstate_out = a->gstate_out; p.gstate_in = a->gstate_in;
         p.dck = (__nv_bfloat16 *)dck; p.e0 = e0; p.status = (int *)ws;
-        p.timeline = getenv("WKV_B200_TIMELINE_DSCAN") ? (long long *)(ws + 64) : nullptr;
         const size_t smem = sizeof(DscanSmem) + 1024;
         if (cudaFuncSetAttribute(k_chunk_dscan, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return WKV_ERR_LAUNCH;
-        k_chunk_dscan<<<B * H, 256, smem, stream>>>(mrh, mgy, ms, p);
+        k_chunk_dscan<<<B * H, 160, smem, stream>>>(mrh, mgy, ms, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 3. per-chunk gradients
