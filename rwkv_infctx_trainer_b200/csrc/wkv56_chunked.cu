@@ -27,17 +27,30 @@ using namespace chunked;
 
 // ---------------------------------------------------------------------------
 // Forward: one CTA per (batch, head), serial over the chunks of the segment.
+//
+// Nine warps.  Warp 8 (one lane) feeds the machine: TMA loads, every tcgen05.mma, the TMA
+// store of r e^{cp}.  Warps 0..7 do the CUDA-core work of a chunk -- operand pass, state
+// update, mask pass, y epilogue -- and meet only on a named barrier of their own.  The fp32
+// state lives in registers (thread = key row, 16 value columns); the tensor core forms only
+// the chunk's own contribution U_j = khat_j^T V_j, which does not depend on the state, so the
+// serial chain per chunk is one fused multiply-add per state element.
 struct FwdSmem {
     Tile in[2][4];     // per stage: r, k, v, w  (r,k,w are overwritten in place by
                        // r*fr, k*fk, r*e^{cp})
     Tile x, khat[2], atil, sbf;   // khat is double-buffered: chunk j+1 is prepared while the
-                                  // state update of chunk j still reads khat of chunk j
-    float dpart[8][CH];
-    float dvec[CH];
+                                  // state product of chunk j may still read khat of chunk j
+    float dpart[4][CH];    // score-diagonal partials per token
+    float dvec[2][CH];     // decay of the whole chunk per key channel, by chunk parity
     float btot[2][CH];     // log2-decay total of each 32-token block, per channel
-    uint64_t load_bar[2];
-    uint64_t mma_bar;
+    uint64_t load_bar[2];  // TMA: a stage has landed
+    uint64_t ops_bar[2];   // compute warps -> feeder: the operands of a chunk are in place (by chunk parity:
+                           // in a state-only pass the compute warps may run a chunk ahead of the feeder)
+    uint64_t yrdy_bar;     // compute warps -> feeder: masked scores and bf16 state are in place
+    uint64_t score_bar;    // tensor core: scores of a chunk
+    uint64_t u_bar[2];     // tensor core: state product of a chunk, by chunk parity
+    uint64_t y_bar;        // tensor core: y of a chunk
     uint32_t tmem_base;
+    int abort_flag;        // set by any thread whose bounded wait ran out; ends every other wait
 };
 
 struct FwdParams {
@@ -55,17 +68,28 @@ struct FwdParams {
 };
 
 // Tensor-memory columns.  An M=64 accumulator fills lanes 0..15 of each 32-lane quarter ("lo");
-// a second one can sit in lanes 16..31 ("hi") of the same columns, which lets both halves of a
-// warp work on one token row: score columns 0..31 / y columns 0..31 in lo, 32..63 in hi.
-//   S       lo   0.. 31   state[key, value 0..31]      hi  0.. 31   state[key, value 32..63]
-//   A1a     lo  32.. 63   same-block scores, columns (s) 0..31
-//   A2      lo  64.. 95   cross-block scores (rows 32..63, columns 0..31)
-//   A1b     hi  64.. 95   same-block scores, columns (s) 32..63
-//   Y       lo  96..127   y[:, 0..31]                  hi 96..127   y[:, 32..63]
-enum { COL_S = 0, COL_A1A = 32, COL_A2 = 64, COL_Y = 96, FWD_TMEM_COLS = 128 };
+// a second one can sit in lanes 16..31 ("hi") of the same columns.
+//   U[q]    lo  32q..32q+31  khat^T V [key, value 0..31]  hi: [key, value 32..63]   (q = chunk parity)
+//   A1a     lo  64.. 95   same-block scores, columns (s) 0..31
+//   A2      lo  96..127   cross-block scores (rows 32..63, columns 0..31)
+//   A1b     hi  96..127   same-block scores, columns (s) 32..63
+//   Y       lo 128..159   y[:, 0..31]                  hi 128..159   y[:, 32..63]
+enum { COL_U = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
+constexpr int FWD_COMPUTE_THREADS = 256, FWD_THREADS = 288;
+
+// wait on an mbarrier, bounded, and cut short when another thread of the CTA has given up
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, const int *abort_flag) {
+    for (uint32_t i = 0; i < 4000000u; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63 && *reinterpret_cast<const volatile int *>(abort_flag)) return false;
+    }
+    return false;
+}
+// barrier of the 256 compute threads
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <bool PER_TOKEN>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(FWD_THREADS, 2)
 k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
             const __grid_constant__ CUtensorMap map_rh, const FwdParams P) {
@@ -73,390 +97,385 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, C = P.H * 64;
-    const bool active = (lane & 16) == 0;          // lo half-warp: owns an accumulator row in lanes 0..15
-    const int row = warp * 16 + (lane & 15);       // that row
-    const uint32_t lane_base = (uint32_t)(warp * 32);
-    // operand-pass coordinates (see wkv56_chunked.cuh)
-    const int blk = warp >> 1, cc = 4 * (warp & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
     const int n = P.nchunk;
     const bool full = P.state_only == 0;
 
     if (tid == 0) {
         mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1);
-        mbar_init(&s.mma_bar, 4);   // lane 0 of every warp issues a share of each MMA group and commits
+        mbar_init(&s.ops_bar[0], 1); mbar_init(&s.ops_bar[1], 1); mbar_init(&s.yrdy_bar, 1);
+        mbar_init(&s.score_bar, 1); mbar_init(&s.u_bar[0], 1); mbar_init(&s.u_bar[1], 1); mbar_init(&s.y_bar, 1);
+        s.abort_flag = 0;
         fence_mbar_init();
-        prefetch_tmap(&map_r); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
-        if (PER_TOKEN) prefetch_tmap(&map_w);
     }
     if (warp == 0) { tmem_alloc(&s.tmem_base, FWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = s.tmem_base, tm_hi = tm + (16u << 16);
+    int fail = 0;
 
-    auto issue_load = [&](int j) {
-        const int st = j & 1;
-        const uint32_t bytes = (PER_TOKEN ? 4 : 3) * TILE_BYTES;
-        mbar_expect_tx(&s.load_bar[st], bytes);
-        tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
-        tma_load_3d(&s.in[st][1], &map_k, &s.load_bar[st], h * 64, j * CH, b);
-        tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, j * CH, b);
-        if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, j * CH, b);
-    };
-    if (tid == 0 && n > 0) issue_load(0);
-
-    // state -> tensor memory (row = key channel, column = value channel); tcgen05.ld/st are
-    // warp-wide, lanes 16..31 of a warp touch the unused upper half of the quarter
-    const size_t sbase = (size_t)bh * 64 * 64;
-    const int vcol0 = active ? 0 : 32;             // value columns this thread holds of state row `row`
-    {
-        float v[32];
+    if (warp == 8) {
+        // ------------------------------------------------------------------ feeder
+        if (lane == 0) {
+            prefetch_tmap(&map_r); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
+            if (PER_TOKEN) prefetch_tmap(&map_w);
+            auto issue_load = [&](int j) {
+                const int st = j & 1;
+                mbar_expect_tx(&s.load_bar[st], (PER_TOKEN ? 4 : 3) * TILE_BYTES);
+                tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
+                tma_load_3d(&s.in[st][1], &map_k, &s.load_bar[st], h * 64, j * CH, b);
+                tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, j * CH, b);
+                if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, j * CH, b);
+            };
+            int issued = -1;
+            for (int j = 0; j < 2 && j < n; j++) { issue_load(j); issued = j; }
+            // descriptors: a tile's descriptor plus (byte offset >> 4) addresses inside it
+            const uint64_t d_x = make_desc(smem_u32(&s.x)), d_atil = make_desc(smem_u32(&s.atil)),
+                           d_sbf = make_desc(smem_u32(&s.sbf));
+            constexpr uint64_t KSTEP = 32 >> 4;            // K-major: 16 elements along the row
+            constexpr uint64_t MSTEP = (16 * 128) >> 4;    // MN-major: 16 rows
+            constexpr uint64_t ROW32 = (32 * 128) >> 4;    // rows 32..63 of a tile
+            constexpr uint64_t HI = 64 >> 4;               // the upper 32 of 64 contiguous elements
+            const uint32_t id32 = make_idesc(64, 32, false, false), id_mm32 = make_idesc(64, 32, true, true),
+                           id_km32 = make_idesc(64, 32, false, true);
+            int pending = -1;   // last chunk whose products may still be running
+            for (int c = 0; c < n; c++) {
+                const int st = c & 1;
+                const bool fstamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && c == n / 2 + 1;
+                if (fstamp) P.timeline[8] = clock64();
+                const uint64_t d_r = make_desc(smem_u32(&s.in[st][0])), d_k = make_desc(smem_u32(&s.in[st][1])),
+                               d_v = make_desc(smem_u32(&s.in[st][2])), d_rh = make_desc(smem_u32(&s.in[st][3])),
+                               d_kh = make_desc(smem_u32(&s.khat[st]));
+                if (!wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
+                tc_fence_after();
+                if (fstamp) P.timeline[9] = clock64();
+                if (full) {
+                    // scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T
 #pragma unroll
-        for (int q = 0; q < 32; q++) {
+                    for (int k = 0; k < 4; k++) mma_ss(tm + COL_A1A, d_r + k * KSTEP, d_k + k * KSTEP, id32, k > 0);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) mma_ss(tm_hi + COL_A2, d_r + k * KSTEP, d_k + ROW32 + k * KSTEP, id32, k > 0);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) mma_ss(tm + COL_A2, d_x + k * KSTEP, d_x + k * KSTEP, id32, k > 0);
+                    mma_commit(&s.score_bar);
+                }
+                // U = Khat^T V  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        mma_ss((hf ? tm_hi : tm) + COL_U + 32 * (c & 1), d_kh + k * MSTEP, d_v + k * MSTEP + (hf ? HI : 0),
+                               id_mm32, k > 0);
+                mma_commit(&s.u_bar[c & 1]);
+                pending = c;
+                if (fstamp) P.timeline[10] = clock64();
+                // r e^{cp} of this chunk goes out for the backward pass
+                if (P.dchunk) {
+                    tma_store_3d(&map_rh, &s.in[st][3], h * 64, c * CH, b);
+                    tma_store_commit();
+                }
+                if (full) {
+                    if (!wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag)) { fail = 1; break; }
+                    tc_fence_after();
+                    if (fstamp) P.timeline[11] = clock64();
+                    // y = Atil V + Rhat Sbf  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        const uint32_t d = (hf ? tm_hi : tm) + COL_Y;
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            mma_ss(d, d_atil + k * KSTEP, d_v + k * MSTEP + (hf ? HI : 0), id_km32, k > 0);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            mma_ss(d, d_rh + k * KSTEP, d_sbf + k * MSTEP + (hf ? HI : 0), id_km32, true);
+                    }
+                    mma_commit(&s.y_bar);
+                    if (fstamp) P.timeline[12] = clock64();
+                }
+                // the stage is free for chunk c+2 when every product of chunk c is done (the last
+                // commit covers all earlier ones of this thread) and the store has read its tile
+                if (c + 2 < n) {
+                    uint64_t *last = full ? &s.y_bar : &s.u_bar[c & 1];
+                    const uint32_t par = full ? (uint32_t)(c & 1) : (uint32_t)((c >> 1) & 1);
+                    if (!wait_or_abort(last, par, &s.abort_flag)) { fail = 1; break; }
+                    pending = -1;
+                    tma_store_wait_read();
+                    issue_load(c + 2);
+                    issued = c + 2;
+                    if (fstamp) P.timeline[13] = clock64();
+                }
+            }
+            if (fail) {
+                atomicExch(&s.abort_flag, 1);
+                if (P.status) atomicOr(P.status, 1);
+                // let whatever is in flight finish before shared and tensor memory go away
+                for (int q = 0; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1), 200000u);
+                if (pending >= 0) {
+                    mbar_wait(&s.u_bar[pending & 1], (uint32_t)((pending >> 1) & 1), 200000u);
+                    if (full) mbar_wait(&s.score_bar, (uint32_t)(pending & 1), 200000u);
+                }
+            }
+            tma_store_wait_read();
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ compute warps
+        const int wg = warp >> 2, w4 = warp & 3;
+        const bool lo = (lane & 16) == 0;
+        const int row = w4 * 16 + (lane & 15);         // accumulator row: key channel (state) or token (scores, y)
+        const uint32_t lane_base = (uint32_t)(w4 * 32);
+        // operand-pass coordinates (see wkv56_chunked.cuh): 4 tokens x 4 channels per thread
+        const int blk = w4 >> 1, cc = 4 * (w4 & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
+        const int ch0 = cc * 8 + 4 * wg;
+        const int vcol0 = (lo ? 0 : 32) + 16 * wg;     // 16 columns of the row this thread holds
+
+        const size_t sbase = (size_t)bh * 64 * 64;
+        float S[16];
+#pragma unroll
+        for (int q = 0; q < 16; q++) {
             const int vc = vcol0 + q;
             const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-            v[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
+            S[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
         }
-        tmem_st16(tmem_addr(tm, lane_base, COL_S), v);
-        tmem_st16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
-    }
-    tmem_st_wait();
+        float uu[4], lwc[4];
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            uu[ch] = __bfloat162float(P.u[h * 64 + ch0 + ch]);
+            bool live;
+            lwc[ch] = PER_TOKEN ? 0.f : log2_decay(P.wvec[h * 64 + ch0 + ch], P.w_kind, live);
+        }
 
-    // per-thread constants of the 8 channels this thread prepares
-    float uu[8], lwc[8];
-    {
-        const uint4 q = *reinterpret_cast<const uint4 *>(P.u + h * 64 + cc * 8);
-        unpack8(q, uu);
-        if (!PER_TOKEN) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                bool live;
-                lwc[ch] = log2_decay(P.wvec[h * 64 + cc * 8 + ch], P.w_kind, live);
-            }
-        }
-    }
-
-    // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
-    // score-diagonal partials and the chunk decay.  Contains one __syncthreads.
-    auto prep = [&](int j) {
-        Tile *in = s.in[j & 1];
-        Tile &khat = s.khat[j & 1];
-        float c[4][8];
-        Decay D;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int t = tok0 + i;
-            const bool valid = j * CH + t < P.T;
-            if (PER_TOKEN) {
-                float x[8];
-                unpack8(ld_tile(in[3], t, cc), x);
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
-                    bool live;
-                    const float l2 = log2_decay(x[ch], P.w_kind, live);
-                    c[i][ch] = valid ? l2 : 0.f;
-                }
-            } else {
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
-            }
-        }
-        decay_scan(c, lane, D);
-        if (tgl == 7) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) s.btot[blk][cc * 8 + ch] = D.e[ch];
-        }
-        __syncthreads();
-        float other[8];          // 2^{total of the other block}
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) other[ch] = exp2f(s.btot[blk ^ 1][cc * 8 + ch]);
-        if (blk == 0 && tgl == 7) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                const float d = exp2f(D.e[ch]) * other[ch];
-                s.dvec[cc * 8 + ch] = d;
-                if (P.dchunk) P.dchunk[((size_t)bh * n + j) * 64 + cc * 8 + ch] = d;
-            }
-        }
-        // r-side operands, walking forward over the thread's tokens:
-        //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
-        //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
-        float fa[8], fb[8];
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
-            fb[ch] = exp2f(D.cp0[ch]);
-        }
-        if (full) {
+        // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
+        // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
+        auto prep = [&](int j) {
+            Tile *in = s.in[j & 1];
+            Tile &khat = s.khat[j & 1];
+            float c[4][4];
+            DecayT<4> D;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int t = tok0 + i;
-                float r[8], k[8], rt[8], rh[8], xx[8];
-                unpack8(ld_tile(in[0], t, cc), r);
-                unpack8(ld_tile(in[1], t, cc), k);
-                float dsum = 0.f;
+                const bool valid = j * CH + t < P.T;
+                if (PER_TOKEN) {
+                    float x[4];
+                    unpack4(ld_tile4(in[3], t, cc, wg), x);
 #pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
-                    rt[ch] = r[ch] * fa[ch];
-                    xx[ch] = r[ch] * fb[ch];
-                    rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
-                    dsum += r[ch] * uu[ch] * k[ch];
+                    for (int ch = 0; ch < 4; ch++) {
+                        bool live;
+                        const float l2 = log2_decay(x[ch], P.w_kind, live);
+                        c[i][ch] = valid ? l2 : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
+                }
+            }
+            decay_scan(c, lane, D);
+            if (tgl == 7) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) s.btot[blk][ch0 + ch] = D.e[ch];
+            }
+            compute_sync();
+            float other[4];          // 2^{total of the other block}
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(s.btot[blk ^ 1][ch0 + ch]);
+            if (blk == 0 && tgl == 7) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    const float d = exp2f(D.e[ch]) * other[ch];
+                    s.dvec[j & 1][ch0 + ch] = d;
+                    if (P.dchunk) P.dchunk[((size_t)bh * n + j) * 64 + ch0 + ch] = d;
+                }
+            }
+            // r-side operands, walking forward over the thread's tokens:
+            //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
+            //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
+            float fa[4], fb[4];
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+                fb[ch] = exp2f(D.cp0[ch]);
+            }
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = tok0 + i;
+                    float r[4], k[4], rt[4], rh[4], xx[4];
+                    unpack4(ld_tile4(in[0], t, cc, wg), r);
+                    unpack4(ld_tile4(in[1], t, cc, wg), k);
+                    float dsum = 0.f;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        rt[ch] = r[ch] * fa[ch];
+                        xx[ch] = r[ch] * fb[ch];
+                        rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
+                        dsum += r[ch] * uu[ch] * k[ch];
+                        fa[ch] *= D.w[i][ch];
+                        fb[ch] *= D.w[i][ch];
+                    }
+                    st_tile4(in[0], t, cc, wg, pack4(rt));
+                    st_tile4(in[3], t, cc, wg, pack4(rh));
+                    if (blk) st_tile4(s.x, t, cc, wg, pack4(xx));
+                    // the four lanes that share this token (lane & 3) pool their channels
+                    dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+                    dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+                    if ((lane & 3) == 0) s.dpart[2 * wg + (w4 & 1)][t] = dsum;
+                }
+            } else if (P.dchunk) {
+                // state-only pass on behalf of a backward call: r e^{cp} alone
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = tok0 + i;
+                    float r[4], rh[4];
+                    unpack4(ld_tile4(in[0], t, cc, wg), r);
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        const float xx = r[ch] * fb[ch];
+                        rh[ch] = blk ? xx * other[ch] : xx;
+                        fb[ch] *= D.w[i][ch];
+                    }
+                    st_tile4(in[3], t, cc, wg, pack4(rh));
+                }
+            }
+            // k-side operands, walking backward:
+            //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
+            //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+                fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
+            }
+#pragma unroll
+            for (int i = 3; i >= 0; i--) {
+                const int t = tok0 + i;
+                float k[4], kt[4], kh[4], xx[4];
+                unpack4(ld_tile4(in[1], t, cc, wg), k);
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    kt[ch] = k[ch] * fa[ch];
+                    xx[ch] = k[ch] * fb[ch];
+                    kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
                     fa[ch] *= D.w[i][ch];
                     fb[ch] *= D.w[i][ch];
                 }
-                st_tile(in[0], t, cc, pack8(rt));
-                st_tile(in[3], t, cc, pack8(rh));
-                if (blk) st_tile(s.x, t, cc, pack8(xx));
-                s.dpart[cc][t] = dsum;
-            }
-        } else if (P.dchunk) {
-            // state-only pass on behalf of a backward call: r e^{cp} alone
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int t = tok0 + i;
-                float r[8], rh[8];
-                unpack8(ld_tile(in[0], t, cc), r);
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
-                    const float xx = r[ch] * fb[ch];
-                    rh[ch] = blk ? xx * other[ch] : xx;
-                    fb[ch] *= D.w[i][ch];
+                if (full) {
+                    st_tile4(in[1], t, cc, wg, pack4(kt));
+                    if (!blk) st_tile4(s.x, t, cc, wg, pack4(xx));
                 }
-                st_tile(in[3], t, cc, pack8(rh));
+                st_tile4(khat, t, cc, wg, pack4(kh));
             }
-        }
-        // k-side operands, walking backward:
-        //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
-        //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-            fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
-            fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
-        }
-#pragma unroll
-        for (int i = 3; i >= 0; i--) {
-            const int t = tok0 + i;
-            float k[8], kt[8], kh[8], xx[8];
-            unpack8(ld_tile(in[1], t, cc), k);
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                kt[ch] = k[ch] * fa[ch];
-                xx[ch] = k[ch] * fb[ch];
-                kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
-                fa[ch] *= D.w[i][ch];
-                fb[ch] *= D.w[i][ch];
-            }
-            if (full) {
-                st_tile(in[1], t, cc, pack8(kt));
-                if (!blk) st_tile(s.x, t, cc, pack8(xx));
-            }
-            st_tile(khat, t, cc, pack8(kh));
-        }
-    };
-
-    uint32_t mma_phase = 0;
-    int fail = 0;        // a bounded wait ran out (carried through the next barrier)
-    int aborted = 0;
-    int issued = n > 0 ? 0 : -1, landed = -1;   // TMA loads issued / seen complete
-
-    // prologue: operands of chunk 0
-    if (n > 0) {
-        if (mbar_wait(&s.load_bar[0], 0)) landed = 0; else fail = 1;
-        prep(0);
-        if (n > 1) {
-            if (tid == 0) issue_load(1);
-            issued = 1;
-        }
-    }
-    fence_async_smem();
-    tc_fence_before();
-    if (__syncthreads_or(fail)) aborted = 1;
-
-    // Software pipeline: while the tensor core runs y/state of chunk j, the CUDA cores prepare
-    // the operands of chunk j+1.
-    for (int j = 0; j < n && !aborted; j++) {
-        const int st = j & 1;
-        Tile *in = s.in[st];
-        const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
-        if (stamp) P.timeline[0] = clock64();
-        // r e^{cp} of this chunk goes out for the backward pass (read again by the state product below)
-        if (tid == 0 && P.dchunk) {
-            tma_store_3d(&map_rh, &in[3], h * 64, j * CH, b);
-            tma_store_commit();
-        }
-
-        // (A) scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T.  A tcgen05.mma is
-        // issued by one thread and costs it ~100 cycles of descriptor arithmetic, so the three
-        // accumulators go out from three warps at once; every warp's lane 0 commits.
-        if (lane == 0 && full) {
-            tc_fence_after();
-            const uint32_t id32 = make_idesc(64, 32, false, false);
-            if (warp == 0) {
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(tm + COL_A1A, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 0, k), id32, k > 0);
-            } else if (warp == 1) {
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(tm_hi + COL_A2, desc_kmajor(&in[0], 0, k), desc_kmajor(&in[1], 32, k), id32, k > 0);
-            } else if (warp == 2) {
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(tm + COL_A2, desc_kmajor(&s.x, 0, k), desc_kmajor(&s.x, 0, k), id32, k > 0);
-            }
-            mma_commit(&s.mma_bar);
-        }
-        // (B) meanwhile: snapshot the state as bf16 (operand of rhat*S, checkpoint) and decay it;
-        // each half-warp holds 32 of the 64 value columns of its state row
-        {
-            float v[32];
-            tmem_ld16(tmem_addr(tm, lane_base, COL_S), v);
-            tmem_ld16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
-            tmem_ld_wait();
-            const float d = s.dvec[row];
-            uint4 q[4];
-#pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) {
-                q[c8] = pack8(v + 8 * c8);
-                st_tile(s.sbf, row, (vcol0 >> 3) + c8, q[c8]);
+        };
+        // a wait of a compute thread; running out of patience ends everybody else's waits too
+        auto cwait = [&](uint64_t *bar, uint32_t parity) {
+            if (wait_or_abort(bar, parity, &s.abort_flag)) return true;
+            *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
+            return false;
+        };
+        // bf16 copy of the state at the start of chunk jn: operand of rhat*S, checkpoint
+        auto publish_state = [&](int jn) {
+            const uint4 q0 = pack8(S), q1 = pack8(S + 8);
+            if (full && jn < n) {
+                st_tile(s.sbf, row, (vcol0 >> 3), q0);
+                st_tile(s.sbf, row, (vcol0 >> 3) + 1, q1);
             }
             if (P.ckpt) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + j) * 64 + row) * 64 + vcol0);
-#pragma unroll
-                for (int c8 = 0; c8 < 4; c8++) dst[c8] = q[c8];
+                uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + jn) * 64 + row) * 64 + vcol0);
+                dst[0] = q0;
+                dst[1] = q1;
             }
-#pragma unroll
-            for (int c = 0; c < 32; c++) v[c] *= d;
-            tmem_st16(tmem_addr(tm, lane_base, COL_S), v);
-            tmem_st16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
-        }
-        tmem_st_wait();
-        if (stamp) P.timeline[1] = clock64();
-        // (C) mask pass: lo lanes own columns 0..31 of token row t, hi lanes columns 32..63
-        if (full) {
-            if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
-            mma_phase ^= 1;
-            tc_fence_after();
-            const int t = row;
-            const int col0 = active ? 0 : 32;
-            float a[32];
-            // rows 0..31 (warps 0,1): A1a for the lo half, nothing to read for the hi half;
-            // rows 32..63 (warps 2,3): A2 (lo) and A1b (hi) share their columns
-            const int src = warp < 2 ? COL_A1A : COL_A2;
-            tmem_ld16(tmem_addr(tm, lane_base, src), a);
-            tmem_ld16(tmem_addr(tm, lane_base, src + 16), a + 16);
-            tmem_ld_wait();
-            float diag = 0.f;
-#pragma unroll
-            for (int q = 0; q < 8; q++) diag += s.dpart[q][t];
-            const bool cross = t >= HB && active;          // A2 block: every entry is kept
-            const bool empty = t < HB && !active;          // upper-right block: all zero
-#pragma unroll
-            for (int q = 0; q < 32; q++) {
-                const int sx = col0 + q;
-                float val = a[q];
-                if (!cross) val = sx < t ? val : (sx == t ? diag : 0.f);
-                if (empty) val = 0.f;
-                a[q] = val;
-            }
-#pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) st_tile(s.atil, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
-        }
-        if (stamp) P.timeline[2] = clock64();
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(fail)) { aborted = 1; break; }
+        };
 
-        // (D) y = Atil V + Rhat Sbf (value columns 0..31 -> lo lanes, 32..63 -> hi lanes) ;
-        //     S = d*S + Khat^T V
-        if (lane == 0) {
-            tc_fence_after();
-            if (warp < 2 && full) {
-                const uint32_t id_km32 = make_idesc(64, 32, false, true);
-                const uint32_t d = (warp ? tm_hi : tm) + COL_Y;
-                const uint64_t off = warp ? 4 : 0;   // +64 bytes along the contiguous dim
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(d, desc_kmajor(&s.atil, 0, k), desc_mnmajor(&in[2], 0, k) + off, id_km32, k > 0);
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(d, desc_kmajor(&in[3], 0, k), desc_mnmajor(&s.sbf, 0, k) + off, id_km32, true);
-            } else if (warp >= 2) {
-                const uint32_t id_mm32 = make_idesc(64, 32, true, true);
-                const uint32_t d = (warp == 3 ? tm_hi : tm) + COL_S;
-                const uint64_t off = warp == 3 ? 4 : 0;
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    mma_ss(d, desc_mnmajor(&s.khat[st], 0, k), desc_mnmajor(&in[2], 0, k) + off, id_mm32, true);
+        // Iteration j works on three chunks at once: operands of chunk j+1, y of chunk j, and the
+        // state / masked scores that the y product of chunk j+1 needs.  j = -1 is the prologue.
+        for (int j = -1; j < n; j++) {
+            const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
+            if (stamp) P.timeline[0] = clock64();
+            // (P) operands of chunk j+1
+            if (j + 1 < n) {
+                if (!cwait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) fail = 1;
+                if (stamp) P.timeline[5] = clock64();
+                prep(j + 1);
+                if (stamp) P.timeline[6] = clock64();
+                fence_async_smem();
+                compute_sync();
+                if (tid == 0) mbar_arrive(&s.ops_bar[(j + 1) & 1]);
             }
-            mma_commit(&s.mma_bar);
-        }
-        if (stamp) P.timeline[3] = clock64();
-        // (E) operands of the next chunk while the tensor core works
-        if (j + 1 < n) {
-            if (mbar_wait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) landed = j + 1; else fail = 1;
-            prep(j + 1);
-        }
-        if (stamp) P.timeline[4] = clock64();
-        // (F) y of this chunk
-        if (!mbar_wait(&s.mma_bar, mma_phase)) fail = 1;
-        mma_phase ^= 1;
-        tc_fence_after();
-        if (stamp) P.timeline[5] = clock64();
-        if (full) {
-            const int t = j * CH + row;
-            float yv[32];
-            tmem_ld16(tmem_addr(tm, lane_base, COL_Y), yv);
-            tmem_ld16(tmem_addr(tm, lane_base, COL_Y + 16), yv + 16);
-            tmem_ld_wait();
-            if (t < P.T) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64 + (active ? 0 : 32));
-#pragma unroll
-                for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(yv + 8 * c8);
+            if (stamp) P.timeline[1] = clock64();
+            // (E) y of chunk j
+            if (j >= 0 && full) {
+                if (!cwait(&s.y_bar, (uint32_t)(j & 1))) fail = 1;
+                tc_fence_after();
+                float yv[16];
+                tmem_ld16(tmem_addr(tm, lane_base, COL_Y + 16 * wg), yv);
+                tmem_ld_wait();
+                const int t = j * CH + row;
+                if (t < P.T) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64 + vcol0);
+                    dst[0] = pack8(yv);
+                    dst[1] = pack8(yv + 8);
+                }
             }
+            if (stamp) P.timeline[2] = clock64();
+            // (S) state at the start of chunk j+1:  S = d_j S + U_j
+            if (j >= 0) {
+                if (!cwait(&s.u_bar[j & 1], (uint32_t)((j >> 1) & 1))) fail = 1;
+                tc_fence_after();
+                float uacc[16];
+                tmem_ld16(tmem_addr(tm, lane_base, COL_U + 32 * (j & 1) + 16 * wg), uacc);
+                tmem_ld_wait();
+                const float d = s.dvec[j & 1][row];
+#pragma unroll
+                for (int q = 0; q < 16; q++) S[q] = fmaf(d, S[q], uacc[q]);
+            }
+            publish_state(j + 1);
+            if (stamp) P.timeline[3] = clock64();
+            // (M) masked scores of chunk j+1: lo lanes own columns 0..31 of token row t, hi lanes 32..63;
+            // this warp group 16 of them
+            if (j + 1 < n && full) {
+                if (!cwait(&s.score_bar, (uint32_t)((j + 1) & 1))) fail = 1;
+                tc_fence_after();
+                const int t = row;
+                float a[16];
+                // rows 0..31 (w4 0,1): A1a for the lo half, nothing kept for the hi half;
+                // rows 32..63 (w4 2,3): A2 (lo) and A1b (hi) share their columns
+                tmem_ld16(tmem_addr(tm, lane_base, (w4 < 2 ? COL_A1A : COL_A2) + 16 * wg), a);
+                tmem_ld_wait();
+                const float diag = s.dpart[0][t] + s.dpart[1][t] + s.dpart[2][t] + s.dpart[3][t];
+                // entries left of local column `lim` are kept, column lim is the diagonal
+                const bool cross = t >= HB && lo, empty = t < HB && !lo;
+                const int lim = cross ? 99 : (empty ? -1 : (t & 31) - 16 * wg);
+#pragma unroll
+                for (int q = 0; q < 16; q++) a[q] = q < lim ? a[q] : (q == lim ? diag : 0.f);
+                st_tile(s.atil, t, (vcol0 >> 3), pack8(a));
+                st_tile(s.atil, t, (vcol0 >> 3) + 1, pack8(a + 8));
+            }
+            fence_async_smem();
+            tc_fence_before();
+            {
+                // closing barrier of the iteration; a failed wait anywhere ends the loop for everyone
+                uint32_t any;
+                asm volatile(
+                    "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, 256, q;\nselp.u32 %0, 1, 0, p;\n}"
+                    : "=r"(any) : "r"((uint32_t)fail) : "memory");
+                if (any) { fail = 1; break; }
+            }
+            if (j + 1 < n && full && tid == 0) mbar_arrive(&s.yrdy_bar);
+            if (stamp) P.timeline[4] = clock64();
         }
-        if (stamp) P.timeline[6] = clock64();
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(fail)) { aborted = 1; break; }
-        // stage j&1 is free now (its last reader was the MMA group that just completed)
-        if (j + 2 < n) {
+        if (fail) {
             if (tid == 0) {
-                tma_store_wait_read();     // the store above has read its tile of this stage
-                issue_load(j + 2);
+                atomicExch(&s.abort_flag, 1);
+                if (P.status) atomicOr(P.status, 1);
             }
-            issued = j + 2;
-        }
-        if (stamp) P.timeline[7] = clock64();
-    }
-
-    // after a failed wait: let TMA loads that were issued land (bounded), so that the CTA
-    // never exits under one
-    if (aborted) {
-        for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1));
-    }
-    tc_fence_after();
-    {
-        float v[32];
-        tmem_ld16(tmem_addr(tm, lane_base, COL_S), v);
-        tmem_ld16(tmem_addr(tm, lane_base, COL_S + 16), v + 16);
-        tmem_ld_wait();
-        if (!aborted && P.state_out) {
+        } else if (P.state_out) {
 #pragma unroll
-            for (int q = 0; q < 32; q++) {
+            for (int q = 0; q < 16; q++) {
                 const int vc = vcol0 + q;
                 const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-                P.state_out[sbase + idx] = v[q];
+                P.state_out[sbase + idx] = S[q];
             }
         }
-        if (!aborted && P.ckpt) {
-            uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + n) * 64 + row) * 64 + vcol0);
-#pragma unroll
-            for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
-        }
     }
-    if (aborted && P.status && tid == 0) atomicOr(P.status, 1);
-    if (tid == 0) tma_store_wait_read();
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tm, FWD_TMEM_COLS);
@@ -511,7 +530,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return WKV_ERR_LAUNCH;
-    kern<<<B * H, 128, smem, stream>>>(mr, mk, mv, mw, mrh, p);
+    kern<<<B * H, FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
     return launch_status();
 }
 
