@@ -58,10 +58,56 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait: gives up after `limit` polls (each poll itself blocks for a
 // hardware-defined time slice) and returns false; the caller records the
 // failure and unwinds.  Nothing in these kernels ever spins without a bound.
+// The polling loop is written in PTX: as a C loop the compiler unrolls it and
+// treats the code after it as possibly divergent, which costs hundreds of
+// instructions per kernel.  (Labels inside a { } block are local to it.)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = 4000000u) {
-    for (uint32_t i = 0; i < limit; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .u32 n;\n"
+        "mov.u32 n, %3;\n"
+        "WAIT_LOOP:\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "@p bra WAIT_DONE;\n"
+        "sub.u32 n, n, 1;\n"
+        "setp.ne.u32 p, n, 0;\n"
+        "@p bra WAIT_LOOP;\n"
+        "WAIT_DONE:\n"
+        "selp.b32 %0, 1, 0, p;\n"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(limit)
+        : "memory");
+    return ok != 0;
+}
+// The same, cut short when the word at `abort_flag` (shared memory) becomes non-zero:
+// lets one thread that gave up end the waits of every other thread of the CTA.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, const int *abort_flag,
+                                                   uint32_t limit = 4000000u) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        ".reg .u32 n, f;\n"
+        "mov.u32 n, %3;\n"
+        "WAIT_LOOP:\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "@p bra WAIT_DONE;\n"
+        "ld.volatile.shared.u32 f, [%4];\n"
+        "setp.ne.u32 q, f, 0;\n"
+        "@q bra WAIT_DONE;\n"
+        "sub.u32 n, n, 1;\n"
+        "setp.ne.u32 p, n, 0;\n"
+        "@p bra WAIT_LOOP;\n"
+        "WAIT_DONE:\n"
+        "selp.b32 %0, 1, 0, p;\n"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(limit), "r"(smem_u32(abort_flag))
+        : "memory");
+    return ok != 0;
 }
 
 // ---------------------------------------------------------------------- TMA

@@ -41,7 +41,7 @@ struct FwdSmem {
                                   // state product of chunk j may still read khat of chunk j
     float dpart[4][CH];    // score-diagonal partials per token
     float dvec[2][CH];     // decay of the whole chunk per key channel, by chunk parity
-    float btot[2][CH];     // log2-decay total of each 32-token block, per channel
+    float wtot[8][CH];     // log2-decay total of each warp's 8 tokens, per channel
     uint64_t load_bar[2];  // TMA: a stage has landed
     uint64_t ops_bar[2];   // compute warps -> feeder: the operands of a chunk are in place (by chunk parity:
                            // in a state-only pass the compute warps may run a chunk ahead of the feeder)
@@ -77,14 +77,6 @@ struct FwdParams {
 enum { COL_U = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
 constexpr int FWD_COMPUTE_THREADS = 256, FWD_THREADS = 288;
 
-// wait on an mbarrier, bounded, and cut short when another thread of the CTA has given up
-__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, const int *abort_flag) {
-    for (uint32_t i = 0; i < 4000000u; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63 && *reinterpret_cast<const volatile int *>(abort_flag)) return false;
-    }
-    return false;
-}
 // barrier of the 256 compute threads
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -95,7 +87,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             const __grid_constant__ CUtensorMap map_rh, const FwdParams P) {
     extern __shared__ unsigned char smem_raw[];
     FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // tells the compiler it is uniform across the warp
     const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, C = P.H * 64;
     const int n = P.nchunk;
     const bool full = P.state_only == 0;
@@ -146,7 +139,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const uint64_t d_r = make_desc(smem_u32(&s.in[st][0])), d_k = make_desc(smem_u32(&s.in[st][1])),
                                d_v = make_desc(smem_u32(&s.in[st][2])), d_rh = make_desc(smem_u32(&s.in[st][3])),
                                d_kh = make_desc(smem_u32(&s.khat[st]));
-                if (!wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
+                if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
                 tc_fence_after();
                 if (fstamp) P.timeline[9] = clock64();
                 if (full) {
@@ -175,7 +168,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     tma_store_commit();
                 }
                 if (full) {
-                    if (!wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag)) { fail = 1; break; }
+                    if (!mbar_wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag)) { fail = 1; break; }
                     tc_fence_after();
                     if (fstamp) P.timeline[11] = clock64();
                     // y = Atil V + Rhat Sbf  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
@@ -197,7 +190,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 if (c + 2 < n) {
                     uint64_t *last = full ? &s.y_bar : &s.u_bar[c & 1];
                     const uint32_t par = full ? (uint32_t)(c & 1) : (uint32_t)((c >> 1) & 1);
-                    if (!wait_or_abort(last, par, &s.abort_flag)) { fail = 1; break; }
+                    if (!mbar_wait_or_abort(last, par, &s.abort_flag)) { fail = 1; break; }
                     pending = -1;
                     tma_store_wait_read();
                     issue_load(c + 2);
@@ -224,9 +217,9 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         const bool lo = (lane & 16) == 0;
         const int row = w4 * 16 + (lane & 15);         // accumulator row: key channel (state) or token (scores, y)
         const uint32_t lane_base = (uint32_t)(w4 * 32);
-        // operand-pass coordinates (see wkv56_chunked.cuh): 4 tokens x 4 channels per thread
-        const int blk = w4 >> 1, cc = 4 * (w4 & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
-        const int ch0 = cc * 8 + 4 * wg;
+        // operand-pass coordinates (see decay_scan8 in wkv56_chunked.cuh): 4 tokens x 4 channels per thread
+        const int blk = warp >> 2, cc = (lane & 15) >> 1, hf = lane & 1, tok0 = 8 * warp + 4 * (lane >> 4);
+        const int ch0 = cc * 8 + 4 * hf;
         const int vcol0 = (lo ? 0 : 32) + 16 * wg;     // 16 columns of the row this thread holds
 
         const size_t sbase = (size_t)bh * 64 * 64;
@@ -248,6 +241,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
         // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
         auto prep = [&](int j) {
+            const bool pst = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2 + 1;
             Tile *in = s.in[j & 1];
             Tile &khat = s.khat[j & 1];
             float c[4][4];
@@ -258,7 +252,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const bool valid = j * CH + t < P.T;
                 if (PER_TOKEN) {
                     float x[4];
-                    unpack4(ld_tile4(in[3], t, cc, wg), x);
+                    unpack4(ld_tile4(in[3], t, cc, hf), x);
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
                         bool live;
@@ -270,16 +264,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     for (int ch = 0; ch < 4; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
                 }
             }
-            decay_scan(c, lane, D);
-            if (tgl == 7) {
-#pragma unroll
-                for (int ch = 0; ch < 4; ch++) s.btot[blk][ch0 + ch] = D.e[ch];
-            }
-            compute_sync();
+            float other_l2[4];
+            if (pst) P.timeline[14] = clock64();
+            decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [] { compute_sync(); });
+            if (pst) P.timeline[15] = clock64();
             float other[4];          // 2^{total of the other block}
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(s.btot[blk ^ 1][ch0 + ch]);
-            if (blk == 0 && tgl == 7) {
+            for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
+            if (warp == 0 && lane < 16) {
 #pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     const float d = exp2f(D.e[ch]) * other[ch];
@@ -301,8 +293,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int i = 0; i < 4; i++) {
                     const int t = tok0 + i;
                     float r[4], k[4], rt[4], rh[4], xx[4];
-                    unpack4(ld_tile4(in[0], t, cc, wg), r);
-                    unpack4(ld_tile4(in[1], t, cc, wg), k);
+                    unpack4(ld_tile4(in[0], t, cc, hf), r);
+                    unpack4(ld_tile4(in[1], t, cc, hf), k);
                     float dsum = 0.f;
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
@@ -313,13 +305,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                         fa[ch] *= D.w[i][ch];
                         fb[ch] *= D.w[i][ch];
                     }
-                    st_tile4(in[0], t, cc, wg, pack4(rt));
-                    st_tile4(in[3], t, cc, wg, pack4(rh));
-                    if (blk) st_tile4(s.x, t, cc, wg, pack4(xx));
-                    // the four lanes that share this token (lane & 3) pool their channels
+                    st_tile4(in[0], t, cc, hf, pack4(rt));
+                    st_tile4(in[3], t, cc, hf, pack4(rh));
+                    if (blk) st_tile4(s.x, t, cc, hf, pack4(xx));
+                    // groups of four lanes pool their channels; four partials per token remain
                     dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
                     dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
-                    if ((lane & 3) == 0) s.dpart[2 * wg + (w4 & 1)][t] = dsum;
+                    if ((lane & 3) == 0) s.dpart[(lane & 15) >> 2][t] = dsum;
                 }
             } else if (P.dchunk) {
                 // state-only pass on behalf of a backward call: r e^{cp} alone
@@ -327,16 +319,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int i = 0; i < 4; i++) {
                     const int t = tok0 + i;
                     float r[4], rh[4];
-                    unpack4(ld_tile4(in[0], t, cc, wg), r);
+                    unpack4(ld_tile4(in[0], t, cc, hf), r);
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
                         const float xx = r[ch] * fb[ch];
                         rh[ch] = blk ? xx * other[ch] : xx;
                         fb[ch] *= D.w[i][ch];
                     }
-                    st_tile4(in[3], t, cc, wg, pack4(rh));
+                    st_tile4(in[3], t, cc, hf, pack4(rh));
                 }
             }
+            if (pst) P.timeline[16] = clock64();
             // k-side operands, walking backward:
             //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
             //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
@@ -349,7 +342,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             for (int i = 3; i >= 0; i--) {
                 const int t = tok0 + i;
                 float k[4], kt[4], kh[4], xx[4];
-                unpack4(ld_tile4(in[1], t, cc, wg), k);
+                unpack4(ld_tile4(in[1], t, cc, hf), k);
 #pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     kt[ch] = k[ch] * fa[ch];
@@ -359,15 +352,15 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     fb[ch] *= D.w[i][ch];
                 }
                 if (full) {
-                    st_tile4(in[1], t, cc, wg, pack4(kt));
-                    if (!blk) st_tile4(s.x, t, cc, wg, pack4(xx));
+                    st_tile4(in[1], t, cc, hf, pack4(kt));
+                    if (!blk) st_tile4(s.x, t, cc, hf, pack4(xx));
                 }
-                st_tile4(khat, t, cc, wg, pack4(kh));
+                st_tile4(khat, t, cc, hf, pack4(kh));
             }
         };
         // a wait of a compute thread; running out of patience ends everybody else's waits too
         auto cwait = [&](uint64_t *bar, uint32_t parity) {
-            if (wait_or_abort(bar, parity, &s.abort_flag)) return true;
+            if (mbar_wait_or_abort(bar, parity, &s.abort_flag)) return true;
             *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
             return false;
         };
@@ -440,7 +433,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 // rows 32..63 (w4 2,3): A2 (lo) and A1b (hi) share their columns
                 tmem_ld16(tmem_addr(tm, lane_base, (w4 < 2 ? COL_A1A : COL_A2) + 16 * wg), a);
                 tmem_ld_wait();
-                const float diag = s.dpart[0][t] + s.dpart[1][t] + s.dpart[2][t] + s.dpart[3][t];
+                const float diag = (s.dpart[0][t] + s.dpart[1][t]) + (s.dpart[2][t] + s.dpart[3][t]);
                 // entries left of local column `lim` are kept, column lim is the diagonal
                 const bool cross = t >= HB && lo, empty = t < HB && !lo;
                 const int lim = cross ? 99 : (empty ? -1 : (t & 31) - 16 * wg);

@@ -106,6 +106,62 @@ __device__ __forceinline__ void decay_scan(float (&l2)[4][NCH], int lane, DecayT
     }
 }
 
+// Operand-pass layout for kernels with eight compute warps (256 threads):
+//   warp w owns tokens 8w .. 8w+7 of the chunk (so warps 0..3 are block 0, warps 4..7 block 1);
+//   lane = 16*r + 2*cc + hf:  tokens 8w + 4r .. +3,  channels 8*cc + 4*hf .. +3,
+// i.e. a thread owns 4 tokens x 4 channels and reads or writes 8 bytes of a tile row at a time.
+// The 16 lanes of a half-warp then cover one whole 128-byte row: free of bank conflicts.
+//
+// In: l2[i][ch] per-token log2-decay.  Out: l2 holds the block-local inclusive sums c; D as in
+// decay_scan; other_l2 = log2-decay total of the other block.  The totals of the eight warps go
+// through `wtot` ([8][CH] floats of shared memory); `sync` is the barrier of the 256 threads.
+template <class Sync>
+__device__ __forceinline__ void decay_scan8(float (&l2)[4][4], int warp, int lane, float *wtot, DecayT<4> &D,
+                                            float (&other_l2)[4], Sync sync) {
+    const int r = lane >> 4, ch0 = (lane & 15) * 4, blk = warp >> 2, wb = warp & 3;
+    float tot[4], first[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) D.w[i][ch] = exp2f(l2[i][ch]);
+        first[ch] = l2[0][ch];
+#pragma unroll
+        for (int i = 1; i < 4; i++) l2[i][ch] += l2[i - 1][ch];
+        const float o = __shfl_xor_sync(0xffffffffu, l2[3][ch], 16);
+        tot[ch] = l2[3][ch] + o;
+        if (r) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) l2[i][ch] += o;
+        }
+    }
+    if (r) *reinterpret_cast<float4 *>(wtot + warp * CH + ch0) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    sync();
+    const float *own = wtot + 4 * blk * CH + ch0, *oth = wtot + 4 * (blk ^ 1) * CH + ch0;
+    float base[4] = {0.f, 0.f, 0.f, 0.f}, m[4], e[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(own + q * CH);
+        const float4 b4 = *reinterpret_cast<const float4 *>(oth + q * CH);
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            if (q == 0) { m[ch] = a[ch]; other_l2[ch] = b[ch]; }
+            else if (q == 1) { m[ch] += a[ch]; e[ch] = m[ch]; other_l2[ch] += b[ch]; }     // m: through token 15 of the block
+            else { e[ch] += a[ch]; other_l2[ch] += b[ch]; }                                // e: the whole block
+            if (wb > q) base[ch] += a[ch];
+        }
+    }
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) l2[i][ch] += base[ch];
+        D.cp0[ch] = l2[0][ch] - first[ch];
+        D.c3[ch] = l2[3][ch];
+        D.m[ch] = m[ch];
+        D.e[ch] = e[ch];
+    }
+}
+
 // 8-byte halves of a 16-byte tile chunk (4 bf16)
 __device__ __forceinline__ void unpack4(const uint2 &q, float *f) {
     f[0] = __uint_as_float(q.x << 16); f[1] = __uint_as_float(q.x & 0xFFFF0000u);

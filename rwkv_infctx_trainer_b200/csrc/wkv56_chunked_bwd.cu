@@ -313,14 +313,14 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             const __grid_constant__ CUtensorMap map_gw, const BwdParams P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     BwdSmem &s = *reinterpret_cast<BwdSmem *>(smem_raw);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // tells the compiler it is uniform across the warp
     const int wg = warp >> 2, w4 = warp & 3;
     const int n = P.nchunk;
     const int bh = blockIdx.x / n, j = blockIdx.x % n, b = bh / P.H, h = bh % P.H;
     const bool lo = (lane & 16) == 0;
     const int row = w4 * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
     const uint32_t lane_base = (uint32_t)(w4 * 32);
-    const int blk = w4 >> 1, cc = 4 * (w4 & 1) + (lane & 3), tgl = lane >> 2, tok0 = 32 * blk + 4 * tgl;
 
     // the swizzled tiles need a 1024-byte aligned base; refuse to run otherwise
     if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -351,8 +351,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     const uint32_t tm = s.tmem_base;
     const uint32_t tm_lo = tm, tm_hi = tm + (16u << 16);
 
-    // operand pass: this thread's 4 channels are 8*cc + 4*wg .. +3 (one 8-byte half of a tile chunk)
-    const int ch0 = cc * 8 + 4 * wg;
+    // operand-pass coordinates (see decay_scan8): 4 tokens x 4 channels per thread, a half-warp per tile row
+    const int pblk = warp >> 2, pcc = (lane & 15) >> 1, phf = lane & 1, ptok0 = 8 * warp + 4 * (lane >> 4);
+    const int ch0 = pcc * 8 + 4 * phf;
     float lwc[4];
     bool livec[4];
     if (!PER_TOKEN) {
@@ -397,16 +398,16 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         float c[4][4];
         DecayT<4> D;
         unsigned livebits[4];
-        // per-block totals are exchanged through the first bytes of the A~ tile (unused until the mask pass)
-        float (*btot)[CH] = reinterpret_cast<float (*)[CH]>(s.atil.b);
+        // the warps' decay totals are exchanged through the first bytes of the A~ tile (unused until the mask pass)
+        float *wtot = reinterpret_cast<float *>(s.atil.b);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = tok0 + i;
+            const int t = ptok0 + i;
             const bool valid = j * CH + t < P.T;
             livebits[i] = 0;
             if (PER_TOKEN) {
                 float x[4];
-                unpack4(ld_tile4(s.in[T_W], t, cc, wg), x);
+                unpack4(ld_tile4(s.in[T_W], t, pcc, phf), x);
 #pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     bool live;
@@ -422,26 +423,19 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             }
         }
-        decay_scan(c, lane, D);
-        if (tgl == 7) {
-#pragma unroll
-            for (int ch = 0; ch < 4; ch++) btot[blk][ch0 + ch] = D.e[ch];
-        }
-        __syncthreads();   // block totals visible; every w value has been read, so its slot may take the table
         float other_l2[4], other[4];
+        // (the barrier inside: every w value has been read, so its slot may take the table)
+        decay_scan8(c, warp, lane, wtot, D, other_l2, [] { __syncthreads(); });
 #pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-            other_l2[ch] = btot[blk ^ 1][ch0 + ch];
-            other[ch] = exp2f(other_l2[ch]);
-        }
+        for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = tok0 + i;
+            const int t = ptok0 + i;
             float cv[4];      // cumulative log2-decay counted from the chunk start; its lowest mantissa
                               // bit is replaced by the "decay above the floor" flag of the token
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                const float cabs = blk ? c[i][ch] + other_l2[ch] : c[i][ch];
+                const float cabs = pblk ? c[i][ch] + other_l2[ch] : c[i][ch];
                 cv[ch] = __uint_as_float((__float_as_uint(cabs) & ~1u) | ((livebits[i] >> ch) & 1u));
             }
             *ctab_ptr4(s.in[T_W], s.ctab_hi, t, ch0 >> 2) = make_float4(cv[0], cv[1], cv[2], cv[3]);
@@ -455,9 +449,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int t = tok0 + i;
+            const int t = ptok0 + i;
             float r[4], rt[4], xx[4];
-            unpack4(ld_tile4(s.in[T_R], t, cc, wg), r);
+            unpack4(ld_tile4(s.in[T_R], t, pcc, phf), r);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
                 rt[ch] = r[ch] * fa[ch];
@@ -465,8 +459,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 fa[ch] *= D.w[i][ch];
                 fb[ch] *= D.w[i][ch];
             }
-            st_tile4(s.rt, t, cc, wg, pack4(rt));
-            if (blk) st_tile4(s.x, t, cc, wg, pack4(xx));
+            st_tile4(s.rt, t, pcc, phf, pack4(rt));
+            if (pblk) st_tile4(s.x, t, pcc, phf, pack4(xx));
         }
         // k-side operands, walking backward:  fa = 2^{m - c};  fb = 2^{e - c}
         //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
@@ -477,20 +471,20 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
 #pragma unroll
         for (int i = 3; i >= 0; i--) {
-            const int t = tok0 + i;
+            const int t = ptok0 + i;
             float k[4], kt[4], kh[4], xx[4];
-            unpack4(ld_tile4(s.in[T_K], t, cc, wg), k);
+            unpack4(ld_tile4(s.in[T_K], t, pcc, phf), k);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
                 kt[ch] = k[ch] * fa[ch];
                 xx[ch] = k[ch] * fb[ch];
-                kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
+                kh[ch] = pblk ? xx[ch] : xx[ch] * other[ch];
                 fa[ch] *= D.w[i][ch];
                 fb[ch] *= D.w[i][ch];
             }
-            st_tile4(s.kt, t, cc, wg, pack4(kt));
-            if (!blk) st_tile4(s.x, t, cc, wg, pack4(xx));
-            st_tile4(s.khat, t, cc, wg, pack4(kh));
+            st_tile4(s.kt, t, pcc, phf, pack4(kt));
+            if (!pblk) st_tile4(s.x, t, pcc, phf, pack4(xx));
+            st_tile4(s.khat, t, pcc, phf, pack4(kh));
         }
     }
     fence_async_smem();
