@@ -39,9 +39,9 @@ METRIC = "wkv_fwd_bwd_tokens_per_s"
 # bytes each tensor element is touched, once: fwd r,k,v,w -> y ; bwd r,k,v,w,gy -> gr,gk,gv,gw
 FWD_ELEMS, BWD_ELEMS = 5, 9
 # DRAM bytes per head-token of the backward launch group, from the ncu captures of the B=1,
-# T=4096, H=64 case: (134.3 + 19.0 MB dS scan) + (236.0 + 101.4 MB per-chunk kernel) over
+# T=4096, H=64 case: (102.3 + 15.1 MB dS scan) + (236.0 + 101.9 MB per-chunk kernel) over
 # 64 * 4096 head-tokens.  Traffic grows in proportion to head-tokens.
-NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN = (134.26e6 + 19.03e6 + 236.03e6 + 101.43e6) / (64 * 4096)
+NCU_BWD_DRAM_BYTES_PER_HEAD_TOKEN = (102.27e6 + 15.10e6 + 236.01e6 + 101.88e6) / (64 * 4096)
 
 
 def peaks():
@@ -154,7 +154,7 @@ class Runner:
                 e1.record()
                 self.fwd_events.append((e0, e1))
             states.append(s)
-            self.launches += 1
+            self.launches += 1          # k_chunk_fwd
         gs = None
         out = None
         for (t0, t1), s_in, ck in reversed(list(zip(self.bounds, states[:-1], ckpts))):
@@ -168,7 +168,7 @@ class Runner:
                 e1.record()
                 self.bwd_events.append((e0, e1))
             gs = out[5]
-            self.launches += 1
+            self.launches += 3          # k_chunk_dscan, k_chunk_bwd, k_reduce_partials
         return out
 
 
@@ -191,6 +191,8 @@ def run_ours(args):
     wl = dict(WORKLOAD)
     if args.small:
         wl.update(name=wl["name"] + "_small", B=1, T=4096)
+    if args.medium:
+        wl.update(name=wl["name"] + "_medium", T=4096)
     H_total = wl["H"]
     if args.scaling == "strong" and world > 1:
         from rwkv_infctx_trainer_b200.sharding import shard_units
@@ -527,6 +529,9 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
                          "still larger than L2) instead of the benchmark workload")
+    ap.add_argument("--medium", action="store_true",
+                    help="profiling aid: the benchmark's batch and heads but a single 4096-token segment "
+                         "(under 2 GB on the device) -- the grid sizes of the benchmark's launches")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: no end-to-end leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline leg")
     args = ap.parse_args()

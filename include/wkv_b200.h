@@ -154,9 +154,10 @@ typedef struct wkv_args {
     /* scratch */
     void *workspace;
     size_t workspace_bytes;
-    /* optional hand-over from forward to backward (chunked path only): the state at the
-     * start of every 64-token chunk, bf16, wkv56_state_ckpt_bytes() bytes.  Forward fills
-     * it when non-NULL; backward given the same buffer skips recomputing those states.
+    /* optional hand-over from forward to backward (chunked path only), wkv56_state_ckpt_bytes()
+     * bytes: the state at the start of every 64-token chunk (bf16), r scaled by the decay
+     * accumulated since the chunk start (bf16 [B,T,C]) and the decay of every whole chunk.
+     * Forward fills it when non-NULL; backward given the same buffer skips recomputing it.
      * The trainer's activation checkpointing re-runs the op's forward anyway
      * (RWKV-v6/src/model.py:660-662); this is the op-level equivalent. */
     void *state_ckpt;

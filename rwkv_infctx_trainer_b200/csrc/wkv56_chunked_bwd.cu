@@ -1,26 +1,25 @@
 // Chunked tensor-core backward of the v5/v6 WKV recurrence (bf16 I/O, fp32 state).
 //
 // Three kernels per BPTT segment:
-//   1. the forward kernel in state-only mode writes S_j, the state at the start of
-//      every 64-token chunk (bf16);
-//   2. k_chunk_dscan runs the reverse recurrence  D_j = diag(e^{c_63}) D_{j+1} +
-//      (r e^{cp})^T gy  with D in tensor memory, writes every D_{j+1} (bf16) and
-//      the state gradient D_0;
+//   1. the forward kernel has left (or, in a state-only mode, now writes) S_j, the state at
+//      the start of every 64-token chunk (bf16), the tiles r e^{cp} and the chunk decays d_j;
+//   2. k_chunk_dscan runs the reverse recurrence  D_j = d_j D_{j+1} + (r e^{cp})^T gy  with D
+//      in registers and only the chunk's own product on the tensor core, writes every D_{j+1}
+//      (bf16), E_j = rowsum(S_j * D_j) and the state gradient D_0;
 //   3. k_chunk_bwd handles every (batch, head, chunk) independently from S_j and
 //      D_{j+1}: recomputes the masked scores A, P = gy v^T, and from them
 //         gv = A^T gy + khat D
-//         gr = fr*(P~ Kt) + g*(P~ X) + e^{cp}*(gy S^T) + p_tt u k
-//         gk = fk*(P~^T Rt) + g*(P~^T X) + e^{c_63-c}*(v D^T) + p_tt u r
-//      (P~ = strictly lower part of P; Rt, Kt, X, khat the scaled operands of the
-//      forward kernel) with every product on tcgen05.mma, accumulators laid out
-//      [channel, token] so that one thread owns one channel over all 64 tokens.
+//         gr = fr*(P~d Kt) + g*(P~x X) + e^{cp}*(gy S^T) + p_tt u k
+//         gk = fk*(P~d^T Rt) + g*(P~x^T X) + e^{c_63-c}*(v D^T) + p_tt u r
+//      (P~d / P~x = same-block / cross-block part of the strictly lower P; Rt, Kt, X, khat the
+//      scaled operands of the forward kernel) with every product on tcgen05.mma, accumulators
+//      laid out [token, channel] so that the epilogue works on whole 16-byte tile chunks.
 //
 // Decay gradient.  dL/d(log w_t)[k] = w_t sum_v S_t[k,v] D_{t+1}[k,v] expands into
-//   d sum_v S_j D_{j+1}  +  sum_{t'>t} qrS_t'  +  sum_{s<t} qkD_s  +  C_t,
-//   C_{t+1} = C_t + qkI_t - qrI_{t+1},
+//   E_j + sum_{t'<=t} (a_t' + b_t') - b_t,     a = -(qrS + qrI),   b = qkD + qkI,
 // where qrS/qkD are the state parts of r*gr and k*gk and qrI/qkI their intra-chunk
-// parts.  C is a difference of large sums; it is exact only because qrI and qkI
-// are built from the SAME bf16-rounded factors (Rt * (P~ Kt) and Kt * (P~^T Rt)),
+// parts.  The sum is a difference of large terms; it is exact only because qrI and qkI
+// are built from the SAME bf16-rounded factors (Rt * (P~d Kt) and Kt * (P~d^T Rt)),
 // so the common terms cancel to fp32 rounding instead of to bf16 rounding.
 //
 // Math reference: RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:70-293 (what the
