@@ -134,14 +134,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             int pending = -1;   // last chunk whose products may still be running
             for (int c = 0; c < n; c++) {
                 const int st = c & 1;
-                const bool fstamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && c == n / 2 + 1;
-                if (fstamp) P.timeline[8] = clock64();
                 const uint64_t d_r = make_desc(smem_u32(&s.in[st][0])), d_k = make_desc(smem_u32(&s.in[st][1])),
                                d_v = make_desc(smem_u32(&s.in[st][2])), d_rh = make_desc(smem_u32(&s.in[st][3])),
                                d_kh = make_desc(smem_u32(&s.khat[st]));
                 if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
                 tc_fence_after();
-                if (fstamp) P.timeline[9] = clock64();
                 if (full) {
                     // scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T
 #pragma unroll
@@ -161,7 +158,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                                id_mm32, k > 0);
                 mma_commit(&s.u_bar[c & 1]);
                 pending = c;
-                if (fstamp) P.timeline[10] = clock64();
                 // r e^{cp} of this chunk goes out for the backward pass
                 if (P.dchunk) {
                     tma_store_3d(&map_rh, &s.in[st][3], h * 64, c * CH, b);
@@ -170,7 +166,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 if (full) {
                     if (!mbar_wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag)) { fail = 1; break; }
                     tc_fence_after();
-                    if (fstamp) P.timeline[11] = clock64();
                     // y = Atil V + Rhat Sbf  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
 #pragma unroll
                     for (int hf = 0; hf < 2; hf++) {
@@ -183,7 +178,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                             mma_ss(d, d_rh + k * KSTEP, d_sbf + k * MSTEP + (hf ? HI : 0), id_km32, true);
                     }
                     mma_commit(&s.y_bar);
-                    if (fstamp) P.timeline[12] = clock64();
                 }
                 // the stage is free for chunk c+2 when every product of chunk c is done (the last
                 // commit covers all earlier ones of this thread) and the store has read its tile
@@ -195,7 +189,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     tma_store_wait_read();
                     issue_load(c + 2);
                     issued = c + 2;
-                    if (fstamp) P.timeline[13] = clock64();
                 }
             }
             if (fail) {
@@ -241,7 +234,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
         // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
         auto prep = [&](int j) {
-            const bool pst = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2 + 1;
             Tile *in = s.in[j & 1];
             Tile &khat = s.khat[j & 1];
             float c[4][4];
@@ -265,9 +257,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             }
             float other_l2[4];
-            if (pst) P.timeline[14] = clock64();
             decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [] { compute_sync(); });
-            if (pst) P.timeline[15] = clock64();
+            {
+                // Debug stamp "decay scan done".  The clock read is also a scheduling boundary: without
+                // it the loads of the r-side stage are hoisted above the scan and, under the 96-register
+                // cap of two 288-thread CTAs per SM, the pass spills inside the serial loop (+30 % time).
+                const long long t_scan = clock64();
+                if (P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2 + 1) P.timeline[5] = t_scan;
+            }
             float other[4];          // 2^{total of the other block}
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
@@ -329,7 +326,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     st_tile4(in[3], t, cc, hf, pack4(rh));
                 }
             }
-            if (pst) P.timeline[16] = clock64();
             // k-side operands, walking backward:
             //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
             //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
@@ -386,9 +382,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             // (P) operands of chunk j+1
             if (j + 1 < n) {
                 if (!cwait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) fail = 1;
-                if (stamp) P.timeline[5] = clock64();
                 prep(j + 1);
-                if (stamp) P.timeline[6] = clock64();
                 fence_async_smem();
                 compute_sync();
                 if (tid == 0) mbar_arrive(&s.ops_bar[(j + 1) & 1]);

@@ -327,7 +327,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         return;
     }
     const bool stamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && tid == 0;
-    const bool stamp2 = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && (tid & 127) == 0;
     if (stamp) P.timeline[0] = clock64();
     if (tid == 0) {
         mbar_init(&s.load_bar, 1);
@@ -742,7 +741,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
     };
     if (wg == 0) side_pass(std::true_type{}); else side_pass(std::false_type{});
-    if (stamp2) P.timeline[9 + 5 * wg] = clock64();
     if (wg == 0) {
         // gv: accumulator [s, v]
         if (!abort2 && !mbar_wait(&s.bar_gv, 0)) fail = 1;
@@ -754,9 +752,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
         for (int c8 = 0; c8 < 4; c8++) st_tile(o_gv, t, 4 * hh + c8, pack8(gv + 8 * c8));
     }
-    if (stamp2) P.timeline[10 + 5 * wg] = clock64();
     __syncthreads();
-    if (stamp2) P.timeline[11 + 5 * wg] = clock64();
     // the token scan of z = a + b for this thread's 16 channels: 32*hh + 16*wg .. +15
     float bsub[16];
     {
@@ -787,7 +783,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     make_float4(keep[4 * c4], keep[4 * c4 + 1], keep[4 * c4 + 2], keep[4 * c4 + 3]);
         }
     }
-    if (stamp2) P.timeline[12 + 5 * wg] = clock64();
     __syncthreads();
     {
         const int kb0 = 32 * hh + 16 * wg;                 // first of the 16 channels
@@ -835,7 +830,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             }
         }
     }
-    if (stamp2) P.timeline[13 + 5 * wg] = clock64();
     fence_async_smem();
     tc_fence_before();
     const int abort3 = __syncthreads_or(fail) | abort2;
