@@ -120,6 +120,12 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, ui
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// pull the tile a later 3-D tiled load will fetch into L2
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void *tmap, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(c0), "r"(c1),
+                 "r"(c2)
+                 : "memory");
+}
 // untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16)
 __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

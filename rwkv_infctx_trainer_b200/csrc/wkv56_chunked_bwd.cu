@@ -243,6 +243,7 @@ static_assert(sizeof(BwdSmem) <= 115712, "two CTAs per SM need <= 113 KiB each")
 
 struct BwdParams {
     int T, H, nchunk, w_kind;
+    int prefetch_dist;   // CTAs resident on the device at once: that far ahead tiles are pulled into L2
     const __nv_bfloat16 *u;
     const float *wvec;
     const float *e0;  // [B*H, nchunk+1, 64]: sum_v S_j[k,v] D_j[k,v] at chunk boundary j (from the dS scan)
@@ -341,6 +342,20 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         tma_load_3d(&s.in[T_GY], &map_gy, &s.load_bar, h * 64, j * CH, b);
         tma_load_3d(&s.in[T_S], &map_s, &s.load_bar, 0, 0, bh * (n + 1) + j);
         tma_load_3d(&s.in[T_D], &map_d, &s.load_bar, 0, 0, bh * (n + 1) + j + 1);
+    }
+    if (tid == 32) {
+        // the CTA that will take this one's place on the SM finds its tiles in L2
+        const int nb = blockIdx.x + P.prefetch_dist;
+        if (nb < (int)gridDim.x) {
+            const int bh2 = nb / n, j2 = nb % n, b2 = bh2 / P.H, h2 = bh2 % P.H;
+            tma_prefetch_l2_3d(&map_r, h2 * 64, j2 * CH, b2);
+            tma_prefetch_l2_3d(&map_k, h2 * 64, j2 * CH, b2);
+            tma_prefetch_l2_3d(&map_v, h2 * 64, j2 * CH, b2);
+            if (PER_TOKEN) tma_prefetch_l2_3d(&map_w, h2 * 64, j2 * CH, b2);
+            tma_prefetch_l2_3d(&map_gy, h2 * 64, j2 * CH, b2);
+            tma_prefetch_l2_3d(&map_s, 0, 0, bh2 * (n + 1) + j2);
+            tma_prefetch_l2_3d(&map_d, 0, 0, bh2 * (n + 1) + j2 + 1);
+        }
     }
     if (warp == 0) { tmem_alloc(&s.tmem_base, BWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
@@ -591,36 +606,17 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
     // ------------------------------------------------- phase 2: token-major accumulators
     // every accumulator is [token, 32 channels]: channels 0..31 in the lo lanes, 32..63 in the hi lanes
-    // gv is needed last and goes to a barrier of its own.  (A commit covers everything its thread has
-    // issued before, so the gv warps arrive on the gradient barrier first.)
+    // gv is needed last: it goes to a barrier of its own and is issued behind the gradient products
+    // (the warps that issue it first issue their share of the gradients and commit those).
     if (lane == 0) {
         tc_fence_after();
         const uint32_t id_kn = make_idesc(64, 32, false, true), id_nn = make_idesc(64, 32, true, true);
         const int hf = warp & 1;
         const uint32_t tmh = hf ? tm_hi : tm_lo;
         const uint64_t boff = hf ? 4 : 0;     // +64 bytes: the upper 32 of the 64 contiguous elements
-        if (warp < 2) mma_commit(&s.bar_grad);
         if (abort2) {
-            // nothing is issued
-        } else if (warp < 2) {
-            // gv[s, v] = sum_t A~[t,s] gy[t,v] + sum_k khat[s,k] D[k,v]
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tmh + C_GV, desc_mnmajor(&s.atil, 0, k), desc_mnmajor(&s.in[T_GY], 0, k) + boff, id_nn, k > 0);
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tmh + C_GV, desc_kmajor(&s.khat, 0, k), desc_mnmajor(&s.in[T_D], 0, k) + boff, id_kn, true);
-        } else if (warp < 4) {
-            // gr intra, same block: G1r[t,k] = sum_s P~d[t,s] Kt[s,k]
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tmh + C_G1R, desc_kmajor(&s.ptil, 0, k), desc_mnmajor(&s.kt, 0, k) + boff, id_kn, k > 0);
-        } else if (warp < 6) {
-            // gk intra, same block: G1k[s,k] = sum_t P~d[t,s] Rt[t,k]
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                mma_ss(tmh + C_G1K, desc_mnmajor(&s.ptil, 0, k), desc_mnmajor(&s.rt, 0, k) + boff, id_nn, k > 0);
-        } else if (warp == 6) {
+            mma_commit(&s.bar_grad);          // nothing is issued
+        } else if (warp == 0) {
             // gr intra, across blocks: G2r[t >= 32, k] = sum_{s<32} P~x[t,s] X[s,k]   (rows t < 32 are not read)
 #pragma unroll
             for (int hq = 0; hq < 2; hq++)
@@ -628,7 +624,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int k = 0; k < 2; k++)
                     mma_ss((hq ? tm_hi : tm_lo) + C_G2R, desc_kmajor(&s.in[T_V], 0, k),
                            desc_mnmajor(&s.x, 0, k) + (hq ? 4 : 0), id_kn, k > 0);
-        } else {
+            mma_commit(&s.bar_grad);
+        } else if (warp == 1) {
             // gk intra, across blocks: G2k[s < 32, k] = sum_{t>=32} P~x[t,s] X[t,k]   (rows s >= 32 are not read)
 #pragma unroll
             for (int hq = 0; hq < 2; hq++)
@@ -636,8 +633,31 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int k = 0; k < 2; k++)
                     mma_ss((hq ? tm_hi : tm_lo) + C_G2K, desc_mnmajor(&s.in[T_V], 32, k),
                            desc_mnmajor(&s.x, 32, k) + (hq ? 4 : 0), id_nn, k > 0);
+            mma_commit(&s.bar_grad);
+        } else if (warp < 4) {
+            // gr intra, same block: G1r[t,k] = sum_s P~d[t,s] Kt[s,k]
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tmh + C_G1R, desc_kmajor(&s.ptil, 0, k), desc_mnmajor(&s.kt, 0, k) + boff, id_kn, k > 0);
+            mma_commit(&s.bar_grad);
+        } else if (warp < 6) {
+            // gk intra, same block: G1k[s,k] = sum_t P~d[t,s] Rt[t,k]
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tmh + C_G1K, desc_mnmajor(&s.ptil, 0, k), desc_mnmajor(&s.rt, 0, k) + boff, id_nn, k > 0);
+            mma_commit(&s.bar_grad);
+        } else {
+            mma_commit(&s.bar_grad);
         }
-        if (warp >= 2) mma_commit(&s.bar_grad);
+        if (!abort2 && warp < 2) {
+            // gv[s, v] = sum_t A~[t,s] gy[t,v] + sum_k khat[s,k] D[k,v]
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tmh + C_GV, desc_mnmajor(&s.atil, 0, k), desc_mnmajor(&s.in[T_GY], 0, k) + boff, id_nn, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                mma_ss(tmh + C_GV, desc_kmajor(&s.khat, 0, k), desc_mnmajor(&s.in[T_D], 0, k) + boff, id_kn, true);
+        }
         mma_commit(&s.bar_gv);
     }
 
@@ -941,6 +961,13 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
     {
         BwdParams p;
         p.T = T; p.H = H; p.nchunk = n; p.w_kind = a->w_kind;
+        {
+            int dev = 0, sms = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+                return WKV_ERR_LAUNCH;
+            p.prefetch_dist = 2 * sms;      // two CTAs of this kernel fit on an SM
+        }
         p.u = (const __nv_bfloat16 *)a->u;
         p.wvec = per_token_w ? nullptr : (const float *)a->w;
         p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
