@@ -606,8 +606,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
     // ------------------------------------------------- phase 2: token-major accumulators
     // every accumulator is [token, 32 channels]: channels 0..31 in the lo lanes, 32..63 in the hi lanes
-    // gv is needed last: it goes to a barrier of its own and is issued behind the gradient products
-    // (the warps that issue it first issue their share of the gradients and commit those).
+    // gv is needed last: it goes to a barrier of its own, from the two warps that have no gradient
+    // product to issue (so that no warp enters the epilogue later than the others).
     if (lane == 0) {
         tc_fence_after();
         const uint32_t id_kn = make_idesc(64, 32, false, true), id_nn = make_idesc(64, 32, true, true);
@@ -649,7 +649,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         } else {
             mma_commit(&s.bar_grad);
         }
-        if (!abort2 && warp < 2) {
+        if (!abort2 && warp >= 6) {
             // gv[s, v] = sum_t A~[t,s] gy[t,v] + sum_k khat[s,k] D[k,v]
 #pragma unroll
             for (int k = 0; k < 4; k++)
