@@ -38,7 +38,7 @@ using namespace chunked;
 // ----------------------------------------------------------------------------
 // dS scan
 
-constexpr int DS_STAGES = 3;
+constexpr int DS_STAGES = 3;   // (four stages measured no faster: the kernel is HBM bound)
 
 struct DscanSmem {
     Tile in[DS_STAGES][3];              // r e^{cp} and gy of the step's chunk; S at the chunk's end
@@ -64,7 +64,7 @@ struct DscanParams {
 // segment, step i = 0..n-1 handling chunk j = n-1-i.  The scaled r tiles and the chunk decays
 // d_j come from the forward kernel, so a step has no operand pass.
 //
-// Five warps.  Warp 4 (one lane) feeds the machine: TMA loads three steps ahead, and for every
+// Five warps.  Warp 4 (one lane) feeds the machine: TMA loads DS_STAGES steps ahead, and for every
 // step the product U_j = (r e^{cp})^T gy into one of two tensor-memory buffers -- U_j does not
 // depend on the carried gradient, so it is ready before the scan gets there.  Warps 0..3 carry
 // D in registers (thread = key row, 32 value columns) and run the serial chain,
@@ -129,11 +129,11 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
                     mma_commit(&s.mma_bar[i & 1]);
                     mma_issued = i;
                 }
-                // the stage of step i-1 goes to step i+2 as soon as the scan warps are done with it
-                if (i >= 1 && i + 2 <= n) {
+                // the stage of step i-1 goes to step i-1+DS_STAGES as soon as the scan warps are done with it
+                if (i >= 1 && i + DS_STAGES - 1 <= n) {
                     if (!mbar_wait(&s.stage_free[(i - 1) % DS_STAGES], load_parity(i - 1))) { fail = 1; break; }
-                    issue_load(i + 2);
-                    issued = i + 2;
+                    issue_load(i + DS_STAGES - 1);
+                    issued = i + DS_STAGES - 1;
                 }
             }
             if (fail) {
