@@ -51,6 +51,7 @@ struct FwdSmem {
     uint64_t y_bar;        // tensor core: y of a chunk
     uint32_t tmem_base;
     int abort_flag;        // set by any thread whose bounded wait ran out; ends every other wait
+    int mild_flag[2];      // compute warps -> feeder, by chunk parity: the chunk is mild (see decay_scan8)
 };
 
 struct FwdParams {
@@ -77,6 +78,13 @@ struct FwdParams {
 enum { COL_U = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
 constexpr int FWD_COMPUTE_THREADS = 256, FWD_THREADS = 288;
 
+// barrier of the 256 compute threads that also ORs a predicate over them
+__device__ __forceinline__ bool compute_sync_or(bool pred) {
+    uint32_t any;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, 256, q;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(any) : "r"((uint32_t)pred) : "memory");
+    return any != 0;
+}
 // barrier of the 256 compute threads
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -140,13 +148,19 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
                 tc_fence_after();
                 if (full) {
-                    // scores: A1 = Rt Kt^T (same-block halves), A2 = X X[0:32]^T
+                    // scores: A1 = Rt Kt^T (column halves), A2 = X X[0:32]^T.  In a mild chunk Rt and Kt are
+                    // scaled around one point, A1's rows 32..63 of columns 0..31 ARE the cross-block scores:
+                    // that half goes where A2 would have gone and A2 is not formed.
+                    const bool mild = *reinterpret_cast<volatile int *>(&s.mild_flag[c & 1]) != 0;
+                    const uint32_t a1a = tm + (mild ? COL_A2 : COL_A1A);
 #pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss(tm + COL_A1A, d_r + k * KSTEP, d_k + k * KSTEP, id32, k > 0);
+                    for (int k = 0; k < 4; k++) mma_ss(a1a, d_r + k * KSTEP, d_k + k * KSTEP, id32, k > 0);
 #pragma unroll
                     for (int k = 0; k < 4; k++) mma_ss(tm_hi + COL_A2, d_r + k * KSTEP, d_k + ROW32 + k * KSTEP, id32, k > 0);
+                    if (!mild) {
 #pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss(tm + COL_A2, d_x + k * KSTEP, d_x + k * KSTEP, id32, k > 0);
+                        for (int k = 0; k < 4; k++) mma_ss(tm + COL_A2, d_x + k * KSTEP, d_x + k * KSTEP, id32, k > 0);
+                    }
                     mma_commit(&s.score_bar);
                 }
                 // U = Khat^T V  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
@@ -233,7 +247,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
         // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
         // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
-        auto prep = [&](int j) {
+        auto prep = [&](int j) -> bool {
             Tile *in = s.in[j & 1];
             Tile &khat = s.khat[j & 1];
             float c[4][4];
@@ -257,7 +271,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
             }
             float other_l2[4];
-            decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [] { compute_sync(); });
+            const bool mild = decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [](bool p) { return compute_sync_or(p); });
+            if (tid == 0) s.mild_flag[j & 1] = mild;
             {
                 // Debug stamp "decay scan done".  The clock read is also a scheduling boundary: without
                 // it the loads of the r-side stage are hoisted above the scan and, under the 96-register
@@ -279,10 +294,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             // r-side operands, walking forward over the thread's tokens:
             //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
             //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
-            float fa[4], fb[4];
+            float fa[4], fb[4], ref[4];     // ref: the reference point of the score factors (block-local)
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+                ref[ch] = mild ? (blk ? 0.f : D.e[ch]) : D.m[ch];
+                fa[ch] = exp2f(D.cp0[ch] - ref[ch]);
                 fb[ch] = exp2f(D.cp0[ch]);
             }
             if (full) {
@@ -304,7 +320,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     }
                     st_tile4(in[0], t, cc, hf, pack4(rt));
                     st_tile4(in[3], t, cc, hf, pack4(rh));
-                    if (blk) st_tile4(s.x, t, cc, hf, pack4(xx));
+                    if (blk && !mild) st_tile4(s.x, t, cc, hf, pack4(xx));
                     // groups of four lanes pool their channels; four partials per token remain
                     dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
                     dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
@@ -331,7 +347,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+                fa[ch] = exp2f(ref[ch] - D.c3[ch]);
                 fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
             }
 #pragma unroll
@@ -349,10 +365,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 }
                 if (full) {
                     st_tile4(in[1], t, cc, hf, pack4(kt));
-                    if (!blk) st_tile4(s.x, t, cc, hf, pack4(xx));
+                    if (!blk && !mild) st_tile4(s.x, t, cc, hf, pack4(xx));
                 }
                 st_tile4(khat, t, cc, hf, pack4(kh));
             }
+            return mild;
         };
         // a wait of a compute thread; running out of patience ends everybody else's waits too
         auto cwait = [&](uint64_t *bar, uint32_t parity) {
@@ -376,13 +393,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
         // Iteration j works on three chunks at once: operands of chunk j+1, y of chunk j, and the
         // state / masked scores that the y product of chunk j+1 needs.  j = -1 is the prologue.
+        bool mild_next = false;      // chunk j+1 is mild
         for (int j = -1; j < n; j++) {
             const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
             if (stamp) P.timeline[0] = clock64();
             // (P) operands of chunk j+1
             if (j + 1 < n) {
                 if (!cwait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) fail = 1;
-                prep(j + 1);
+                mild_next = prep(j + 1);
                 fence_async_smem();
                 compute_sync();
                 if (tid == 0) mbar_arrive(&s.ops_bar[(j + 1) & 1]);
@@ -424,8 +442,8 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const int t = row;
                 float a[16];
                 // rows 0..31 (w4 0,1): A1a for the lo half, nothing kept for the hi half;
-                // rows 32..63 (w4 2,3): A2 (lo) and A1b (hi) share their columns
-                tmem_ld16(tmem_addr(tm, lane_base, (w4 < 2 ? COL_A1A : COL_A2) + 16 * wg), a);
+                // rows 32..63 (w4 2,3): A2 (lo) and A1b (hi) share their columns; in a mild chunk A1a sits there too
+                tmem_ld16(tmem_addr(tm, lane_base, (w4 < 2 && !mild_next ? COL_A1A : COL_A2) + 16 * wg), a);
                 tmem_ld_wait();
                 const float diag = (s.dpart[0][t] + s.dpart[1][t]) + (s.dpart[2][t] + s.dpart[3][t]);
                 // entries left of local column `lim` are kept, column lim is the diagonal

@@ -114,12 +114,20 @@ __device__ __forceinline__ void decay_scan(float (&l2)[4][NCH], int lane, DecayT
 //
 // In: l2[i][ch] per-token log2-decay.  Out: l2 holds the block-local inclusive sums c; D as in
 // decay_scan; other_l2 = log2-decay total of the other block.  The totals of the eight warps go
-// through `wtot` ([8][CH] floats of shared memory); `sync` is the barrier of the 256 threads.
+// through `wtot` ([8][CH] floats of shared memory); `sync(pred)` is the barrier of the 256 threads,
+// returning the OR of `pred` over them.
+//
+// Returns true when the chunk is "mild": no 8 consecutive tokens decay by more than 2^-30 in any
+// channel, so that the whole chunk can be factored around ONE reference point, the end of block 0
+// (both halves then stay within 2^+-120), and the separate treatment of the pairs across the two
+// blocks is not needed.
+constexpr float MILD_L2_PER_8 = -30.f;
 template <class Sync>
-__device__ __forceinline__ void decay_scan8(float (&l2)[4][4], int warp, int lane, float *wtot, DecayT<4> &D,
+__device__ __forceinline__ bool decay_scan8(float (&l2)[4][4], int warp, int lane, float *wtot, DecayT<4> &D,
                                             float (&other_l2)[4], Sync sync) {
     const int r = lane >> 4, ch0 = (lane & 15) * 4, blk = warp >> 2, wb = warp & 3;
     float tot[4], first[4];
+    bool steep = false;
 #pragma unroll
     for (int ch = 0; ch < 4; ch++) {
 #pragma unroll
@@ -129,13 +137,14 @@ __device__ __forceinline__ void decay_scan8(float (&l2)[4][4], int warp, int lan
         for (int i = 1; i < 4; i++) l2[i][ch] += l2[i - 1][ch];
         const float o = __shfl_xor_sync(0xffffffffu, l2[3][ch], 16);
         tot[ch] = l2[3][ch] + o;
+        steep |= tot[ch] < MILD_L2_PER_8;
         if (r) {
 #pragma unroll
             for (int i = 0; i < 4; i++) l2[i][ch] += o;
         }
     }
     if (r) *reinterpret_cast<float4 *>(wtot + warp * CH + ch0) = make_float4(tot[0], tot[1], tot[2], tot[3]);
-    sync();
+    const bool mild = !sync(steep);
     const float *own = wtot + 4 * blk * CH + ch0, *oth = wtot + 4 * (blk ^ 1) * CH + ch0;
     float base[4] = {0.f, 0.f, 0.f, 0.f}, m[4], e[4];
 #pragma unroll
@@ -160,6 +169,7 @@ __device__ __forceinline__ void decay_scan8(float (&l2)[4][4], int warp, int lan
         D.m[ch] = m[ch];
         D.e[ch] = e[ch];
     }
+    return mild;
 }
 
 // 8-byte halves of a 16-byte tile chunk (4 bf16)

@@ -407,6 +407,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     }
 
     // ---------------------------------------------------------------- operand pass
+    // mild chunk (see decay_scan8): one reference point, the end of block 0, for all 64 tokens; the
+    // cross-block operands x / P~x and the products A2, G2r, G2k are then not needed
+    bool mild = false;
     {
         float c[4][4];
         DecayT<4> D;
@@ -438,7 +441,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
         float other_l2[4], other[4];
         // (the barrier inside: every w value has been read, so its slot may take the table)
-        decay_scan8(c, warp, lane, wtot, D, other_l2, [] { __syncthreads(); });
+        mild = decay_scan8(c, warp, lane, wtot, D, other_l2, [](bool p) { return __syncthreads_or(p) != 0; });
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
 #pragma unroll
@@ -454,10 +457,11 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             *ctab_ptr4(s.in[T_W], s.ctab_hi, t, ch0 >> 2) = make_float4(cv[0], cv[1], cv[2], cv[3]);
         }
         // r-side operands, walking forward:  fa = 2^{cp - m};  block 1 also x = r 2^{cp}  (block-local cp)
-        float fa[4], fb[4];
+        float fa[4], fb[4], ref[4];      // ref: the reference point of the same-block factors (block-local)
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) {
-            fa[ch] = exp2f(D.cp0[ch] - D.m[ch]);
+            ref[ch] = mild ? (pblk ? 0.f : D.e[ch]) : D.m[ch];
+            fa[ch] = exp2f(D.cp0[ch] - ref[ch]);
             fb[ch] = exp2f(D.cp0[ch]);
         }
 #pragma unroll
@@ -468,18 +472,23 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
                 rt[ch] = r[ch] * fa[ch];
-                xx[ch] = r[ch] * fb[ch];
                 fa[ch] *= D.w[i][ch];
-                fb[ch] *= D.w[i][ch];
             }
             st_tile4(s.rt, t, pcc, phf, pack4(rt));
-            if (pblk) st_tile4(s.x, t, pcc, phf, pack4(xx));
+            if (pblk && !mild) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    xx[ch] = r[ch] * fb[ch];
+                    fb[ch] *= D.w[i][ch];
+                }
+                st_tile4(s.x, t, pcc, phf, pack4(xx));
+            }
         }
         // k-side operands, walking backward:  fa = 2^{m - c};  fb = 2^{e - c}
         //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) {
-            fa[ch] = exp2f(D.m[ch] - D.c3[ch]);
+            fa[ch] = exp2f(ref[ch] - D.c3[ch]);
             fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
         }
 #pragma unroll
@@ -496,7 +505,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 fb[ch] *= D.w[i][ch];
             }
             st_tile4(s.kt, t, pcc, phf, pack4(kt));
-            if (!pblk) st_tile4(s.x, t, pcc, phf, pack4(xx));
+            if (!pblk && !mild) st_tile4(s.x, t, pcc, phf, pack4(xx));
             st_tile4(s.khat, t, pcc, phf, pack4(kh));
         }
     }
@@ -514,7 +523,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
                 for (int k = 0; k < 4; k++)
                     mma_ss(tm_lo + C_A1, desc_kmajor(&s.rt, 0, k), desc_kmajor(&s.kt, 0, k), id64, k > 0);
-            } else if (warp == 1) {
+            } else if (warp == 1 && !mild) {
                 const uint32_t id32 = make_idesc(64, 32, false, false);
 #pragma unroll
                 for (int k = 0; k < 4; k++)
@@ -556,7 +565,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0), a);
             tmem_ld16(tmem_addr(tm, lane_base, C_A1 + col0 + 16), a + 16);
         }
-        if (cross_warp) {           // rows 32..63, columns 0..31: every entry kept; A~ takes the cross-block scores
+        if (cross_warp && mild) {   // rows 32..63, columns 0..31: every entry kept; A1 holds the cross-block scores too
+            tmem_ld_wait();
+        } else if (cross_warp) {    // ... A~ takes the cross-block scores from their own product
             float a2[32];
             tmem_ld16(tmem_addr(tm, lane_base, C_A2), a2);
             tmem_ld16(tmem_addr(tm, lane_base, C_A2 + 16), a2 + 16);
@@ -591,10 +602,10 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 32; q++) a[q] = 0.f;
         }
-        Tile &dst = lo ? s.atil : (cross_warp ? s.in[T_V] : s.ptil);
+        Tile &dst = lo ? s.atil : (cross_warp && !mild ? s.in[T_V] : s.ptil);
 #pragma unroll
         for (int c8 = 0; c8 < 4; c8++) st_tile(dst, t, (col0 >> 3) + c8, pack8(a + 8 * c8));
-        if (cross_warp && !lo) {
+        if (cross_warp && !mild && !lo) {
 #pragma unroll
             for (int c8 = 0; c8 < 4; c8++) st_tile(s.ptil, t, c8, make_uint4(0u, 0u, 0u, 0u));
         }
@@ -616,7 +627,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         const uint64_t boff = hf ? 4 : 0;     // +64 bytes: the upper 32 of the 64 contiguous elements
         if (abort2) {
             mma_commit(&s.bar_grad);          // nothing is issued
-        } else if (warp == 0) {
+        } else if (warp == 0 && !mild) {
             // gr intra, across blocks: G2r[t >= 32, k] = sum_{s<32} P~x[t,s] X[s,k]   (rows t < 32 are not read)
 #pragma unroll
             for (int hq = 0; hq < 2; hq++)
@@ -625,7 +636,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     mma_ss((hq ? tm_hi : tm_lo) + C_G2R, desc_kmajor(&s.in[T_V], 0, k),
                            desc_mnmajor(&s.x, 0, k) + (hq ? 4 : 0), id_kn, k > 0);
             mma_commit(&s.bar_grad);
-        } else if (warp == 1) {
+        } else if (warp == 1 && !mild) {
             // gk intra, across blocks: G2k[s < 32, k] = sum_{t>=32} P~x[t,s] X[t,k]   (rows s >= 32 are not read)
 #pragma unroll
             for (int hq = 0; hq < 2; hq++)
@@ -634,14 +645,14 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     mma_ss((hq ? tm_hi : tm_lo) + C_G2K, desc_mnmajor(&s.in[T_V], 32, k),
                            desc_mnmajor(&s.x, 32, k) + (hq ? 4 : 0), id_nn, k > 0);
             mma_commit(&s.bar_grad);
-        } else if (warp < 4) {
-            // gr intra, same block: G1r[t,k] = sum_s P~d[t,s] Kt[s,k]
+        } else if (warp == 2 || warp == 3) {
+            // gr intra, same block (mild chunk: the whole chunk): G1r[t,k] = sum_s P~d[t,s] Kt[s,k]
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tmh + C_G1R, desc_kmajor(&s.ptil, 0, k), desc_mnmajor(&s.kt, 0, k) + boff, id_kn, k > 0);
             mma_commit(&s.bar_grad);
-        } else if (warp < 6) {
-            // gk intra, same block: G1k[s,k] = sum_t P~d[t,s] Rt[t,k]
+        } else if (warp == 4 || warp == 5) {
+            // gk intra, same block (mild chunk: the whole chunk): G1k[s,k] = sum_t P~d[t,s] Rt[t,k]
 #pragma unroll
             for (int k = 0; k < 4; k++)
                 mma_ss(tmh + C_G1K, desc_mnmajor(&s.ptil, 0, k), desc_mnmajor(&s.rt, 0, k) + boff, id_nn, k > 0);
@@ -685,16 +696,17 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     // The decay gradient of token t is  glw_t = K_j + sum_{t'<=t} (a_t' + b_t') - b_t  with
     //   a_t = -(qrS_t + qrI_t)   (gr side),     b_t = qkD_t + qkI_t   (gk side),
     // qrS/qkD the state parts of r*gr and k*gk and qrI/qkI their intra-chunk parts (file header).
-    auto side_pass = [&](auto side_tag) {
+    auto side_pass = [&](auto side_tag, auto mild_tag) {
         constexpr bool GR = decltype(side_tag)::value;
-        const bool has2 = GR ? (w4 >= 2) : (w4 < 2);         // the cross-block accumulator covers this token
+        constexpr bool MILD = decltype(mild_tag)::value;      // compiled twice: without / with the cross-block terms
+        const bool has2 = !MILD && (GR ? (w4 >= 2) : (w4 < 2));   // the cross-block accumulator covers this token
         const Tile &t_own = GR ? s.rt : s.kt;
         const Tile &t_raw = GR ? s.in[T_R] : s.in[T_K], &t_oth = GR ? s.in[T_K] : s.in[T_R];
         constexpr int cGS = GR ? C_GSR : C_GSK, cG1 = GR ? C_G1R : C_G1K, cG2 = GR ? C_G2R : C_G2K;
         Tile &o_main = GR ? o_gr : o_gk;
         Tile &exch = GR ? s.in[T_S] : s.ptil;                 // what the other group needs from this one
         const int zrow = GR ? t - 1 : t;                      // gr factors use c_{t-1}, gk factors c_t
-        const int mrow = t < HB ? 15 : 47;
+        const int mrow = MILD ? 31 : (t < HB ? 15 : 47);          // row of the table that holds the reference point
 #pragma unroll 1
         for (int bt = 0; bt < 4; bt++) {
             const int c8 = 4 * hh + bt;       // 16-byte column of the bf16 tiles; channels 8*c8 .. +7
@@ -760,7 +772,11 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             }
         }
     };
-    if (wg == 0) side_pass(std::true_type{}); else side_pass(std::false_type{});
+    if (mild) {
+        if (wg == 0) side_pass(std::true_type{}, std::true_type{}); else side_pass(std::false_type{}, std::true_type{});
+    } else {
+        if (wg == 0) side_pass(std::true_type{}, std::false_type{}); else side_pass(std::false_type{}, std::false_type{});
+    }
     if (wg == 0) {
         // gv: accumulator [s, v]
         if (!abort2 && !mbar_wait(&s.bar_gv, 0)) fail = 1;

@@ -100,6 +100,22 @@ def test_chunked_v6_decay_extremes(shift):
         TL.assert_close(f"v6.{n}", got[n], want[n], 2e-2, extra=f"(shift={shift})")
 
 
+def test_chunked_v6_mild_and_steep_chunks_mixed():
+    """the kernels factor a chunk around one point when its decay is mild and around block
+    midpoints otherwise; here chunks of both kinds alternate inside one call (and inside one head)"""
+    W, wkv56 = _pkg()
+    q = TL.case56("v6", 2, 512, 2, BF, seed=41)
+    x = q["x"].copy()
+    x[:, 64:128] += 3.0          # a steep chunk
+    x[:, 200:210] += 4.0         # ten steep tokens inside an otherwise mild chunk
+    x[:, 320:448, :64] += 2.5    # steep in one head only
+    q["x"] = TL.rounded(x, BF)
+    want = floored_oracle("v6", q)
+    got = run("v6", q, W.WKV_STATE_KV, wkv56, W, W.WKV_PATH_CHUNKED)
+    for n in EXTREME_CHECKED:
+        TL.assert_close(f"v6.{n}", got[n], want[n], 2e-2)
+
+
 def test_chunked_bitwise_repeatable():
     """no atomics anywhere: the same call twice gives identical bits"""
     W, wkv56 = _pkg()
