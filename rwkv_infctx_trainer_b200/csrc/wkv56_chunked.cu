@@ -291,83 +291,150 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     if (P.dchunk) P.dchunk[((size_t)bh * n + j) * 64 + ch0 + ch] = d;
                 }
             }
-            // r-side operands, walking forward over the thread's tokens:
-            //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
-            //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
-            float fa[4], fb[4], ref[4];     // ref: the reference point of the score factors (block-local)
+            if (mild) {
+                // One reference point (the end of block 0) for the whole chunk.  With it the state-term
+                // factors are the score factors times a per-channel constant:
+                //   block 0:  rt = r 2^{cp - e0},  rhat = rt 2^{e0};   kt = k 2^{e0 - c},  khat = kt 2^{total of block 1}
+                //   block 1:  rt = r 2^{cp},       rhat = rt 2^{e0};   kt = k 2^{-c},      khat = kt 2^{total of block 1}
+                // (cp, c counted from the thread's block start) -- one running factor per side instead of two.
+                float fa[4], cr[4], ck[4];
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
-                ref[ch] = mild ? (blk ? 0.f : D.e[ch]) : D.m[ch];
-                fa[ch] = exp2f(D.cp0[ch] - ref[ch]);
-                fb[ch] = exp2f(D.cp0[ch]);
-            }
-            if (full) {
+                for (int ch = 0; ch < 4; ch++) {
+                    const float own = exp2f(D.e[ch]);
+                    cr[ch] = blk ? other[ch] : own;
+                    ck[ch] = blk ? own : other[ch];
+                    fa[ch] = exp2f(D.cp0[ch] - (blk ? 0.f : D.e[ch]));
+                }
+                if (full) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
+                    for (int i = 0; i < 4; i++) {
+                        const int t = tok0 + i;
+                        float r[4], k[4], rt[4], rh[4];
+                        unpack4(ld_tile4(in[0], t, cc, hf), r);
+                        unpack4(ld_tile4(in[1], t, cc, hf), k);
+                        float dsum = 0.f;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            rt[ch] = r[ch] * fa[ch];
+                            rh[ch] = rt[ch] * cr[ch];
+                            dsum += r[ch] * uu[ch] * k[ch];
+                            fa[ch] *= D.w[i][ch];
+                        }
+                        st_tile4(in[0], t, cc, hf, pack4(rt));
+                        st_tile4(in[3], t, cc, hf, pack4(rh));
+                        dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+                        dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+                        if ((lane & 3) == 0) s.dpart[(lane & 15) >> 2][t] = dsum;
+                    }
+                } else if (P.dchunk) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int t = tok0 + i;
+                        float r[4], rh[4];
+                        unpack4(ld_tile4(in[0], t, cc, hf), r);
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            rh[ch] = r[ch] * fa[ch] * cr[ch];
+                            fa[ch] *= D.w[i][ch];
+                        }
+                        st_tile4(in[3], t, cc, hf, pack4(rh));
+                    }
+                }
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) fa[ch] = exp2f((blk ? 0.f : D.e[ch]) - D.c3[ch]);
+#pragma unroll
+                for (int i = 3; i >= 0; i--) {
                     const int t = tok0 + i;
-                    float r[4], k[4], rt[4], rh[4], xx[4];
-                    unpack4(ld_tile4(in[0], t, cc, hf), r);
+                    float k[4], kt[4], kh[4];
                     unpack4(ld_tile4(in[1], t, cc, hf), k);
-                    float dsum = 0.f;
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
-                        rt[ch] = r[ch] * fa[ch];
-                        xx[ch] = r[ch] * fb[ch];
-                        rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
-                        dsum += r[ch] * uu[ch] * k[ch];
+                        kt[ch] = k[ch] * fa[ch];
+                        kh[ch] = kt[ch] * ck[ch];
+                        fa[ch] *= D.w[i][ch];
+                    }
+                    if (full) st_tile4(in[1], t, cc, hf, pack4(kt));
+                    st_tile4(khat, t, cc, hf, pack4(kh));
+                }
+            } else {
+                // r-side operands, walking forward over the thread's tokens:
+                //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
+                //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
+                float fa[4], fb[4], ref[4];     // ref: the reference point of the score factors (block-local)
+    #pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    ref[ch] = D.m[ch];
+                    fa[ch] = exp2f(D.cp0[ch] - ref[ch]);
+                    fb[ch] = exp2f(D.cp0[ch]);
+                }
+                if (full) {
+    #pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int t = tok0 + i;
+                        float r[4], k[4], rt[4], rh[4], xx[4];
+                        unpack4(ld_tile4(in[0], t, cc, hf), r);
+                        unpack4(ld_tile4(in[1], t, cc, hf), k);
+                        float dsum = 0.f;
+    #pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            rt[ch] = r[ch] * fa[ch];
+                            xx[ch] = r[ch] * fb[ch];
+                            rh[ch] = blk ? xx[ch] * other[ch] : xx[ch];
+                            dsum += r[ch] * uu[ch] * k[ch];
+                            fa[ch] *= D.w[i][ch];
+                            fb[ch] *= D.w[i][ch];
+                        }
+                        st_tile4(in[0], t, cc, hf, pack4(rt));
+                        st_tile4(in[3], t, cc, hf, pack4(rh));
+                        if (blk) st_tile4(s.x, t, cc, hf, pack4(xx));
+                        // groups of four lanes pool their channels; four partials per token remain
+                        dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+                        dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+                        if ((lane & 3) == 0) s.dpart[(lane & 15) >> 2][t] = dsum;
+                    }
+                } else if (P.dchunk) {
+                    // state-only pass on behalf of a backward call: r e^{cp} alone
+    #pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int t = tok0 + i;
+                        float r[4], rh[4];
+                        unpack4(ld_tile4(in[0], t, cc, hf), r);
+    #pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            const float xx = r[ch] * fb[ch];
+                            rh[ch] = blk ? xx * other[ch] : xx;
+                            fb[ch] *= D.w[i][ch];
+                        }
+                        st_tile4(in[3], t, cc, hf, pack4(rh));
+                    }
+                }
+                // k-side operands, walking backward:
+                //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
+                //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
+    #pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    fa[ch] = exp2f(ref[ch] - D.c3[ch]);
+                    fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
+                }
+    #pragma unroll
+                for (int i = 3; i >= 0; i--) {
+                    const int t = tok0 + i;
+                    float k[4], kt[4], kh[4], xx[4];
+                    unpack4(ld_tile4(in[1], t, cc, hf), k);
+    #pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        kt[ch] = k[ch] * fa[ch];
+                        xx[ch] = k[ch] * fb[ch];
+                        kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
                         fa[ch] *= D.w[i][ch];
                         fb[ch] *= D.w[i][ch];
                     }
-                    st_tile4(in[0], t, cc, hf, pack4(rt));
-                    st_tile4(in[3], t, cc, hf, pack4(rh));
-                    if (blk && !mild) st_tile4(s.x, t, cc, hf, pack4(xx));
-                    // groups of four lanes pool their channels; four partials per token remain
-                    dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
-                    dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
-                    if ((lane & 3) == 0) s.dpart[(lane & 15) >> 2][t] = dsum;
-                }
-            } else if (P.dchunk) {
-                // state-only pass on behalf of a backward call: r e^{cp} alone
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int t = tok0 + i;
-                    float r[4], rh[4];
-                    unpack4(ld_tile4(in[0], t, cc, hf), r);
-#pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {
-                        const float xx = r[ch] * fb[ch];
-                        rh[ch] = blk ? xx * other[ch] : xx;
-                        fb[ch] *= D.w[i][ch];
+                    if (full) {
+                        st_tile4(in[1], t, cc, hf, pack4(kt));
+                        if (!blk) st_tile4(s.x, t, cc, hf, pack4(xx));
                     }
-                    st_tile4(in[3], t, cc, hf, pack4(rh));
+                    st_tile4(khat, t, cc, hf, pack4(kh));
                 }
-            }
-            // k-side operands, walking backward:
-            //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
-            //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
-#pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
-                fa[ch] = exp2f(ref[ch] - D.c3[ch]);
-                fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
-            }
-#pragma unroll
-            for (int i = 3; i >= 0; i--) {
-                const int t = tok0 + i;
-                float k[4], kt[4], kh[4], xx[4];
-                unpack4(ld_tile4(in[1], t, cc, hf), k);
-#pragma unroll
-                for (int ch = 0; ch < 4; ch++) {
-                    kt[ch] = k[ch] * fa[ch];
-                    xx[ch] = k[ch] * fb[ch];
-                    kh[ch] = blk ? xx[ch] : xx[ch] * other[ch];
-                    fa[ch] *= D.w[i][ch];
-                    fb[ch] *= D.w[i][ch];
-                }
-                if (full) {
-                    st_tile4(in[1], t, cc, hf, pack4(kt));
-                    if (!blk && !mild) st_tile4(s.x, t, cc, hf, pack4(xx));
-                }
-                st_tile4(khat, t, cc, hf, pack4(kh));
             }
             return mild;
         };

@@ -486,27 +486,52 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
         // k-side operands, walking backward:  fa = 2^{m - c};  fb = 2^{e - c}
         //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-            fa[ch] = exp2f(ref[ch] - D.c3[ch]);
-            fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
-        }
-#pragma unroll
-        for (int i = 3; i >= 0; i--) {
-            const int t = ptok0 + i;
-            float k[4], kt[4], kh[4], xx[4];
-            unpack4(ld_tile4(s.in[T_K], t, pcc, phf), k);
+        if (mild) {
+            // one reference point: khat is kt times a per-channel constant (block 0: kt = k 2^{e0 - c},
+            // khat = kt 2^{total of block 1};  block 1: kt = k 2^{-c}, khat = kt 2^{total of block 1})
+            float ck[4];
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                kt[ch] = k[ch] * fa[ch];
-                xx[ch] = k[ch] * fb[ch];
-                kh[ch] = pblk ? xx[ch] : xx[ch] * other[ch];
-                fa[ch] *= D.w[i][ch];
-                fb[ch] *= D.w[i][ch];
+                fa[ch] = exp2f(ref[ch] - D.c3[ch]);
+                ck[ch] = pblk ? exp2f(D.e[ch]) : other[ch];
             }
-            st_tile4(s.kt, t, pcc, phf, pack4(kt));
-            if (!pblk && !mild) st_tile4(s.x, t, pcc, phf, pack4(xx));
-            st_tile4(s.khat, t, pcc, phf, pack4(kh));
+#pragma unroll
+            for (int i = 3; i >= 0; i--) {
+                const int t = ptok0 + i;
+                float k[4], kt[4], kh[4];
+                unpack4(ld_tile4(s.in[T_K], t, pcc, phf), k);
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    kt[ch] = k[ch] * fa[ch];
+                    kh[ch] = kt[ch] * ck[ch];
+                    fa[ch] *= D.w[i][ch];
+                }
+                st_tile4(s.kt, t, pcc, phf, pack4(kt));
+                st_tile4(s.khat, t, pcc, phf, pack4(kh));
+            }
+        } else {
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                fa[ch] = exp2f(ref[ch] - D.c3[ch]);
+                fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
+            }
+#pragma unroll
+            for (int i = 3; i >= 0; i--) {
+                const int t = ptok0 + i;
+                float k[4], kt[4], kh[4], xx[4];
+                unpack4(ld_tile4(s.in[T_K], t, pcc, phf), k);
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    kt[ch] = k[ch] * fa[ch];
+                    xx[ch] = k[ch] * fb[ch];
+                    kh[ch] = pblk ? xx[ch] : xx[ch] * other[ch];
+                    fa[ch] *= D.w[i][ch];
+                    fb[ch] *= D.w[i][ch];
+                }
+                st_tile4(s.kt, t, pcc, phf, pack4(kt));
+                if (!pblk) st_tile4(s.x, t, pcc, phf, pack4(xx));
+                st_tile4(s.khat, t, pcc, phf, pack4(kh));
+            }
         }
     }
     fence_async_smem();
