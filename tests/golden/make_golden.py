@@ -99,7 +99,7 @@ CASES = [
     # name, variant, project dir, B, T, H, N, seed, seg_len, state, gstate, token stride stored
     ("v5_small", "v5", "RWKV-v5", 2, 256, 2, 64, 11, 128, True, True, 1),
     ("v6_small", "v6", "RWKV-v6", 2, 256, 2, 64, 12, 128, True, True, 1),
-    # BASELINE config 0: B=2, T=512 as 4 segments of 128, H=4, N=64, zero state, seed 0
+    # the CPU-runnable benchmark case: B=2, T=512 as 4 segments of 128, H=4, N=64, zero state, seed 0
     ("v5_config0", "v5", "RWKV-v5", 2, 512, 4, 64, 0, 128, False, False, 4),
     ("v6_config0shape", "v6", "RWKV-v6", 2, 512, 4, 64, 0, 128, False, False, 4),
 ]
