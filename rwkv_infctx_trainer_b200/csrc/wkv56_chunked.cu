@@ -361,21 +361,21 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 //   fa = 2^{cp - m};  fb = 2^{cp}   (cp counted from the block start)
                 //   block 0: rhat = r fb                 block 1: x = r fb, rhat = x 2^{total of block 0}
                 float fa[4], fb[4], ref[4];     // ref: the reference point of the score factors (block-local)
-    #pragma unroll
+#pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     ref[ch] = D.m[ch];
                     fa[ch] = exp2f(D.cp0[ch] - ref[ch]);
                     fb[ch] = exp2f(D.cp0[ch]);
                 }
                 if (full) {
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const int t = tok0 + i;
                         float r[4], k[4], rt[4], rh[4], xx[4];
                         unpack4(ld_tile4(in[0], t, cc, hf), r);
                         unpack4(ld_tile4(in[1], t, cc, hf), k);
                         float dsum = 0.f;
-    #pragma unroll
+#pragma unroll
                         for (int ch = 0; ch < 4; ch++) {
                             rt[ch] = r[ch] * fa[ch];
                             xx[ch] = r[ch] * fb[ch];
@@ -394,12 +394,12 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                     }
                 } else if (P.dchunk) {
                     // state-only pass on behalf of a backward call: r e^{cp} alone
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const int t = tok0 + i;
                         float r[4], rh[4];
                         unpack4(ld_tile4(in[0], t, cc, hf), r);
-    #pragma unroll
+#pragma unroll
                         for (int ch = 0; ch < 4; ch++) {
                             const float xx = r[ch] * fb[ch];
                             rh[ch] = blk ? xx * other[ch] : xx;
@@ -411,17 +411,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 // k-side operands, walking backward:
                 //   fa = 2^{m - c};  fb = 2^{e - c}   (e = total of the thread's block)
                 //   block 0: x = k fb, khat = x 2^{total of block 1}      block 1: khat = k fb
-    #pragma unroll
+#pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     fa[ch] = exp2f(ref[ch] - D.c3[ch]);
                     fb[ch] = exp2f(D.e[ch] - D.c3[ch]);
                 }
-    #pragma unroll
+#pragma unroll
                 for (int i = 3; i >= 0; i--) {
                     const int t = tok0 + i;
                     float k[4], kt[4], kh[4], xx[4];
                     unpack4(ld_tile4(in[1], t, cc, hf), k);
-    #pragma unroll
+#pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
                         kt[ch] = k[ch] * fa[ch];
                         xx[ch] = k[ch] * fb[ch];
