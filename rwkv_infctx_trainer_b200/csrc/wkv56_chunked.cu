@@ -237,13 +237,18 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
             S[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
         }
-        float uu[4], lwc[4];
+        float uu[4], lwc[4], wc[4];
+        bool steep_static = false;
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) {
             uu[ch] = __bfloat162float(P.u[h * 64 + ch0 + ch]);
             bool live;
             lwc[ch] = PER_TOKEN ? 0.f : log2_decay(P.wvec[h * 64 + ch0 + ch], P.w_kind, live);
+            wc[ch] = exp2f(lwc[ch]);
+            steep_static |= 8.f * lwc[ch] < MILD_L2_PER_8;
         }
+        // static decay: whether the head's chunks are mild is known once and for all
+        const bool mild_static = PER_TOKEN ? false : !compute_sync_or(steep_static);
 
         // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
         // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
@@ -252,26 +257,33 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             Tile &khat = s.khat[j & 1];
             float c[4][4];
             DecayT<4> D;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int t = tok0 + i;
-                const bool valid = j * CH + t < P.T;
-                if (PER_TOKEN) {
-                    float x[4];
-                    unpack4(ld_tile4(in[3], t, cc, hf), x);
-#pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {
-                        bool live;
-                        const float l2 = log2_decay(x[ch], P.w_kind, live);
-                        c[i][ch] = valid ? l2 : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 4; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
-                }
-            }
             float other_l2[4];
-            const bool mild = decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [](bool p) { return compute_sync_or(p); });
+            bool mild;
+            if (!PER_TOKEN && (j + 1) * CH <= P.T) {
+                // static decay, whole chunk in range: closed form, nothing to scan or exchange
+                decay_static(lwc, wc, tok0, c, D, other_l2);
+                mild = mild_static;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = tok0 + i;
+                    const bool valid = j * CH + t < P.T;
+                    if (PER_TOKEN) {
+                        float x[4];
+                        unpack4(ld_tile4(in[3], t, cc, hf), x);
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            bool live;
+                            const float l2 = log2_decay(x[ch], P.w_kind, live);
+                            c[i][ch] = valid ? l2 : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) c[i][ch] = valid ? lwc[ch] : 0.f;
+                    }
+                }
+                mild = decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [](bool p) { return compute_sync_or(p); });
+            }
             if (tid == 0) s.mild_flag[j & 1] = mild;
             {
                 // Debug stamp "decay scan done".  The clock read is also a scheduling boundary: without

@@ -172,6 +172,27 @@ __device__ __forceinline__ bool decay_scan8(float (&l2)[4][4], int warp, int lan
     return mild;
 }
 
+// The same quantities for a static per-channel decay (v5) and a chunk with all 64 tokens in range:
+// every token of channel ch decays by lw[ch] (log2), so nothing has to be scanned or exchanged.
+// w[ch] = 2^{lw[ch]}; tok0 = first of the thread's 4 tokens (0..63).
+__device__ __forceinline__ void decay_static(const float (&lw)[4], const float (&w)[4], int tok0, float (&l2)[4][4],
+                                             DecayT<4> &D, float (&other_l2)[4]) {
+    const float t0 = (float)(tok0 & (HB - 1));
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            D.w[i][ch] = w[ch];
+            l2[i][ch] = (t0 + (float)(i + 1)) * lw[ch];
+        }
+        D.cp0[ch] = t0 * lw[ch];
+        D.c3[ch] = l2[3][ch];
+        D.m[ch] = 16.f * lw[ch];
+        D.e[ch] = 32.f * lw[ch];
+        other_l2[ch] = D.e[ch];
+    }
+}
+
 // 8-byte halves of a 16-byte tile chunk (4 bf16)
 __device__ __forceinline__ void unpack4(const uint2 &q, float *f) {
     f[0] = __uint_as_float(q.x << 16); f[1] = __uint_as_float(q.x & 0xFFFF0000u);

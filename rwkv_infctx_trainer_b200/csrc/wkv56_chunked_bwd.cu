@@ -416,32 +416,49 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         unsigned livebits[4];
         // the warps' decay totals are exchanged through the first bytes of the A~ tile (unused until the mask pass)
         float *wtot = reinterpret_cast<float *>(s.atil.b);
+        float other_l2[4], other[4];
+        if (!PER_TOKEN && (j + 1) * CH <= P.T) {
+            // static decay, whole chunk in range: closed form, nothing to scan or exchange
+            float wc[4];
+            bool steep = false;
+            unsigned lb = 0;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int t = ptok0 + i;
-            const bool valid = j * CH + t < P.T;
-            livebits[i] = 0;
-            if (PER_TOKEN) {
-                float x[4];
-                unpack4(ld_tile4(s.in[T_W], t, pcc, phf), x);
+            for (int ch = 0; ch < 4; ch++) {
+                wc[ch] = exp2f(lwc[ch]);
+                steep |= 8.f * lwc[ch] < MILD_L2_PER_8;
+                lb |= (livec[ch] ? 1u : 0u) << ch;
+            }
 #pragma unroll
-                for (int ch = 0; ch < 4; ch++) {
-                    bool live;
-                    const float l2 = log2_decay(x[ch], P.w_kind, live);
-                    livebits[i] |= (live ? 1u : 0u) << ch;
-                    c[i][ch] = valid ? l2 : 0.f;
-                }
-            } else {
+            for (int i = 0; i < 4; i++) livebits[i] = lb;
+            decay_static(lwc, wc, ptok0, c, D, other_l2);
+            mild = __syncthreads_or(steep) == 0;
+        } else {
 #pragma unroll
-                for (int ch = 0; ch < 4; ch++) {
-                    livebits[i] |= (livec[ch] ? 1u : 0u) << ch;
-                    c[i][ch] = valid ? lwc[ch] : 0.f;
+            for (int i = 0; i < 4; i++) {
+                const int t = ptok0 + i;
+                const bool valid = j * CH + t < P.T;
+                livebits[i] = 0;
+                if (PER_TOKEN) {
+                    float x[4];
+                    unpack4(ld_tile4(s.in[T_W], t, pcc, phf), x);
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        bool live;
+                        const float l2 = log2_decay(x[ch], P.w_kind, live);
+                        livebits[i] |= (live ? 1u : 0u) << ch;
+                        c[i][ch] = valid ? l2 : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        livebits[i] |= (livec[ch] ? 1u : 0u) << ch;
+                        c[i][ch] = valid ? lwc[ch] : 0.f;
+                    }
                 }
             }
+            // (the barrier inside: every w value has been read, so its slot may take the table)
+            mild = decay_scan8(c, warp, lane, wtot, D, other_l2, [](bool p) { return __syncthreads_or(p) != 0; });
         }
-        float other_l2[4], other[4];
-        // (the barrier inside: every w value has been read, so its slot may take the table)
-        mild = decay_scan8(c, warp, lane, wtot, D, other_l2, [](bool p) { return __syncthreads_or(p) != 0; });
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
 #pragma unroll
