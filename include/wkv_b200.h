@@ -4,9 +4,12 @@
  * carried across BPTT segments, for the v4, v5 and v6 variants.
  *
  * Every entry point takes raw device pointers and sizes, launches on the
- * stream it is given (a cudaStream_t passed as void*), allocates nothing,
- * never synchronises and keeps no global state.  The caller makes the device
- * that owns the pointers current before the call.  Return value: WKV_OK or
+ * stream it is given (a cudaStream_t passed as void*), allocates nothing and
+ * never synchronises.  The caller makes the device that owns the pointers
+ * current before the call.  State kept between calls: per-device facts looked
+ * up once (SM count, kernel attributes already set), a per-thread cache of the
+ * last TMA descriptors built, and -- wkv4_backward_static only -- the device
+ * address and contents of its built-in scratch array (see there).  Return value: WKV_OK or
  * one of the WKV_ERR_* codes (wkv_error_string() gives the text); on error
  * nothing was launched.  Nothing ever aborts the process or traps the device.
  *
@@ -60,6 +63,15 @@ enum {
     WKV_PATH_SCALAR = 1, /* token-serial fp32 CUDA-core kernels (any dtype, any T) */
     WKV_PATH_CHUNKED = 2 /* tcgen05 chunked kernels (bf16 only) */
 };
+/* The two paths differ in one documented way.  The chunked kernels floor every per-token
+ * decay at 0.005 and pass no gradient to a floored element -- what the project's working
+ * path does (w.clamp(0.005), RWKV-v6/src/module/rwkv_inner.py:40-45) and what keeps every
+ * operand of the tensor-core products inside the bf16 exponent range.  The token-serial
+ * kernels do not floor, like the project's CUDA kernels (wkv6state_cuda_v1.cu, wkv5_cuda.cu).
+ * So a bf16 call under WKV_PATH_AUTO follows rwkv_inner on decays below 0.005 (they need
+ * x > 1.667), and WKV_PATH_SCALAR follows the CUDA kernels; above the floor they agree.
+ * The v6 chunked kernels read the decay activation x in bf16: given WKV_W_NEGEXP they first
+ * rebuild x = log(-ew) in bf16 (exact when ew came from a bf16 x, as in TimeMix.py:49-51). */
 
 const char *wkv_error_string(int code);
 
@@ -162,6 +174,13 @@ typedef struct wkv_args {
      * (RWKV-v6/src/model.py:660-662); this is the op-level equivalent. */
     void *state_ckpt;
     size_t state_ckpt_bytes;
+    /* Chunked path only.  The chunks of a segment form a serial chain per (batch, head); when
+     * there are too few chains to fill the GPU (few heads per GPU, batch 1) the chain is cut
+     * into this many groups of consecutive chunks that run in parallel (a summary pass per
+     * group, a scan over the groups, then the full pass per group).  0 = the library decides
+     * from B*H, T and the SM count; 1 = never split; n > 1 = n groups (at most one per chunk).
+     * The *_workspace() sizes depend on it: fill it in before asking for them. */
+    int time_groups;
 } wkv_args_t;
 
 /* Bytes of wkv_args_t.state_ckpt for these arguments (0 when the call would not run on
@@ -193,6 +212,27 @@ int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
 
 /* Library build identification: "wkv_b200 <n> sm_100a". */
 const char *wkv_version(void);
+
+/* ------------------------------------------------------------ self-tests --
+ * (No counterpart in RWKV-infctx-trainer: its kernels have no device-side waits.)
+ * Every device-side wait of the chunked kernels is bounded: after a number of polls it
+ * gives up, the kernel sets its bit in the status word, lets copies and products in
+ * flight finish, frees its tensor memory and returns.  These two entry points make that
+ * happen on purpose, safely: nothing spins without a bound and nothing traps.
+ *
+ * wkv_selftest_wait_timeout: one CTA waits on a barrier nobody arrives on, `limit`
+ * polls (1..100000); afterwards *status_word (device memory, zeroed by the caller) holds
+ * 16 | 32: the plain wait gave up, and the abort flag it raised ended the CTA's other wait.
+ *
+ * wkv56_selftest_abort: a normal v5/v6 forward (backward_call = 0) or backward call on
+ * the chunked kernels in which one kernel (0 forward, 1 dS scan, 2 per-chunk backward)
+ * never issues the loads of chunk `skip_chunk`, with every wait cut to `limit` polls.
+ * The call returns WKV_OK (the launch succeeded); the status word at the start of the
+ * workspace then has bit 1 (forward), 2 (dS scan) or 4 (per-chunk backward) set and the
+ * outputs are invalid. */
+int wkv_selftest_wait_timeout(int *status_word, unsigned limit, void *stream);
+int wkv56_selftest_abort(const wkv_args_t *a, int per_token_w, int backward_call, int kernel,
+                         int skip_chunk, unsigned limit, void *stream);
 
 #ifdef __cplusplus
 }

@@ -33,6 +33,7 @@ class WkvArgs(ctypes.Structure):
         ("gr", _vp), ("gk", _vp), ("gv", _vp), ("gw", _vp), ("gu", _vp), ("gstate_in", _vp),
         ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
         ("state_ckpt", _vp), ("state_ckpt_bytes", ctypes.c_size_t),
+        ("time_groups", ctypes.c_int),
     ]
 
 
@@ -42,19 +43,24 @@ EXPORTS = [
     "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
+    "wkv_selftest_wait_timeout", "wkv56_selftest_abort",
 ]
 
 _lib = None
 
 
 def load() -> ctypes.CDLL:
-    """Load (building first if the in-tree library is missing or stale and nvcc exists)."""
+    """Load the in-tree library.  Where nvcc exists it is first rebuilt if it is missing or older
+    than its sources; where it does not (a GPU box that received a prebuilt copy) the file is
+    taken as it is, and a missing file is an error."""
     global _lib
     if _lib is not None:
         return _lib
     path = _build.LIB
-    if not os.path.exists(path):
+    if _build.have_nvcc():
         path = _build.build()
+    elif not os.path.exists(path):
+        raise ImportError(f"{path} is missing and there is no nvcc to build it")
     lib = ctypes.CDLL(path)
     if any(not hasattr(lib, name) for name in EXPORTS):
         # a library from older sources: rebuild once (raises if nvcc is absent)
@@ -83,6 +89,10 @@ def load() -> ctypes.CDLL:
     lib.wkv56_uses_chunked.argtypes = [ctypes.POINTER(WkvArgs), i]
     lib.wkv56_state_ckpt_bytes.restype = ctypes.c_size_t
     lib.wkv56_state_ckpt_bytes.argtypes = [ctypes.POINTER(WkvArgs), i]
+    lib.wkv_selftest_wait_timeout.restype = i
+    lib.wkv_selftest_wait_timeout.argtypes = [_vp, ctypes.c_uint, _vp]
+    lib.wkv56_selftest_abort.restype = i
+    lib.wkv56_selftest_abort.argtypes = [ctypes.POINTER(WkvArgs), i, i, i, i, ctypes.c_uint, _vp]
     for v in ("wkv5", "wkv6"):
         for d in ("forward", "backward"):
             fn = getattr(lib, f"{v}_{d}")

@@ -4,6 +4,7 @@
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -12,19 +13,37 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libwkv_b200.so")
+STAMP = LIB + ".digest"
 SOURCES = ["wkv_api.cu", "wkv4.cu", "wkv4_par.cu", "wkv56_scalar.cu", "wkv56_chunked.cu", "wkv56_chunked_bwd.cu"]
 HEADERS = ["wkv_common.cuh", os.path.join("..", "..", "include", "wkv_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC"]
 
 
+def have_nvcc() -> bool:
+    return bool(shutil.which("nvcc")) or os.path.exists("/usr/local/cuda/bin/nvcc")
+
+
+def _source_digest() -> str:
+    """sha256 over the names and contents of everything the library is compiled from"""
+    h = hashlib.sha256()
+    files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cuh", ".h"))]
+    files.append(os.path.join(PKG, "..", "include", "wkv_b200.h"))
+    for f in files:
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
 def _stale() -> bool:
-    if not os.path.exists(LIB):
+    """The library is current when the digest recorded beside it at build time matches the
+    sources (file times are not used: they do not survive a copy of the tree)."""
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
-    deps += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    with open(STAMP) as f:
+        return f.read().strip() != _source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -52,8 +71,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {s}:\n{out}")
         if verbose and out:
             print(out)
-    cmd = [nvcc, "-shared", "-o", LIB, *objs]
-    subprocess.check_call(cmd)
+    # link beside the target and move into place: another process may be loading the library
+    tmp = f"{LIB}.{os.getpid()}.tmp"
+    subprocess.check_call([nvcc, "-shared", "-o", tmp, *objs])
+    os.replace(tmp, LIB)
+    with open(STAMP + f".{os.getpid()}", "w") as f:
+        f.write(_source_digest())
+    os.replace(STAMP + f".{os.getpid()}", STAMP)
     return LIB
 
 

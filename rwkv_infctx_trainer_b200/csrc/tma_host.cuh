@@ -25,18 +25,40 @@ inline encode_tiled_fn tensor_map_encoder() {
     return fn;
 }
 
-// Map over a contiguous bf16 tensor [B, T, C]; box = 64 channels x box_t tokens
-// x 1 batch row, 128-byte swizzle, out-of-range tokens read as zero.
-inline bool make_btc_map(CUtensorMap *map, const void *base, int B, int T, int C, int box_t = 64) {
+// Map over a contiguous bf16 tensor [B, T, C]; box = 64 channels x 64 tokens x 1 batch row,
+// 128-byte swizzle, out-of-range tokens read as zero.  A map depends on the base address and the
+// shape only, so the last few are remembered per host thread: a training loop that calls the op
+// with the same buffers every step (or a T = 1 decode loop) encodes each map once.
+inline bool make_btc_map(CUtensorMap *map, const void *base, int B, int T, int C) {
+    struct Entry {
+        const void *base;
+        int B, T, C;
+        CUtensorMap map;
+    };
+    constexpr int SLOTS = 64;
+    static thread_local Entry cache[SLOTS];
+    static thread_local int next = 0;
+    for (int i = 0; i < SLOTS; i++) {
+        const Entry &e = cache[i];
+        if (e.base == base && e.B == B && e.T == T && e.C == C && base != nullptr) {
+            *map = e.map;
+            return true;
+        }
+    }
     encode_tiled_fn enc = tensor_map_encoder();
     if (!enc) return false;
     cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)T, (cuuint64_t)B};
     cuuint64_t strides[2] = {(cuuint64_t)C * 2, (cuuint64_t)T * C * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)box_t, 1};
+    cuuint32_t box[3] = {64, 64, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    Entry &e = cache[next];
+    next = (next + 1) % SLOTS;
+    e.base = base; e.B = B; e.T = T; e.C = C; e.map = *map;
+    return true;
 }
 
 }  // namespace wkv

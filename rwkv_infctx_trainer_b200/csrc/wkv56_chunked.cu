@@ -14,8 +14,17 @@
 //
 // All contractions run on tcgen05.mma (M=64, bf16 operands in 128-byte-swizzled
 // shared-memory tiles, fp32 accumulators in tensor memory); input tiles arrive by
-// TMA; the fp32 state lives in tensor memory for the whole segment.
-#include <cstdlib>
+// TMA; the fp32 state is carried in registers by the compute warps (the tensor core
+// only forms each chunk's own contribution to it).
+//
+// Time groups.  A segment's chunks are a serial chain per (batch, head).  When there are
+// too few chains to fill the device the chain is cut into G groups of consecutive
+// chunks and the forward runs as three launches:
+//   A. per (chain, group), from a zero state: the group's own contribution U_g and the
+//      decay d_g of the whole group (no y, no scores -- a "summary" pass);
+//   B. k_group_scan: S_start[g+1] = d_g * S_start[g] + U_g, elementwise over the groups;
+//   C. per (chain, group), from S_start[g]: the full pass.
+// With G = 1 only C runs, from the caller's state.
 
 #include "wkv56_chunked.cuh"
 
@@ -55,17 +64,22 @@ struct FwdSmem {
 };
 
 struct FwdParams {
-    int T, H, nchunk, layout, w_kind, state_only;
+    int T, H, nchunk, layout, w_kind;
+    int G, L;                 // time groups per chain, chunks per group (the last group may be shorter)
     const __nv_bfloat16 *u;
     const float *wvec;        // v5: per-channel decay parameter [H*64]
-    const float *state_in;
-    float *state_out;
+    const float *state_in;    // G == 1: the caller's state (layout `layout`)
+    const float *gstart;      // G > 1, pass C: [B*H*G, 64, 64] state at the start of every group ([key,value])
+    float *state_out;         // G == 1 only (with G > 1 the group scan writes it)
+    float *gU;                // pass A: [B*H*G, 64, 64] state a group builds from zero ([key,value])
+    float *gD;                // pass A: [B*H*G, 64] decay of a whole group per key channel
     __nv_bfloat16 *y;
     __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
     float *dchunk;            // [B*H,nchunk,64] decay of each whole chunk, or NULL; with it the
                               // kernel also stores r e^{cp} of every chunk through map_rh
     int *status;
-    long long *timeline;      // optional debug aid: clock stamps of one mid-sequence step of one CTA
+    uint32_t wait_limit;      // polls before a wait gives up
+    int skip_load;            // -1; a local chunk index leaves that chunk's TMA load out (wait-timeout test)
 };
 
 // Tensor-memory columns.  An M=64 accumulator fills lanes 0..15 of each 32-lane quarter ("lo");
@@ -76,7 +90,7 @@ struct FwdParams {
 //   A1b     hi  96..127   same-block scores, columns (s) 32..63
 //   Y       lo 128..159   y[:, 0..31]                  hi 128..159   y[:, 32..63]
 enum { COL_U = 0, COL_A1A = 64, COL_A2 = 96, COL_Y = 128, FWD_TMEM_COLS = 256 };
-constexpr int FWD_COMPUTE_THREADS = 256, FWD_THREADS = 288;
+constexpr int FWD_THREADS = 288;
 
 // barrier of the 256 compute threads that also ORs a predicate over them
 __device__ __forceinline__ bool compute_sync_or(bool pred) {
@@ -88,7 +102,11 @@ __device__ __forceinline__ bool compute_sync_or(bool pred) {
 // barrier of the 256 compute threads
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <bool PER_TOKEN>
+// MODE: what the launch is for (compiled separately so that the full pass does not carry the others' state)
+enum { FWD_FULL = 0,      // y, state_out and, when asked for, the hand-over to the backward pass
+       FWD_STATES = 1,    // backward without a hand-over: chunk-start states, r e^{cp}, chunk decays only
+       FWD_SUMMARY = 2 }; // pass A of the time-group scheme
+template <bool PER_TOKEN, int MODE>
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
@@ -97,9 +115,12 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // tells the compiler it is uniform across the warp
-    const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H, C = P.H * 64;
-    const int n = P.nchunk;
-    const bool full = P.state_only == 0;
+    // this CTA's group of chunks: global chunk index = j0 + local index, n of them
+    // (grid: x = group, y = chain)
+    const int grp = blockIdx.x, bh = blockIdx.y, unit = bh * P.G + grp;
+    const int b = bh / P.H, h = bh % P.H, C = P.H * 64;
+    const int j0 = grp * P.L, n = min(P.L, P.nchunk - j0);
+    constexpr bool full = MODE == FWD_FULL, summary = MODE == FWD_SUMMARY;
 
     if (tid == 0) {
         mbar_init(&s.load_bar[0], 1); mbar_init(&s.load_bar[1], 1);
@@ -120,16 +141,20 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (lane == 0) {
             prefetch_tmap(&map_r); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
             if (PER_TOKEN) prefetch_tmap(&map_w);
-            auto issue_load = [&](int j) {
-                const int st = j & 1;
-                mbar_expect_tx(&s.load_bar[st], (PER_TOKEN ? 4 : 3) * TILE_BYTES);
-                tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, j * CH, b);
-                tma_load_3d(&s.in[st][1], &map_k, &s.load_bar[st], h * 64, j * CH, b);
-                tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, j * CH, b);
-                if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, j * CH, b);
-            };
+            // (local chunk c; P.skip_load names a chunk whose load is left out: the host-side fault
+            // injection of the wait-timeout test, -1 in normal use)
             int issued = -1;
-            for (int j = 0; j < 2 && j < n; j++) { issue_load(j); issued = j; }
+            auto issue_load = [&](int c) {
+                if (c == P.skip_load) return;
+                const int st = c & 1, t0 = (j0 + c) * CH;
+                mbar_expect_tx(&s.load_bar[st], (PER_TOKEN ? 4 : 3) * TILE_BYTES);
+                tma_load_3d(&s.in[st][0], &map_r, &s.load_bar[st], h * 64, t0, b);
+                tma_load_3d(&s.in[st][1], &map_k, &s.load_bar[st], h * 64, t0, b);
+                tma_load_3d(&s.in[st][2], &map_v, &s.load_bar[st], h * 64, t0, b);
+                if (PER_TOKEN) tma_load_3d(&s.in[st][3], &map_w, &s.load_bar[st], h * 64, t0, b);
+                issued = c;
+            };
+            for (int c = 0; c < 2 && c < n; c++) issue_load(c);
             // descriptors: a tile's descriptor plus (byte offset >> 4) addresses inside it
             const uint64_t d_x = make_desc(smem_u32(&s.x)), d_atil = make_desc(smem_u32(&s.atil)),
                            d_sbf = make_desc(smem_u32(&s.sbf));
@@ -145,7 +170,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 const uint64_t d_r = make_desc(smem_u32(&s.in[st][0])), d_k = make_desc(smem_u32(&s.in[st][1])),
                                d_v = make_desc(smem_u32(&s.in[st][2])), d_rh = make_desc(smem_u32(&s.in[st][3])),
                                d_kh = make_desc(smem_u32(&s.khat[st]));
-                if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag)) { fail = 1; break; }
+                if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag, P.wait_limit)) { fail = 1; break; }
                 tc_fence_after();
                 if (full) {
                     // scores: A1 = Rt Kt^T (column halves), A2 = X X[0:32]^T.  In a mild chunk Rt and Kt are
@@ -174,11 +199,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 pending = c;
                 // r e^{cp} of this chunk goes out for the backward pass
                 if (P.dchunk) {
-                    tma_store_3d(&map_rh, &s.in[st][3], h * 64, c * CH, b);
+                    tma_store_3d(&map_rh, &s.in[st][3], h * 64, (j0 + c) * CH, b);
                     tma_store_commit();
                 }
                 if (full) {
-                    if (!mbar_wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag)) { fail = 1; break; }
+                    if (!mbar_wait_or_abort(&s.yrdy_bar, (uint32_t)(c & 1), &s.abort_flag, P.wait_limit)) { fail = 1; break; }
                     tc_fence_after();
                     // y = Atil V + Rhat Sbf  (value columns 0..31 -> lo lanes, 32..63 -> hi lanes)
 #pragma unroll
@@ -198,18 +223,19 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 if (c + 2 < n) {
                     uint64_t *last = full ? &s.y_bar : &s.u_bar[c & 1];
                     const uint32_t par = full ? (uint32_t)(c & 1) : (uint32_t)((c >> 1) & 1);
-                    if (!mbar_wait_or_abort(last, par, &s.abort_flag)) { fail = 1; break; }
+                    if (!mbar_wait_or_abort(last, par, &s.abort_flag, P.wait_limit)) { fail = 1; break; }
                     pending = -1;
                     tma_store_wait_read();
                     issue_load(c + 2);
-                    issued = c + 2;
                 }
             }
             if (fail) {
                 atomicExch(&s.abort_flag, 1);
                 if (P.status) atomicOr(P.status, 1);
                 // let whatever is in flight finish before shared and tensor memory go away
-                for (int q = 0; q <= issued; q++) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1), 200000u);
+                // (the last load issued on each of the two stages; earlier phases of a barrier are over)
+                for (int q = issued > 0 ? issued - 1 : 0; q <= issued; q++)
+                    if (q != P.skip_load) mbar_wait(&s.load_bar[q & 1], (uint32_t)((q >> 1) & 1), 200000u);
                 if (pending >= 0) {
                     mbar_wait(&s.u_bar[pending & 1], (uint32_t)((pending >> 1) & 1), 200000u);
                     if (full) mbar_wait(&s.score_bar, (uint32_t)(pending & 1), 200000u);
@@ -235,13 +261,14 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         for (int q = 0; q < 16; q++) {
             const int vc = vcol0 + q;
             const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-            S[q] = P.state_in ? P.state_in[sbase + idx] : 0.f;
+            if (P.gstart) S[q] = P.gstart[(size_t)unit * 4096 + row * 64 + vc];
+            else S[q] = (P.state_in && !summary) ? P.state_in[sbase + idx] : 0.f;
         }
-        float uu[4], lwc[4], wc[4];
+        float dprod = 1.f;      // summary pass: decay of the whole group for key channel `row`
+        float lwc[4], wc[4];
         bool steep_static = false;
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) {
-            uu[ch] = __bfloat162float(P.u[h * 64 + ch0 + ch]);
             bool live;
             lwc[ch] = PER_TOKEN ? 0.f : log2_decay(P.wvec[h * 64 + ch0 + ch], P.w_kind, live);
             wc[ch] = exp2f(lwc[ch]);
@@ -252,14 +279,15 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
         // Operand pass for chunk j: scaled r/k tiles in place in stage j&1, x, khat[j&1], the
         // score-diagonal partials and the chunk decay.  Contains one barrier of the compute warps.
-        auto prep = [&](int j) -> bool {
+        auto prep = [&](int j) -> bool {          // j: local chunk index
+            const int jg = j0 + j;
             Tile *in = s.in[j & 1];
             Tile &khat = s.khat[j & 1];
             float c[4][4];
             DecayT<4> D;
             float other_l2[4];
             bool mild;
-            if (!PER_TOKEN && (j + 1) * CH <= P.T) {
+            if (!PER_TOKEN && (jg + 1) * CH <= P.T) {
                 // static decay, whole chunk in range: closed form, nothing to scan or exchange
                 decay_static(lwc, wc, tok0, c, D, other_l2);
                 mild = mild_static;
@@ -267,7 +295,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const int t = tok0 + i;
-                    const bool valid = j * CH + t < P.T;
+                    const bool valid = jg * CH + t < P.T;
                     if (PER_TOKEN) {
                         float x[4];
                         unpack4(ld_tile4(in[3], t, cc, hf), x);
@@ -285,13 +313,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 mild = decay_scan8(c, warp, lane, &s.wtot[0][0], D, other_l2, [](bool p) { return compute_sync_or(p); });
             }
             if (tid == 0) s.mild_flag[j & 1] = mild;
-            {
-                // Debug stamp "decay scan done".  The clock read is also a scheduling boundary: without
-                // it the loads of the r-side stage are hoisted above the scan and, under the 96-register
-                // cap of two 288-thread CTAs per SM, the pass spills inside the serial loop (+30 % time).
-                const long long t_scan = clock64();
-                if (P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2 + 1) P.timeline[5] = t_scan;
-            }
+            // The warp reconverges here before it touches the r and k tiles.  The barrier also keeps the
+            // tile loads below the decay scan: hoisted above it they push the pass over the 96 registers
+            // that two 288-thread CTAs per SM allow, and it spills inside the serial loop.
+            __syncwarp();
+            // the bonus u of the thread's 4 channels (read again for every chunk: registers are scarce here)
+            float uu[4];
+            if (full) unpack4(__ldg(reinterpret_cast<const uint2 *>(P.u + h * 64 + ch0)), uu);
             float other[4];          // 2^{total of the other block}
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
@@ -300,7 +328,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 for (int ch = 0; ch < 4; ch++) {
                     const float d = exp2f(D.e[ch]) * other[ch];
                     s.dvec[j & 1][ch0 + ch] = d;
-                    if (P.dchunk) P.dchunk[((size_t)bh * n + j) * 64 + ch0 + ch] = d;
+                    if (P.dchunk) P.dchunk[((size_t)bh * P.nchunk + jg) * 64 + ch0 + ch] = d;
                 }
             }
             if (mild) {
@@ -452,19 +480,21 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         };
         // a wait of a compute thread; running out of patience ends everybody else's waits too
         auto cwait = [&](uint64_t *bar, uint32_t parity) {
-            if (mbar_wait_or_abort(bar, parity, &s.abort_flag)) return true;
+            if (mbar_wait_or_abort(bar, parity, &s.abort_flag, P.wait_limit)) return true;
             *reinterpret_cast<volatile int *>(&s.abort_flag) = 1;
             return false;
         };
         // bf16 copy of the state at the start of chunk jn: operand of rhat*S, checkpoint
+        // (jn local; the state at the end of a group is the next group's first checkpoint, written there)
         auto publish_state = [&](int jn) {
             const uint4 q0 = pack8(S), q1 = pack8(S + 8);
             if (full && jn < n) {
                 st_tile(s.sbf, row, (vcol0 >> 3), q0);
                 st_tile(s.sbf, row, (vcol0 >> 3) + 1, q1);
             }
-            if (P.ckpt) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.ckpt + (((size_t)bh * (n + 1) + jn) * 64 + row) * 64 + vcol0);
+            if (P.ckpt && (jn < n || j0 + n == P.nchunk)) {
+                uint4 *dst = reinterpret_cast<uint4 *>(
+                    P.ckpt + (((size_t)bh * (P.nchunk + 1) + j0 + jn) * 64 + row) * 64 + vcol0);
                 dst[0] = q0;
                 dst[1] = q1;
             }
@@ -474,8 +504,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         // state / masked scores that the y product of chunk j+1 needs.  j = -1 is the prologue.
         bool mild_next = false;      // chunk j+1 is mild
         for (int j = -1; j < n; j++) {
-            const bool stamp = P.timeline != nullptr && tid == 0 && blockIdx.x == gridDim.x / 2 && j == n / 2;
-            if (stamp) P.timeline[0] = clock64();
             // (P) operands of chunk j+1
             if (j + 1 < n) {
                 if (!cwait(&s.load_bar[(j + 1) & 1], (uint32_t)(((j + 1) >> 1) & 1))) fail = 1;
@@ -484,7 +512,6 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 compute_sync();
                 if (tid == 0) mbar_arrive(&s.ops_bar[(j + 1) & 1]);
             }
-            if (stamp) P.timeline[1] = clock64();
             // (E) y of chunk j
             if (j >= 0 && full) {
                 if (!cwait(&s.y_bar, (uint32_t)(j & 1))) fail = 1;
@@ -492,14 +519,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 float yv[16];
                 tmem_ld16(tmem_addr(tm, lane_base, COL_Y + 16 * wg), yv);
                 tmem_ld_wait();
-                const int t = j * CH + row;
+                const int t = (j0 + j) * CH + row;
                 if (t < P.T) {
                     uint4 *dst = reinterpret_cast<uint4 *>(P.y + ((size_t)b * P.T + t) * C + h * 64 + vcol0);
                     dst[0] = pack8(yv);
                     dst[1] = pack8(yv + 8);
                 }
             }
-            if (stamp) P.timeline[2] = clock64();
             // (S) state at the start of chunk j+1:  S = d_j S + U_j
             if (j >= 0) {
                 if (!cwait(&s.u_bar[j & 1], (uint32_t)((j >> 1) & 1))) fail = 1;
@@ -508,11 +534,11 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 tmem_ld16(tmem_addr(tm, lane_base, COL_U + 32 * (j & 1) + 16 * wg), uacc);
                 tmem_ld_wait();
                 const float d = s.dvec[j & 1][row];
+                if (summary) dprod *= d;
 #pragma unroll
                 for (int q = 0; q < 16; q++) S[q] = fmaf(d, S[q], uacc[q]);
             }
             publish_state(j + 1);
-            if (stamp) P.timeline[3] = clock64();
             // (M) masked scores of chunk j+1: lo lanes own columns 0..31 of token row t, hi lanes 32..63;
             // this warp group 16 of them
             if (j + 1 < n && full) {
@@ -544,13 +570,17 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 if (any) { fail = 1; break; }
             }
             if (j + 1 < n && full && tid == 0) mbar_arrive(&s.yrdy_bar);
-            if (stamp) P.timeline[4] = clock64();
         }
         if (fail) {
             if (tid == 0) {
                 atomicExch(&s.abort_flag, 1);
                 if (P.status) atomicOr(P.status, 1);
             }
+        } else if (summary) {
+            float4 *dst = reinterpret_cast<float4 *>(P.gU + (size_t)unit * 4096 + row * 64 + vcol0);
+#pragma unroll
+            for (int q = 0; q < 4; q++) dst[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+            if (vcol0 == 0) P.gD[(size_t)unit * 64 + row] = dprod;
         } else if (P.state_out) {
 #pragma unroll
             for (int q = 0; q < 16; q++) {
@@ -567,22 +597,157 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
 static_assert(sizeof(FwdSmem) + 1024 <= 115712, "two CTAs per SM need <= 113 KiB each");
 
+// Pass B of the time-group scheme: for every chain the elementwise recurrence over its groups,
+//   S <- init;  for each group g (forward order, or reverse for the gradient):  starts[g] = S;  S = d_g * S + U_g
+// and the final S.  One thread per state element; the loads do not depend on S, so the compiler
+// is free to run them ahead.  `init` / `final_out` are in the caller's state layout (NULL init = zeros).
+__global__ void __launch_bounds__(256)
+k_group_scan(const float *__restrict__ U, const float *__restrict__ dG, const float *__restrict__ init,
+             float *__restrict__ starts, float *__restrict__ final_out, int G, int layout, int reverse) {
+    const int idx = blockIdx.x * 256 + threadIdx.x, bh = idx >> 12, e = idx & 4095, row = e >> 6, vc = e & 63;
+    const size_t lidx = (size_t)bh * 4096 + (layout == WKV_STATE_KV ? e : vc * 64 + row);
+    float S = init ? init[lidx] : 0.f;
+#pragma unroll 4
+    for (int step = 0; step < G; step++) {
+        const size_t u = (size_t)bh * G + (reverse ? G - 1 - step : step);
+        starts[u * 4096 + e] = S;
+        S = fmaf(dG[u * 64 + row], S, U[u * 4096 + e]);
+    }
+    if (final_out) final_out[lidx] = S;
+}
+
+// Self-test of the bounded waits: one CTA, one mbarrier on which nobody ever arrives.  Warp 0
+// waits on it with the plain bounded wait; when that runs out it raises the CTA's abort flag,
+// which must end the (much longer) abortable wait of warp 1.  Status bits: 16 = the plain wait
+// gave up, 32 = the abortable wait gave up.
+__global__ void __launch_bounds__(64) k_selftest_wait(int *status, uint32_t limit) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        if (!mbar_wait(&bar, 0, limit)) {
+            if (threadIdx.x == 0) {
+                atomicOr(status, 16);
+                *reinterpret_cast<volatile int *>(&abort_flag) = 1;
+            }
+        }
+    } else {
+        if (!mbar_wait_or_abort(&bar, 0, &abort_flag, limit * 64u) && threadIdx.x == 32) atomicOr(status, 32);
+    }
+}
+
 }  // namespace
+
+int selftest_wait(int *status, uint32_t limit, cudaStream_t stream) {
+    if (limit == 0 || limit > 100000u) return WKV_ERR_SHAPE;     // a test: keep it short
+    k_selftest_wait<<<1, 64, 0, stream>>>(status, limit);
+    return launch_status();
+}
 
 // ---------------------------------------------------------------------------
 // host side
 
-bool chunked_supported(const wkv_args_t *a, bool per_token_w) {
-    if (a->dtype != WKV_BF16 || a->N != 64 || a->T <= 0) return false;
-    if (per_token_w && a->w_kind != WKV_W_RAW) return false;  // fp32 ew tensor: scalar path
-    return true;
+bool chunked_supported(const wkv_args_t *a, bool) {
+    return a->dtype == WKV_BF16 && a->N == 64 && a->T > 0;
 }
 
-// workspace layout: [0,256) status words ; then what the call needs
-size_t chunked_forward_workspace(const wkv_args_t *, bool) { return 256; }
+// The per-token kernels read the decay activation x as a bf16 [B,T,C] tensor.  A caller that
+// holds the fp32 ew = -exp(x) instead (RWKV-v6/src/module/TimeMix.py:49-51) gets x = log(-ew)
+// rebuilt in bf16 first.  That is exact when ew was computed from a bf16 x, as that wrapper does
+// (the round trip is off by ~1e-7 relative, far inside half a bf16 step); an ew that never was
+// a bf16 x is seen at bf16 resolution of x -- the resolution the activation has in bf16 training.
+namespace {
+__global__ void __launch_bounds__(256) k_ew_to_x(const float4 *__restrict__ ew, uint2 *__restrict__ x, size_t n4) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n4) return;
+    const float4 e = ew[i];
+    x[i] = make_uint2(pack2(logf(-e.x), logf(-e.y)), pack2(logf(-e.z), logf(-e.w)));
+}
+}  // namespace
 
-int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, cudaStream_t stream) {
-    const int B = a->B, T = a->T, H = a->H, C = H * 64;
+size_t chunked_wconv_bytes(const wkv_args_t *a, bool per_token_w) {
+    if (!per_token_w || a->w_kind != WKV_W_NEGEXP) return 0;
+    return (((size_t)a->B * a->T * a->H * 64 * 2) + 255) & ~(size_t)255;
+}
+
+int chunked_convert_w(wkv_args_t *a, bool per_token_w, void *scratch, cudaStream_t stream) {
+    if (!per_token_w || a->w_kind != WKV_W_NEGEXP) return WKV_OK;
+    const size_t n4 = (size_t)a->B * a->T * a->H * 16;
+    k_ew_to_x<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float4 *)a->w, (uint2 *)scratch, n4);
+    a->w = scratch;
+    a->w_kind = WKV_W_RAW;
+    return launch_status();
+}
+
+int device_sm_count() {
+    static int sms[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = __atomic_load_n(&sms[dev], __ATOMIC_RELAXED);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        __atomic_store_n(&sms[dev], n, __ATOMIC_RELAXED);
+    }
+    return n;
+}
+
+namespace chunked {
+
+GroupPlan plan_groups(int BH, int nchunk, int requested) {
+    int G = 1;
+    if (requested > 0) {
+        G = requested < nchunk ? requested : nchunk;
+    } else if (nchunk >= 8) {
+        // two CTAs of the serial kernels fit on an SM; split only when the chains alone leave
+        // most of those slots empty, and keep every group at two chunks or more
+        const int slots = 2 * device_sm_count();
+        if (BH * 5 < slots * 2) {
+            G = slots / BH;
+            if (G > nchunk / 2) G = nchunk / 2;
+        }
+    }
+    if (G < 1) G = 1;
+    GroupPlan P;
+    P.L = (nchunk + G - 1) / G;
+    P.G = (nchunk + P.L - 1) / P.L;
+    return P;
+}
+
+GroupLayout group_layout(size_t units) {
+    auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    GroupLayout L;
+    L.gU = 0;
+    L.gD = al(units * 4096 * 4);
+    L.gstart = L.gD + al(units * 64 * 4);
+    L.total = L.gstart + al(units * 4096 * 4);
+    return L;
+}
+
+int launch_group_scan(const void *group_ws, int BH, int G, const float *init, float *final_out, int layout,
+                      bool reverse, cudaStream_t stream) {
+    const GroupLayout GL = group_layout((size_t)BH * G);
+    const char *g = (const char *)group_ws;
+    k_group_scan<<<BH * 16, 256, 0, stream>>>((const float *)(g + GL.gU), (const float *)(g + GL.gD), init,
+                                              (float *)(g + GL.gstart), final_out, G, layout, reverse ? 1 : 0);
+    return launch_status();
+}
+
+}  // namespace chunked
+
+// workspace layout: [0,256) status words; then the time-group buffers when the chains are split
+size_t chunked_forward_workspace(const wkv_args_t *a, bool per_token_w) {
+    const GroupPlan gp = plan_groups(a->B * a->H, (a->T + CH - 1) / CH, a->time_groups);
+    return 256 + (gp.G > 1 ? group_layout((size_t)a->B * a->H * gp.G).total : 0) + chunked_wconv_bytes(a, per_token_w);
+}
+
+int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, void *group_ws,
+                         const ChunkedTest &tst, cudaStream_t stream) {
+    const int B = a->B, T = a->T, H = a->H, C = H * 64, BH = B * H;
     CUtensorMap mr, mk, mv, mw;
     if (!make_btc_map(&mr, a->r, B, T, C) || !make_btc_map(&mk, a->k, B, T, C) ||
         !make_btc_map(&mv, a->v, B, T, C))
@@ -594,13 +759,46 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     }
     FwdParams p;
     p.T = T; p.H = H; p.nchunk = (T + CH - 1) / CH; p.layout = a->state_layout; p.w_kind = a->w_kind;
-    p.state_only = a->y == nullptr;
+    const GroupPlan gp = plan_groups(BH, p.nchunk, a->time_groups);
+    p.G = gp.G; p.L = gp.L;
     p.u = (const __nv_bfloat16 *)a->u;
     p.wvec = per_token_w ? nullptr : (const float *)a->w;
-    p.state_in = a->state_in; p.state_out = a->state_out;
+    p.status = (int *)a->workspace;
+    p.wait_limit = tst.wait_limit;
+    p.skip_load = tst.kernel == 0 ? tst.skip_load : -1;
+    const size_t smem = sizeof(FwdSmem) + 1024;
+    const int mode = a->y == nullptr ? FWD_STATES : FWD_FULL;
+    using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                          const CUtensorMap, const FwdParams);
+    static const Kern kerns[2][3] = {
+        {k_chunk_fwd<false, FWD_FULL>, k_chunk_fwd<false, FWD_STATES>, k_chunk_fwd<false, FWD_SUMMARY>},
+        {k_chunk_fwd<true, FWD_FULL>, k_chunk_fwd<true, FWD_STATES>, k_chunk_fwd<true, FWD_SUMMARY>}};
+    static unsigned char attr_done[2][3][64];
+    const int pt = per_token_w ? 1 : 0;
+    CUtensorMap mrh = mr;
+
+    const GroupLayout GL = group_layout((size_t)BH * gp.G);
+    char *g = (char *)group_ws;
+    if (gp.G > 1) {
+        // A: what every group adds to the state, from zero
+        if (!set_max_smem_once(kerns[pt][FWD_SUMMARY], (int)smem, attr_done[pt][FWD_SUMMARY])) return WKV_ERR_LAUNCH;
+        p.state_in = nullptr; p.gstart = nullptr; p.state_out = nullptr;
+        p.gU = (float *)(g + GL.gU); p.gD = (float *)(g + GL.gD);
+        p.y = nullptr; p.ckpt = nullptr; p.dchunk = nullptr;
+        kerns[pt][FWD_SUMMARY]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
+        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        // B: the state at the start of every group, and the state after the segment
+        if (launch_group_scan(g, BH, gp.G, a->state_in, a->state_out, a->state_layout, false, stream) != WKV_OK)
+            return WKV_ERR_LAUNCH;
+    }
+    // C (or the whole job when the chains are not split)
+    if (!set_max_smem_once(kerns[pt][mode], (int)smem, attr_done[pt][mode])) return WKV_ERR_LAUNCH;
+    p.state_in = a->state_in;
+    p.gstart = gp.G > 1 ? (const float *)(g + GL.gstart) : nullptr;
+    p.state_out = gp.G > 1 ? nullptr : a->state_out;
+    p.gU = nullptr; p.gD = nullptr;
     p.y = (__nv_bfloat16 *)a->y;
     const CkptLayout CL = ckpt_layout(B, T, H);
-    CUtensorMap mrh = mr;
     p.ckpt = nullptr; p.dchunk = nullptr;
     if (state_ckpt) {
         char *ck = (char *)state_ckpt;
@@ -608,19 +806,19 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
         p.dchunk = (float *)(ck + CL.dchunk);
         if (!make_btc_map(&mrh, ck + CL.rhat, B, T, C)) return WKV_ERR_LAUNCH;
     }
-    p.status = (int *)a->workspace;
-    p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)((char *)a->workspace + 64) : nullptr;
-    const size_t smem = sizeof(FwdSmem) + 1024;
-    auto kern = per_token_w ? k_chunk_fwd<true> : k_chunk_fwd<false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return WKV_ERR_LAUNCH;
-    kern<<<B * H, FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
+    kerns[pt][mode]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
     return launch_status();
 }
 
-int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
-    if (cudaMemsetAsync(a->workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
-    return chunked_forward_impl(a, per_token_w, a->state_ckpt, stream);
+int chunked_forward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &tst, cudaStream_t stream) {
+    wkv_args_t a = *a0;
+    if (cudaMemsetAsync(a.workspace, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
+    const size_t conv = chunked_wconv_bytes(&a, per_token_w);
+    if (conv) {   // the converted decay tensor sits at the end of the workspace
+        const int err = chunked_convert_w(&a, per_token_w, (char *)a.workspace + chunked_forward_workspace(a0, per_token_w) - conv, stream);
+        if (err != WKV_OK) return err;
+    }
+    return chunked_forward_impl(&a, per_token_w, a.state_ckpt, (char *)a.workspace + 256, tst, stream);
 }
 
 }  // namespace wkv

@@ -15,6 +15,7 @@ constexpr int CH = 64;            // tokens per chunk
 constexpr int HB = 32;            // tokens per block
 constexpr float LW_FLOOR = -5.298317367f;  // log(0.005)
 
+
 struct __align__(16) Tile { unsigned char b[TILE_BYTES]; };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -224,10 +225,60 @@ inline CkptLayout ckpt_layout(int B, int T, int H) {
     return L;
 }
 
+// Time groups (see the head of wkv56_chunked.cu): G groups of L consecutive chunks per chain.
+struct GroupPlan {
+    int G, L;
+};
+// requested: 0 = decide from the number of chains and the device's SM count, 1 = never split,
+// > 1 = that many groups (at most one per chunk)
+GroupPlan plan_groups(int BH, int nchunk, int requested);
+
+// Scratch of the time-group passes, for `units` = chains * G (all fp32, state matrices [key,value]):
+//   gU      [units, 64, 64]  what a group adds to the state (gradient) starting from zero
+//   gD      [units, 64]      decay of the whole group per key channel
+//   gstart  [units, 64, 64]  state (gradient) a group starts from
+struct GroupLayout {
+    size_t gU, gD, gstart, total;
+};
+GroupLayout group_layout(size_t units);
+int launch_group_scan(const void *group_ws, int BH, int G, const float *init, float *final_out, int layout,
+                      bool reverse, cudaStream_t stream);
+
 }  // namespace chunked
 
+// What only the wait-timeout self-test changes: how many polls a device-side wait makes before it
+// gives up, and one TMA load that is deliberately never issued (kernel: 0 forward, 1 dS scan,
+// 2 per-chunk backward; skip_load: local chunk / step index, -1 = none).
+struct ChunkedTest {
+    uint32_t wait_limit = 4000000u;
+    int kernel = -1;
+    int skip_load = -1;
+};
+
+int device_sm_count();
+// v6 with the fp32 ew = -exp(x) encoding: bytes of, and conversion into, a bf16 x tensor (a no-op otherwise)
+size_t chunked_wconv_bytes(const wkv_args_t *a, bool per_token_w);
+int chunked_convert_w(wkv_args_t *a, bool per_token_w, void *scratch, cudaStream_t s);
+int selftest_wait(int *status, uint32_t limit, cudaStream_t s);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: set it on
+// the first launch on each device only (`done` is the call site's own per-device record)
+template <class K>
+inline bool set_max_smem_once(K kern, int bytes, unsigned char (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    if (dev >= 0 && dev < 64 && __atomic_load_n(&done[dev], __ATOMIC_ACQUIRE)) return true;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    if (dev >= 0 && dev < 64) __atomic_store_n(&done[dev], (unsigned char)1, __ATOMIC_RELEASE);
+    return true;
+}
+
 // `state_ckpt` (laid out as chunked::CkptLayout, or NULL) receives what the backward kernels
-// reuse from the forward pass; y is not produced when `y` in `a` is NULL
-int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, cudaStream_t s);
+// reuse from the forward pass; y is not produced when `y` in `a` is NULL; `group_ws` is
+// chunked::group_layout() bytes of scratch, used when the chains are split into time groups
+int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt, void *group_ws,
+                         const ChunkedTest &tst, cudaStream_t s);
+int chunked_forward(const wkv_args_t *a, bool per_token_w, const ChunkedTest &tst, cudaStream_t s);
+int chunked_backward(const wkv_args_t *a, bool per_token_w, const ChunkedTest &tst, cudaStream_t s);
 
 }  // namespace wkv

@@ -24,7 +24,6 @@
 //
 // Math reference: RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:70-293 (what the
 // gradients are), RWKV-v6/src/module/rwkv_inner.py:48-113 (the chunked form).
-#include <cstdlib>
 #include <type_traits>
 
 #include "wkv56_chunked.cuh"
@@ -52,12 +51,19 @@ struct DscanSmem {
 
 struct DscanParams {
     int T, H, nchunk, layout;
+    int G, L;             // time groups per chain, chunks per group (see wkv56_chunked.cu)
+    int summary;          // pass A: zero start, the only outputs are gU / gD
     const float *dchunk;  // [B*H, nchunk, 64] decay of each whole chunk (from the forward kernel)
-    const float *gstate_out;
-    float *gstate_in;
+    const float *gstate_out;   // G == 1: the caller's gradient w.r.t. the state after the segment
+    const float *gstart;       // G > 1, pass C: [B*H*G, 64, 64] gradient at the END of every group ([key,value])
+    float *gstate_in;          // G == 1 only (with G > 1 the group scan writes it)
+    float *gU;                 // pass A: [B*H*G, 64, 64] gradient a group builds from zero
+    float *gD;                 // pass A: [B*H*G, 64] decay of a whole group per key channel
     __nv_bfloat16 *dck;  // [B*H, nchunk+1, 64, 64]; entry j+1 = dL/dS at the end of chunk j
     float *e0;           // [B*H, nchunk+1, 64]; entry j = sum_v S_j[k,v] D_j[k,v] at chunk boundary j
     int *status;
+    uint32_t wait_limit;
+    int skip_load;        // -1; a step index leaves that step's TMA loads out (wait-timeout test)
 };
 
 // Reverse scan of the state gradient:  D_j = d_j D_{j+1} + (r e^{cp})^T gy  over the chunks j of a
@@ -73,14 +79,22 @@ struct DscanParams {
 // it consumes and releases buffers back to warp 4.  A closing step i = n writes E_0 and D_0.
 // Every wait is bounded; a warp whose wait runs out flags the status word and leaves the loop,
 // which makes the waits of the others run out in turn.
+//
+// With time groups a CTA handles the chunks [j0, j0+n) of its chain: as a summary pass (from a
+// zero gradient; no S tiles, no checkpoints, outputs gU / gD) or as the full pass from the
+// gradient the group scan computed for the end of its group.  The closing step (E and D at the
+// chain's first chunk boundary) belongs to the first group alone.
 __global__ void __launch_bounds__(160)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant__ CUtensorMap map_gy,
               const __grid_constant__ CUtensorMap map_s, const DscanParams P) {
     extern __shared__ unsigned char smem_raw[];
     DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int bh = blockIdx.x, b = bh / P.H, h = bh % P.H;
-    const int n = P.nchunk;
+    const int unit = blockIdx.x, bh = unit / P.G, grp = unit - bh * P.G, b = bh / P.H, h = bh % P.H;
+    const int j0 = grp * P.L, n = min(P.L, P.nchunk - j0), N = P.nchunk;
+    const bool summary = P.summary != 0;
+    const int nsteps = n + ((!summary && grp == 0) ? 1 : 0);    // + the closing step
+    const uint32_t LIM = P.wait_limit;
 
     if (tid == 0) {
         for (int q = 0; q < DS_STAGES; q++) { mbar_init(&s.load_bar[q], 1); mbar_init(&s.stage_free[q], 4); }
@@ -98,25 +112,27 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
 
     if (warp == 4) {
         if (lane == 0) {
+            int issued = -1, landed = -1, mma_issued = -1;
             auto issue_load = [&](int i) {
-                const int st = i % DS_STAGES, j = n - 1 - i;
-                mbar_expect_tx(&s.load_bar[st], i < n ? 3 * TILE_BYTES + CH * 4 : TILE_BYTES);
+                if (i == P.skip_load) return;
+                const int st = i % DS_STAGES, j = j0 + n - 1 - i;      // global chunk of step i
+                mbar_expect_tx(&s.load_bar[st], (i < n ? 2 * TILE_BYTES + CH * 4 : 0) + (summary ? 0 : TILE_BYTES));
                 if (i < n) {
                     tma_load_3d(&s.in[st][0], &map_rh, &s.load_bar[st], h * 64, j * CH, b);
                     tma_load_3d(&s.in[st][1], &map_gy, &s.load_bar[st], h * 64, j * CH, b);
-                    bulk_load_1d(s.dvec[st], P.dchunk + ((size_t)bh * n + j) * 64, CH * 4, &s.load_bar[st]);
+                    bulk_load_1d(s.dvec[st], P.dchunk + ((size_t)bh * N + j) * 64, CH * 4, &s.load_bar[st]);
                 }
-                tma_load_3d(&s.in[st][2], &map_s, &s.load_bar[st], 0, 0, bh * (n + 1) + (n - i));
+                if (!summary) tma_load_3d(&s.in[st][2], &map_s, &s.load_bar[st], 0, 0, bh * (N + 1) + j + 1);
+                issued = i;
             };
-            int issued = -1, landed = -1, mma_issued = -1;
-            for (int i = 0; i < DS_STAGES && i <= n; i++) { issue_load(i); issued = i; }
+            for (int i = 0; i < DS_STAGES && i < nsteps; i++) issue_load(i);
             const uint32_t id = make_idesc(64, 32, true, true);
-            for (int i = 0; i <= n && !fail; i++) {
-                if (!mbar_wait(&s.load_bar[i % DS_STAGES], load_parity(i))) { fail = 1; break; }
+            for (int i = 0; i < nsteps && !fail; i++) {
+                if (!mbar_wait(&s.load_bar[i % DS_STAGES], load_parity(i), LIM)) { fail = 1; break; }
                 landed = i;
                 if (i < n) {
                     // buffer i&1 held the product of step i-2
-                    if (i >= 2 && !mbar_wait(&s.prod_free[i & 1], prod_parity(i - 2))) { fail = 1; break; }
+                    if (i >= 2 && !mbar_wait(&s.prod_free[i & 1], prod_parity(i - 2), LIM)) { fail = 1; break; }
                     tc_fence_after();
                     Tile *in = s.in[i % DS_STAGES];
                     // value columns 0..31 into lanes 0..15 of each quarter, 32..63 into lanes 16..31
@@ -130,15 +146,15 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
                     mma_issued = i;
                 }
                 // the stage of step i-1 goes to step i-1+DS_STAGES as soon as the scan warps are done with it
-                if (i >= 1 && i + DS_STAGES - 1 <= n) {
-                    if (!mbar_wait(&s.stage_free[(i - 1) % DS_STAGES], load_parity(i - 1))) { fail = 1; break; }
+                if (i >= 1 && i + DS_STAGES - 1 < nsteps) {
+                    if (!mbar_wait(&s.stage_free[(i - 1) % DS_STAGES], load_parity(i - 1), LIM)) { fail = 1; break; }
                     issue_load(i + DS_STAGES - 1);
-                    issued = i + DS_STAGES - 1;
                 }
             }
             if (fail) {
                 // let everything in flight land before the shared and tensor memory go away
-                for (int q = landed + 1; q <= issued; q++) mbar_wait(&s.load_bar[q % DS_STAGES], load_parity(q));
+                for (int q = landed + 1; q <= issued; q++)
+                    if (q != P.skip_load) mbar_wait(&s.load_bar[q % DS_STAGES], load_parity(q), 200000u);
                 if (mma_issued >= 0) mbar_wait(&s.mma_bar[mma_issued & 1], prod_parity(mma_issued), 100000u);
                 if (mma_issued >= 1) mbar_wait(&s.mma_bar[(mma_issued - 1) & 1], prod_parity(mma_issued - 1), 100000u);
                 if (P.status) atomicOr(P.status, 2);
@@ -157,14 +173,16 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
         for (int q = 0; q < 32; q++) {
             const int vc = vcol0 + q;
             const size_t idx = P.layout == WKV_STATE_KV ? (size_t)row * 64 + vc : (size_t)vc * 64 + row;
-            v[q] = P.gstate_out ? P.gstate_out[sbase + idx] : 0.f;
+            if (P.gstart) v[q] = P.gstart[(size_t)unit * 4096 + row * 64 + vc];
+            else v[q] = (P.gstate_out && !summary) ? P.gstate_out[sbase + idx] : 0.f;
         }
-        for (int i = 0; i <= n; i++) {
-            const int st = i % DS_STAGES, j = n - 1 - i;
+        float dprod = 1.f;      // summary pass: decay of the whole group for key channel `row`
+        for (int i = 0; i < nsteps; i++) {
+            const int st = i % DS_STAGES, j = j0 + n - 1 - i;       // global chunk of step i
             Tile *in = s.in[st];
-            if (!mbar_wait(&s.load_bar[st], load_parity(i))) { fail = 1; break; }
+            if (!mbar_wait(&s.load_bar[st], load_parity(i), LIM)) { fail = 1; break; }
             // with D_{j+1} in hand: its checkpoint and E_{j+1} ...
-            {
+            if (!summary) {
                 float dot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int c8 = 0; c8 < 4; c8++) {
@@ -175,10 +193,10 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
                 }
                 float e = (dot[0] + dot[1]) + (dot[2] + dot[3]);
                 e += __shfl_xor_sync(0xffffffffu, e, 16);
-                if (active) P.e0[((size_t)bh * (n + 1) + (j + 1)) * 64 + row] = e;
+                if (active) P.e0[((size_t)bh * (N + 1) + (j + 1)) * 64 + row] = e;
             }
             if (i == n) {   // closing step: D_0 is the state gradient
-                if (P.gstate_in) {
+                if (P.gstate_in && P.G == 1) {
 #pragma unroll
                     for (int q = 0; q < 32; q++) {
                         const int vc = vcol0 + q;
@@ -188,13 +206,13 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
                 }
                 break;
             }
-            {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (n + 1) + j + 1) * 64 + row) * 64 + vcol0);
+            if (!summary) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.dck + (((size_t)bh * (N + 1) + j + 1) * 64 + row) * 64 + vcol0);
 #pragma unroll
                 for (int c8 = 0; c8 < 4; c8++) dst[c8] = pack8(v + 8 * c8);
             }
             // ... then D_j = d_j D_{j+1} + U_j
-            if (!mbar_wait(&s.mma_bar[i & 1], prod_parity(i))) { fail = 1; break; }
+            if (!mbar_wait(&s.mma_bar[i & 1], prod_parity(i), LIM)) { fail = 1; break; }
             tc_fence_after();
             {
                 float u[32];
@@ -202,6 +220,7 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
                 tmem_ld16(tmem_addr(tm, lane_base, 32 * (i & 1) + 16), u + 16);
                 tmem_ld_wait();
                 const float d = s.dvec[st][row];
+                dprod *= d;
 #pragma unroll
                 for (int q = 0; q < 32; q++) v[q] = fmaf(d, v[q], u[q]);
             }
@@ -210,7 +229,14 @@ k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant_
             __syncwarp();
             if (lane == 0) { mbar_arrive(&s.prod_free[i & 1]); mbar_arrive(&s.stage_free[st]); }
         }
-        if (fail && lane == 0 && P.status) atomicOr(P.status, 2);
+        if (fail) {
+            if (lane == 0 && P.status) atomicOr(P.status, 2);
+        } else if (summary) {
+            float4 *dst = reinterpret_cast<float4 *>(P.gU + (size_t)unit * 4096 + row * 64 + vcol0);
+#pragma unroll
+            for (int q = 0; q < 8; q++) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            if (active) P.gD[(size_t)unit * 64 + row] = dprod;
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -250,7 +276,8 @@ struct BwdParams {
     float *gu_part;   // [B*H, nchunk, 64]
     float *gw_part;   // v5 only: [B*H, nchunk, 64]
     int *status;
-    long long *timeline;  // optional: clock stamps of one CTA (phase boundaries), or NULL
+    uint32_t wait_limit;
+    int skip_load;        // -1; a chunk index whose CTAs leave their TMA loads out (wait-timeout test)
 };
 
 // tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31.
@@ -327,21 +354,22 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         if (tid == 0 && P.status) atomicOr(P.status, 8);
         return;
     }
-    const bool stamp = P.timeline != nullptr && blockIdx.x == gridDim.x / 2 && tid == 0;
-    if (stamp) P.timeline[0] = clock64();
+    const uint32_t LIM = P.wait_limit;
     if (tid == 0) {
         mbar_init(&s.load_bar, 1);
         // lane 0 of every warp commits to every barrier, whether or not it issued a share of the group
         mbar_init(&s.bar_early, 8); mbar_init(&s.bar_score, 8); mbar_init(&s.bar_grad, 8); mbar_init(&s.bar_gv, 8);
         fence_mbar_init();
-        mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
-        tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
-        tma_load_3d(&s.in[T_K], &map_k, &s.load_bar, h * 64, j * CH, b);
-        tma_load_3d(&s.in[T_V], &map_v, &s.load_bar, h * 64, j * CH, b);
-        if (PER_TOKEN) tma_load_3d(&s.in[T_W], &map_w, &s.load_bar, h * 64, j * CH, b);
-        tma_load_3d(&s.in[T_GY], &map_gy, &s.load_bar, h * 64, j * CH, b);
-        tma_load_3d(&s.in[T_S], &map_s, &s.load_bar, 0, 0, bh * (n + 1) + j);
-        tma_load_3d(&s.in[T_D], &map_d, &s.load_bar, 0, 0, bh * (n + 1) + j + 1);
+        if (j != P.skip_load) {
+            mbar_expect_tx(&s.load_bar, (PER_TOKEN ? 7 : 6) * TILE_BYTES);
+            tma_load_3d(&s.in[T_R], &map_r, &s.load_bar, h * 64, j * CH, b);
+            tma_load_3d(&s.in[T_K], &map_k, &s.load_bar, h * 64, j * CH, b);
+            tma_load_3d(&s.in[T_V], &map_v, &s.load_bar, h * 64, j * CH, b);
+            if (PER_TOKEN) tma_load_3d(&s.in[T_W], &map_w, &s.load_bar, h * 64, j * CH, b);
+            tma_load_3d(&s.in[T_GY], &map_gy, &s.load_bar, h * 64, j * CH, b);
+            tma_load_3d(&s.in[T_S], &map_s, &s.load_bar, 0, 0, bh * (n + 1) + j);
+            tma_load_3d(&s.in[T_D], &map_d, &s.load_bar, 0, 0, bh * (n + 1) + j + 1);
+        }
     }
     if (tid == 32) {
         // the CTA that will take this one's place on the SM finds its tiles in L2
@@ -374,9 +402,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         for (int ch = 0; ch < 4; ch++) lwc[ch] = log2_decay(P.wvec[h * 64 + ch0 + ch], P.w_kind, livec[ch]);
     }
     int fail = 0;
-    if (stamp) P.timeline[1] = clock64();
-    if (!mbar_wait(&s.load_bar, 0)) fail = 1;
-    if (stamp) P.timeline[2] = clock64();
+    if (!mbar_wait(&s.load_bar, 0, LIM)) fail = 1;
 
     // The products that need only the raw tiles go to the tensor core before the operand pass
     // (a tcgen05.mma is issued by one thread and costs it ~100 cycles of descriptor arithmetic:
@@ -554,7 +580,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     fence_async_smem();
     tc_fence_before();
     const int abort1 = __syncthreads_or(fail);
-    if (stamp) P.timeline[3] = clock64();
 
     // ------------------------------------------------- phase 1: the scores A1, A2
     if (lane == 0) {
@@ -592,9 +617,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         }
         diag += __shfl_xor_sync(0xffffffffu, diag, 16);
     }
-    if (!abort1 && !(mbar_wait(&s.bar_early, 0) && mbar_wait(&s.bar_score, 0))) fail = 1;
+    if (!abort1 && !(mbar_wait(&s.bar_early, 0, LIM) && mbar_wait(&s.bar_score, 0, LIM))) fail = 1;
     tc_fence_after();
-    if (stamp) P.timeline[4] = clock64();
 
     // mask pass: lo lanes build A~ (row t), hi lanes build P~ (row t); this group's 32 columns.
     // P~ is split: its two same-block triangles go to the P~ tile (cross block zero), the
@@ -655,7 +679,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     fence_async_smem();
     tc_fence_before();
     const int abort2 = __syncthreads_or(fail) | abort1;
-    if (stamp) P.timeline[5] = clock64();
 
     // ------------------------------------------------- phase 2: token-major accumulators
     // every accumulator is [token, 32 channels]: channels 0..31 in the lo lanes, 32..63 in the hi lanes
@@ -731,9 +754,8 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 
     // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (consumed after two more barriers)
     if (tid < CH) s.kb[tid] = P.e0[((size_t)bh * (n + 1) + j) * 64 + tid];
-    if (!abort2 && !mbar_wait(&s.bar_grad, 0)) fail = 1;
+    if (!abort2 && !mbar_wait(&s.bar_grad, 0, LIM)) fail = 1;
     tc_fence_after();
-    if (stamp) P.timeline[6] = clock64();
 
     // The decay gradient of token t is  glw_t = K_j + sum_{t'<=t} (a_t' + b_t') - b_t  with
     //   a_t = -(qrS_t + qrI_t)   (gr side),     b_t = qkD_t + qkI_t   (gk side),
@@ -821,7 +843,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     }
     if (wg == 0) {
         // gv: accumulator [s, v]
-        if (!abort2 && !mbar_wait(&s.bar_gv, 0)) fail = 1;
+        if (!abort2 && !mbar_wait(&s.bar_gv, 0, LIM)) fail = 1;
         tc_fence_after();
         float gv[32];
         tmem_ld16(tmem_addr(tm, lane_base, C_GV), gv);
@@ -911,7 +933,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     fence_async_smem();
     tc_fence_before();
     const int abort3 = __syncthreads_or(fail) | abort2;
-    if (stamp) P.timeline[7] = clock64();
     if (!abort3 && tid == 0) {
         tma_store_3d(&map_gr, &o_gr, h * 64, j * CH, b);
         tma_store_3d(&map_gk, &o_gk, h * 64, j * CH, b);
@@ -936,7 +957,6 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         mbar_wait(&s.bar_early, 0); mbar_wait(&s.bar_score, 0); mbar_wait(&s.bar_grad, 0); mbar_wait(&s.bar_gv, 0);
         if (P.status) atomicOr(P.status, 4);
     }
-    if (stamp) P.timeline[8] = clock64();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
 }
@@ -954,10 +974,11 @@ __global__ void k_reduce_partials(const float *__restrict__ part, float *__restr
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct BwdLayout {
-    size_t status, sck, dck, e0, gu_part, gw_part, total;
+    size_t status, sck, dck, e0, gu_part, gw_part, groups, wconv, total;
 };
 BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     const size_t n = (a->T + CH - 1) / CH, bh = (size_t)a->B * a->H;
+    const GroupPlan gp = plan_groups((int)bh, (int)n, a->time_groups);
     BwdLayout L;
     L.status = 0;
     L.sck = 256;
@@ -965,7 +986,10 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
     L.e0 = L.dck + align256(bh * (n + 1) * 64 * 64 * 2);
     L.gu_part = L.e0 + align256(bh * (n + 1) * 64 * 4);
     L.gw_part = L.gu_part + align256(bh * n * 64 * 4);
-    L.total = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
+    L.groups = L.gw_part + (per_token_w ? 0 : align256(bh * n * 64 * 4));
+    // one region serves the forward re-run (when no hand-over was given) and then the dS scan
+    L.wconv = L.groups + (gp.G > 1 ? group_layout(bh * gp.G).total : 0);
+    L.total = L.wconv + chunked_wconv_bytes(a, per_token_w);
     return L;
 }
 
@@ -973,11 +997,14 @@ BwdLayout bwd_layout(const wkv_args_t *a, bool per_token_w) {
 
 size_t chunked_backward_workspace(const wkv_args_t *a, bool per_token_w) { return bwd_layout(a, per_token_w).total; }
 
-int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream) {
-    const int B = a->B, T = a->T, H = a->H, C = H * 64, n = (T + CH - 1) / CH;
+int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &tst, cudaStream_t stream) {
+    wkv_args_t args = *a0;
+    wkv_args_t *a = &args;
+    const int B = a->B, T = a->T, H = a->H, C = H * 64, n = (T + CH - 1) / CH, BH = B * H;
     const BwdLayout L = bwd_layout(a, per_token_w);
     char *ws = (char *)a->workspace;
     if (cudaMemsetAsync(ws, 0, 256, stream) != cudaSuccess) return WKV_ERR_LAUNCH;
+    if (chunked_convert_w(a, per_token_w, ws + L.wconv, stream) != WKV_OK) return WKV_ERR_LAUNCH;
     // what the forward kernel leaves for this call: chunk-start states, r e^{cp}, chunk decays
     char *fwd_ck = a->state_ckpt ? (char *)a->state_ckpt : ws + L.sck;
     const CkptLayout CL = ckpt_layout(B, T, H);
@@ -989,58 +1016,71 @@ int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t stream)
         wkv_args_t f = *a;
         f.y = nullptr;
         f.state_out = nullptr;
-        const int err = chunked_forward_impl(&f, per_token_w, fwd_ck, stream);
+        const int err = chunked_forward_impl(&f, per_token_w, fwd_ck, ws + L.groups, tst, stream);
         if (err != WKV_OK) return err;
     }
     CUtensorMap mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, mrh;
     bool ok = make_btc_map(&mr, a->r, B, T, C) && make_btc_map(&mk, a->k, B, T, C) &&
               make_btc_map(&mv, a->v, B, T, C) && make_btc_map(&mgy, a->gy, B, T, C) &&
               make_btc_map(&mgr, a->gr, B, T, C) && make_btc_map(&mgk, a->gk, B, T, C) &&
-              make_btc_map(&mgv, a->gv, B, T, C) && make_btc_map(&ms, sck, B * H * (n + 1), 64, 64) &&
-              make_btc_map(&md, dck, B * H * (n + 1), 64, 64) && make_btc_map(&mrh, fwd_ck + CL.rhat, B, T, C);
+              make_btc_map(&mgv, a->gv, B, T, C) && make_btc_map(&ms, sck, BH * (n + 1), 64, 64) &&
+              make_btc_map(&md, dck, BH * (n + 1), 64, 64) && make_btc_map(&mrh, fwd_ck + CL.rhat, B, T, C);
     if (per_token_w) ok = ok && make_btc_map(&mw, a->w, B, T, C) && make_btc_map(&mgw, a->gw, B, T, C);
     else { mw = mr; mgw = mgr; }
     if (!ok) return WKV_ERR_LAUNCH;
 
-    // 2. dS scan
+    // 2. dS scan (with time groups: summary pass, group scan, full pass)
     {
+        const GroupPlan gp = plan_groups(BH, n, a->time_groups);
+        const GroupLayout GL = group_layout((size_t)BH * gp.G);
+        char *g = ws + L.groups;
         DscanParams p;
         p.T = T; p.H = H; p.nchunk = n; p.layout = a->state_layout;
+        p.G = gp.G; p.L = gp.L;
         p.dchunk = (const float *)(fwd_ck + CL.dchunk);
-        p.gstate_out = a->gstate_out; p.gstate_in = a->gstate_in;
         p.dck = (__nv_bfloat16 *)dck; p.e0 = e0; p.status = (int *)ws;
+        p.wait_limit = tst.wait_limit;
+        p.skip_load = tst.kernel == 1 ? tst.skip_load : -1;
         const size_t smem = sizeof(DscanSmem) + 1024;
-        if (cudaFuncSetAttribute(k_chunk_dscan, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return WKV_ERR_LAUNCH;
-        k_chunk_dscan<<<B * H, 160, smem, stream>>>(mrh, mgy, ms, p);
+        static unsigned char attr_done[64];
+        if (!set_max_smem_once(k_chunk_dscan, (int)smem, attr_done)) return WKV_ERR_LAUNCH;
+        if (gp.G > 1) {
+            p.summary = 1;
+            p.gstate_out = nullptr; p.gstart = nullptr; p.gstate_in = nullptr;
+            p.gU = (float *)(g + GL.gU); p.gD = (float *)(g + GL.gD);
+            k_chunk_dscan<<<BH * gp.G, 160, smem, stream>>>(mrh, mgy, ms, p);
+            if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+            if (launch_group_scan(g, BH, gp.G, a->gstate_out, a->gstate_in, a->state_layout, true, stream) != WKV_OK)
+                return WKV_ERR_LAUNCH;
+        }
+        p.summary = 0;
+        p.gstate_out = a->gstate_out;
+        p.gstart = gp.G > 1 ? (const float *)(g + GL.gstart) : nullptr;
+        p.gstate_in = gp.G > 1 ? nullptr : a->gstate_in;
+        p.gU = nullptr; p.gD = nullptr;
+        k_chunk_dscan<<<BH * gp.G, 160, smem, stream>>>(mrh, mgy, ms, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 3. per-chunk gradients
     {
         BwdParams p;
         p.T = T; p.H = H; p.nchunk = n; p.w_kind = a->w_kind;
-        {
-            int dev = 0, sms = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess ||
-                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-                return WKV_ERR_LAUNCH;
-            p.prefetch_dist = 2 * sms;      // two CTAs of this kernel fit on an SM
-        }
+        p.prefetch_dist = 2 * device_sm_count();      // two CTAs of this kernel fit on an SM
         p.u = (const __nv_bfloat16 *)a->u;
         p.wvec = per_token_w ? nullptr : (const float *)a->w;
         p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
-        // bytes [64,256) of the status block take the optional phase timeline (debug aid)
-        p.timeline = getenv("WKV_B200_TIMELINE") ? (long long *)(ws + 64) : nullptr;
+        p.wait_limit = tst.wait_limit;
+        p.skip_load = tst.kernel == 2 ? tst.skip_load : -1;
         const size_t smem = sizeof(BwdSmem);
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return WKV_ERR_LAUNCH;
-        kern<<<B * H * n, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
+        static unsigned char attr_done[2][64];
+        if (!set_max_smem_once(kern, (int)smem, attr_done[per_token_w ? 1 : 0])) return WKV_ERR_LAUNCH;
+        kern<<<BH * n, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 4. fold the per-chunk partial sums
     {
-        const int total = B * H * 64;
+        const int total = BH * 64;
         k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, n, total);
         if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, n, total);
     }

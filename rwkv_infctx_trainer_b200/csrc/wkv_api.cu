@@ -16,6 +16,7 @@ int check_common(const wkv_args_t *a, bool backward, bool per_token_w) {
     if (a->state_layout != WKV_STATE_KV && a->state_layout != WKV_STATE_VK) return WKV_ERR_DTYPE;
     if (a->path != WKV_PATH_AUTO && a->path != WKV_PATH_SCALAR && a->path != WKV_PATH_CHUNKED)
         return WKV_ERR_DTYPE;
+    if (a->time_groups < 0) return WKV_ERR_SHAPE;
     if (a->B == 0 || a->H == 0) return WKV_OK;
     if (!a->u) return WKV_ERR_NULL;
     if (!per_token_w && !a->w) return WKV_ERR_NULL;
@@ -56,7 +57,7 @@ size_t bwd_ws(const wkv_args_t *a, bool pt) {
     return use_chunked(a, pt, &err) ? chunked_backward_workspace(a, pt) : scalar_backward_workspace(a);
 }
 
-int forward(const wkv_args_t *a, bool pt, void *stream) {
+int forward(const wkv_args_t *a, bool pt, void *stream, const ChunkedTest &tst = ChunkedTest()) {
     int err = check_common(a, false, pt);
     if (err != WKV_OK) return err;
     if (a->B == 0 || a->H == 0) return WKV_OK;
@@ -66,10 +67,10 @@ int forward(const wkv_args_t *a, bool pt, void *stream) {
     const size_t need = fwd_ws(a, pt);
     if (need && (!a->workspace || a->workspace_bytes < need)) return WKV_ERR_WORKSPACE;
     if (ch && a->state_ckpt && a->state_ckpt_bytes < wkv56_state_ckpt_bytes(a, pt)) return WKV_ERR_WORKSPACE;
-    return ch ? chunked_forward(a, pt, s) : scalar_forward(a, pt, s);
+    return ch ? chunked_forward(a, pt, tst, s) : scalar_forward(a, pt, s);
 }
 
-int backward(const wkv_args_t *a, bool pt, void *stream) {
+int backward(const wkv_args_t *a, bool pt, void *stream, const ChunkedTest &tst = ChunkedTest()) {
     int err = check_common(a, true, pt);
     if (err != WKV_OK) return err;
     if (a->B == 0 || a->H == 0) return WKV_OK;
@@ -79,7 +80,7 @@ int backward(const wkv_args_t *a, bool pt, void *stream) {
     const size_t need = bwd_ws(a, pt);
     if (need && (!a->workspace || a->workspace_bytes < need)) return WKV_ERR_WORKSPACE;
     if (ch && a->state_ckpt && a->state_ckpt_bytes < wkv56_state_ckpt_bytes(a, pt)) return WKV_ERR_WORKSPACE;
-    return ch ? chunked_backward(a, pt, s) : scalar_backward(a, pt, s);
+    return ch ? chunked_backward(a, pt, tst, s) : scalar_backward(a, pt, s);
 }
 
 }  // namespace
@@ -103,7 +104,7 @@ const char *wkv_error_string(int code) {
 
 int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
 
-const char *wkv_version(void) { return "wkv_b200 1 sm_100a"; }
+const char *wkv_version(void) { return "wkv_b200 2 sm_100a"; }
 
 size_t wkv56_state_ckpt_bytes(const wkv_args_t *a, int per_token_w) {
     if (!wkv56_uses_chunked(a, per_token_w)) return 0;
@@ -114,6 +115,22 @@ int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w) {
     if (!a || a->B <= 0 || a->H <= 0 || a->T <= 0 || a->N != HEAD) return 0;
     int err;
     return use_chunked(a, per_token_w != 0, &err) ? 1 : 0;
+}
+
+int wkv_selftest_wait_timeout(int *status_word, unsigned limit, void *stream) {
+    if (!status_word) return WKV_ERR_NULL;
+    return selftest_wait(status_word, limit, (cudaStream_t)stream);
+}
+
+int wkv56_selftest_abort(const wkv_args_t *a, int per_token_w, int backward_call, int kernel, int skip_chunk,
+                         unsigned limit, void *stream) {
+    if (limit == 0 || limit > 100000u || kernel < 0 || kernel > 2 || skip_chunk < 0) return WKV_ERR_SHAPE;
+    if (!wkv56_uses_chunked(a, per_token_w)) return WKV_ERR_UNSUPPORTED;
+    ChunkedTest tst;
+    tst.wait_limit = limit;
+    tst.kernel = kernel;
+    tst.skip_load = skip_chunk;
+    return backward_call ? backward(a, per_token_w != 0, stream, tst) : forward(a, per_token_w != 0, stream, tst);
 }
 
 size_t wkv5_forward_workspace(const wkv_args_t *a) { return fwd_ws(a, false); }

@@ -38,7 +38,5 @@ int scalar_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t s);
 bool chunked_supported(const wkv_args_t *a, bool per_token_w);
 size_t chunked_forward_workspace(const wkv_args_t *a, bool per_token_w);
 size_t chunked_backward_workspace(const wkv_args_t *a, bool per_token_w);
-int chunked_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t s);
-int chunked_backward(const wkv_args_t *a, bool per_token_w, cudaStream_t s);
 
 }  // namespace wkv

@@ -9,25 +9,81 @@ from . import _lib as L
 
 HEAD_SIZE = 64
 
-# Debug aid: when True every call synchronises and checks the status word the chunked
-# kernels keep at the start of their workspace (non-zero = a bounded device-side wait ran
-# out and the kernel gave up).  Off by default: the ops never synchronise on their own.
+# The chunked kernels keep a status word at the start of their workspace: non-zero means that a
+# bounded device-side wait ran out, the kernel gave up, and its outputs are invalid.  Every call
+# copies that word to pinned host memory (on a side stream, without synchronising); the copies
+# that have completed are looked at when the next v5/v6 call (forward or backward) on that device
+# starts, and ``poll_status()`` looks at them on demand.  A non-zero word raises there.
+# With CHECK_STATUS = True every call synchronises and checks its own word before returning
+# (tests do that).
 CHECK_STATUS = False
 
+_pending = {}      # device index -> list of (event, pinned int32 tensor, description)
+_side_streams = {}  # device index -> stream the status words are copied on
 
-def _check_status(lib, a, variant, ws, what):
-    if (CHECK_STATUS and ws is not None and ws.numel() >= 4
-            and lib.wkv56_uses_chunked(ctypes.byref(a), int(variant == "wkv6"))):
+
+def poll_status(device=None, wait=False):
+    """Raise if a chunked-kernel call on ``device`` (default: all devices) reported a device-side
+    wait that ran out.  ``wait=True`` first waits for the calls issued so far."""
+    keys = list(_pending) if device is None else [torch.device(device).index or 0]
+    for key in keys:
+        still = []
+        for ev, word, what in _pending.get(key, []):
+            if wait:
+                ev.synchronize()
+            if ev.query():
+                code = int(word.item())
+                if code != 0:
+                    _pending[key] = []
+                    raise RuntimeError(f"{what}: a device-side wait ran out (status {code}); "
+                                       "the outputs of that call are invalid")
+            else:
+                still.append((ev, word, what))
+        _pending[key] = still
+
+
+def _watch_status(lib, a, variant, ws, what):
+    if ws is None or ws.numel() < 4 or not lib.wkv56_uses_chunked(ctypes.byref(a), int(variant == "wkv6")):
+        return
+    if CHECK_STATUS:
         torch.cuda.synchronize(ws.device)
         code = int(ws[:4].view(torch.int32).item())
         if code != 0:
-            raise RuntimeError(f"{what}: device-side wait timed out (status {code})")
+            raise RuntimeError(f"{what}: a device-side wait ran out (status {code})")
+        return
+    key = ws.device.index or 0
+    side = _side_streams.get(key)
+    if side is None:
+        side = _side_streams[key] = torch.cuda.Stream(ws.device)
+    # the copy runs on a side stream so that it never sits between two kernels of the caller's stream
+    done = torch.cuda.Event()
+    done.record(torch.cuda.current_stream(ws.device))
+    word = torch.empty(1, dtype=torch.int32, pin_memory=True)
+    with torch.cuda.stream(side):
+        side.wait_event(done)
+        word.copy_(ws[:4].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(side)
+    ws.record_stream(side)
+    _pending.setdefault(key, []).append((ev, word, what))
 
 
-def _args(variant, B, T, H, dtype, w_kind, layout, path, **t) -> L.WkvArgs:
+def _check_layout(B, T, C, **tensors):
+    """the kernels take raw pointers: every [B,T,C] tensor must be exactly that, contiguous"""
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if tuple(t.shape) != (B, T, C):
+            raise ValueError(f"{name} must have shape {(B, T, C)}, got {tuple(t.shape)}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous (a [:, t0:t1] view of a longer tensor is not)")
+
+
+def _args(variant, B, T, H, dtype, w_kind, layout, path, time_groups=0, **t) -> L.WkvArgs:
     a = L.WkvArgs()
     a.B, a.T, a.H, a.N = B, T, H, HEAD_SIZE
     a.dtype, a.w_kind, a.state_layout, a.path = L.DTYPE_CODE[dtype], w_kind, layout, path
+    a.time_groups = time_groups
     for name, tensor in t.items():
         setattr(a, name, L.ptr(tensor))
     return a
@@ -41,21 +97,27 @@ def _with_workspace(lib, variant, direction, a, dev):
 
 
 def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE_KV,
-            path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=False):
+            path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=False, time_groups=0):
     """Launch wkv5_forward / wkv6_forward.  All tensors contiguous, on one device.
     Returns (y, state_out); ``state_out`` may be given (it may be ``state_in`` itself).
     With ``save_ckpt`` a third value is returned: the chunk-start states to hand to
-    ``backward(..., ckpt=...)`` (None when the call did not run on the chunked kernels)."""
+    ``backward(..., ckpt=...)`` (None when the call did not run on the chunked kernels).
+    ``time_groups``: see ``wkv_args_t.time_groups`` (0 = the library decides)."""
     B, T, C = r.shape
     H = C // HEAD_SIZE
     dev = L.require_cuda(r, k, v, w, u, state_in)
+    _check_layout(B, T, C, r=r, k=k, v=v, w=w if variant == "wkv6" else None)
+    for name, t in (("u", u), ("state_in", state_in), ("state_out", state_out)):
+        if t is not None and not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    poll_status(dev)
     y = torch.empty_like(r)
     if state_out is None:
         state_out = torch.empty((B, H, HEAD_SIZE, HEAD_SIZE), device=dev, dtype=torch.float32)
     lib = L.load()
     with torch.cuda.device(dev):
-        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, r=r, k=k, v=v, w=w, u=u,
-                  state_in=state_in, y=y, state_out=state_out)
+        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, time_groups, r=r, k=k, v=v, w=w,
+                  u=u, state_in=state_in, y=y, state_out=state_out)
         ckpt = None
         if save_ckpt:
             nck = lib.wkv56_state_ckpt_bytes(ctypes.byref(a), int(variant == "wkv6"))
@@ -65,7 +127,7 @@ def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE
         ws = _with_workspace(lib, variant, "forward", a, dev)
         L.check(getattr(lib, f"{variant}_forward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_forward")
-        _check_status(lib, a, variant, ws, f"{variant}_forward")
+        _watch_status(lib, a, variant, ws, f"{variant}_forward")
         del ws
     if save_ckpt:
         return y, state_out, ckpt
@@ -73,12 +135,18 @@ def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE
 
 
 def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
-             layout=L.WKV_STATE_KV, path=L.WKV_PATH_AUTO, want_gstate=True, ckpt=None):
+             layout=L.WKV_STATE_KV, path=L.WKV_PATH_AUTO, want_gstate=True, ckpt=None,
+             time_groups=0):
     """Launch wkv5_backward / wkv6_backward.  Returns gr, gk, gv, gw, gu, gstate_in with
     gw = [B,T,C] (v6, activation dtype) or [B,C] fp32 per-batch partials (v5); gu [B,C] fp32."""
     B, T, C = r.shape
     H = C // HEAD_SIZE
     dev = L.require_cuda(r, k, v, w, u, state_in, gy, gstate_out)
+    _check_layout(B, T, C, r=r, k=k, v=v, gy=gy, w=w if variant == "wkv6" else None)
+    for name, t in (("u", u), ("state_in", state_in), ("gstate_out", gstate_out)):
+        if t is not None and not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    poll_status(dev)
     gr, gk, gv = torch.empty_like(r), torch.empty_like(r), torch.empty_like(r)
     if variant == "wkv6":
         gw = torch.empty_like(r)
@@ -89,14 +157,14 @@ def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
            if want_gstate else None)
     lib = L.load()
     with torch.cuda.device(dev):
-        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, r=r, k=k, v=v, w=w, u=u,
-                  state_in=state_in, gy=gy, gstate_out=gstate_out, gr=gr, gk=gk, gv=gv, gw=gw,
+        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, time_groups, r=r, k=k, v=v, w=w,
+                  u=u, state_in=state_in, gy=gy, gstate_out=gstate_out, gr=gr, gk=gk, gv=gv, gw=gw,
                   gu=gu, gstate_in=gsi)
         if ckpt is not None:
             a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), ckpt.numel()
         ws = _with_workspace(lib, variant, "backward", a, dev)
         L.check(getattr(lib, f"{variant}_backward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_backward")
-        _check_status(lib, a, variant, ws, f"{variant}_backward")
+        _watch_status(lib, a, variant, ws, f"{variant}_backward")
         del ws
     return gr, gk, gv, gw, gu, gsi

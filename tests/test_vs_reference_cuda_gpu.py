@@ -133,8 +133,14 @@ def test_v6_matches_reference_state_kernels_b1(path):
     H, T = 3, 256
     C = H * 64
     q = TL.case56("v6", 1, T, H, BF, seed=63, gstate=False)
+    # every decay above the chunked kernels' 0.005 floor, so that both paths compute the same function
+    q["x"] = TL.rounded(np.minimum(q["x"], 1.6), BF)
     r, k, v, u, gy = (TL.to_dev(q[n], BF) for n in ("r", "k", "v", "u", "gy"))
-    ew = TL.to_dev(-np.exp(q["x"]), torch.float32)
+    # the literal lower-level call: ew = -exp(x) in fp32, from the bf16 activation (TimeMix.py:49-51)
+    ew = (-torch.exp(TL.to_dev(q["x"], BF).float())).contiguous()
+    a = wkv56._args("wkv6", 1, T, H, BF, W.WKV_W_NEGEXP, W.WKV_STATE_VK, p)
+    from rwkv_infctx_trainer_b200 import _lib as L
+    assert L.load().wkv56_uses_chunked(ctypes.byref(a), 1) == int(path == "auto")
     # both sides start from the same bf16-rounded state (the reference keeps state in bf16)
     s_bf = TL.to_dev(np.swapaxes(q["state_in"], -1, -2), BF)
     s_in32 = s_bf.float().contiguous()

@@ -119,3 +119,29 @@ def test_v4_workspace_too_small_is_an_error():
     code = lib.wkv4_backward(1, 32, 4, L.WKV_F32, p, p, p, p, None, p, None, p, p, p, p, None,
                              p, 8, None)
     assert code == 5
+
+
+def test_v4_op_called_from_torchscript():
+    """RWKV-v4neo/src/model.py:266-279 reaches torch.ops.rwkv.wkv from inside a
+    torch.jit.script method; the registered op must resolve there, forward and backward"""
+    W = _pkg()
+    B, T, C = 2, 40, 64
+    q = v4_inputs(B, T, C, torch.bfloat16, seed=5)
+
+    @torch.jit.script
+    def scripted(td: torch.Tensor, u: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s: torch.Tensor):
+        out = torch.ops.rwkv.wkv(td, u, k, v, s)
+        return out[0], out[1]
+
+    td = TL.to_dev(q["td"], torch.float32).requires_grad_(True)
+    u, k, v = (TL.to_dev(q[n], torch.bfloat16).requires_grad_(True) for n in ("u", "k", "v"))
+    s0 = torch.zeros((B, C, 3), device="cuda"); s0[..., 2] = -1e38
+    y, s1 = scripted(td, u, k, v, s0)
+    (y.float() * TL.to_dev(q["gy"], torch.float32)).sum().backward()
+    want = oracle_chain(q, T)
+    tol = TL.TOL[torch.bfloat16]
+    TL.assert_close("y", y, want["y"], tol)
+    TL.assert_close("gk", k.grad, want["gk"], tol)
+    TL.assert_close("gv", v.grad, want["gv"], tol)
+    TL.assert_close("gw", td.grad, want["gw"], tol)
+    TL.assert_close("gu", u.grad, want["gu"], tol)
