@@ -9,13 +9,21 @@ shape [B=4, T=16384, C=4096] (H=64 heads of 64), processed as 4 BPTT segments of
 backward over them in reverse with the state gradient carried.  Synthetic
 inputs: r,k,v,gy ~ N(0,1), x ~ N(-0.6,0.5) (decay exp(-exp(x))), u ~ U(-1,1).
 
-With N GPUs every rank runs the same workload on its own (batch x head) units:
-no collective on the data path, weak scaling, value = N * tokens / max-over-ranks
-time.  Prints ONE JSON line (rank 0).
+With N GPUs the workload's 64 heads are split over the ranks (64/N heads of all 4
+batch rows each): strong scaling, value = tokens / max-over-ranks time.  No
+collective runs on the data path (NCCL only carries the barrier and the
+max-over-ranks time).  ``--scaling weak`` makes every rank run the whole workload
+instead.  Prints ONE JSON line (rank 0).
 
-``--impl reference`` times the reference's own CPU implementation of the path
-(the chunked pure-PyTorch algorithm, oracle/wkv_chunked_port.py) on the host
-cores, on a bounded sample of the same workload.
+``--impl reference`` times the reference's own CPU implementation of the path on
+the host cores, on a bounded sample of the same workload: the project's
+``rwkv_inner`` itself where its checkout is present, else the restatement of it in
+oracle/wkv_chunked_port.py.
+
+Side modes (one GPU, a JSON line each, not the headline): ``--config 1|2`` the v4
+fp32 and v5 bf16 workloads, ``--config 4`` one GPU's 5-head slice of the
+1M-token stream, ``--ref-kernels`` the project's own CUDA kernels (compiled
+unchanged for sm_100a into oracle/_ref/) on the shapes they are valid for.
 """
 from __future__ import annotations
 
@@ -53,8 +61,86 @@ def peaks():
         return 6650.0, "fallback"
 
 
+_NVML_CHILD = r"""
+import sys, time
+import pynvml as N
+N.nvmlInit()
+h = N.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+print("ready", flush=True)
+while True:
+    sm = N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)
+    try:
+        r = N.nvmlDeviceGetCurrentClocksEventReasons(h)
+    except Exception:
+        r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+    print("%.6f,%d,%d,%s" % (time.time(), sm, mx, "|".join(k for k, b in bits.items() if r & b)), flush=True)
+    time.sleep(0.003)
+"""
+
+
+class NvmlSampler:
+    """Reads (never sets) the SM clock and the clock-event reasons through NVML every ~3 ms from a
+    child process, so that even a timed region of tens of milliseconds gets its own samples; only
+    the samples whose time stamp falls inside [mark_start, mark_end] are reported."""
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+        self.t0 = self.t1 = None
+
+    def start(self):
+        try:
+            phys = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = int(phys.split(",")[self.index]) if phys and phys.split(",")[self.index].isdigit() else self.index
+            self.proc = subprocess.Popen([sys.executable, "-c", _NVML_CHILD, str(idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            if self.proc.stdout.readline().strip() != "ready":
+                raise RuntimeError("nvml child not ready")
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            if self.proc is not None:
+                self.proc.kill()
+            self.proc = None
+        return self.proc is not None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    def stop(self) -> dict:
+        time.sleep(0.01)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in list(self.lines):
+            f = line.strip().split(",")
+            if len(f) < 4:
+                continue
+            ts = float(f[0])
+            if self.t0 is not None and not (self.t0 <= ts <= (self.t1 or ts)):
+                continue
+            sm.append(float(f[1])); mx.append(float(f[2]))
+            reasons.update(x for x in f[3].split("|") if x)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no_samples"], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "source": "nvml, ~3 ms period, samples inside the timed region only"}
+
+
 class ClockSampler:
-    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs
+    (the fallback when NVML cannot be read from Python)."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -134,9 +220,16 @@ class Runner:
         self.bwd_events = []
         self.fwd_events = []
         self.launches = 0
+        # kernels per call: k_chunk_fwd ; k_chunk_dscan, k_chunk_bwd, k_reduce_partials -- and, when the
+        # library cuts the chains into time groups (few chains per GPU), a summary pass and a group
+        # scan more for the forward and for the dS scan
+        import ctypes
+        a = wkv56._args("wkv6", B, wl["seg"], H, torch.bfloat16, W.WKV_W_RAW, W.WKV_STATE_KV, W.WKV_PATH_AUTO)
+        split = W._lib.load().wkv6_forward_workspace(ctypes.byref(a)) > 256
+        self.fwd_launches, self.bwd_launches = (3, 5) if split else (1, 3)
 
     def seg(self, name, t0, t1):
-        return self.d[name][:, t0:t1]
+        return self.d[name][:, t0:t1].contiguous()     # the op takes contiguous [B, T_seg, C] tensors
 
     def step(self, record=False):
         W, d = self.W, self.d
@@ -154,7 +247,7 @@ class Runner:
                 e1.record()
                 self.fwd_events.append((e0, e1))
             states.append(s)
-            self.launches += 1          # k_chunk_fwd
+            self.launches += self.fwd_launches
         gs = None
         out = None
         for (t0, t1), s_in, ck in reversed(list(zip(self.bounds, states[:-1], ckpts))):
@@ -168,7 +261,7 @@ class Runner:
                 e1.record()
                 self.bwd_events.append((e0, e1))
             gs = out[5]
-            self.launches += 3          # k_chunk_dscan, k_chunk_bwd, k_reduce_partials
+            self.launches += self.bwd_launches
         return out
 
 
@@ -194,6 +287,8 @@ def run_ours(args):
     if args.medium:
         wl.update(name=wl["name"] + "_medium", T=4096)
     H_total = wl["H"]
+    if args.scaling is None:
+        args.scaling = "strong"
     if args.scaling == "strong" and world > 1:
         from rwkv_infctx_trainer_b200.sharding import shard_units
         sh = shard_units(wl["B"], wl["H"], world, rank)
@@ -222,15 +317,25 @@ def run_ours(args):
         runner.step()
     barrier()
     runner.launches = 0
-    sampler = ClockSampler(local)
+    sampler = None
     if rank == 0:
-        sampler.start()
+        sampler = NvmlSampler(local)
+        if not sampler.start():
+            sampler = ClockSampler(local)
+            sampler.start()
+        barrier_free_sleep = 0.05      # let the first samples arrive before the clock starts
+        time.sleep(barrier_free_sleep)
+    barrier()
+    if rank == 0 and isinstance(sampler, NvmlSampler):
+        sampler.mark_start()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
-    for _ in range(args.steps):
-        runner.step(record=True)
+    for i in range(args.steps):
+        runner.step(record=i < 32)      # per-launch events on the first steps only
     t_end.record()
     barrier()
+    if rank == 0 and isinstance(sampler, NvmlSampler):
+        sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     ms = t_start.elapsed_time(t_end)
     launches = runner.launches
@@ -338,7 +443,7 @@ def run_ours(args):
                        "state": "fp32 carried across segments, gradient carried back",
                        "sharding": (f"{world} x (batch x head) replicas of the workload" if args.scaling == "weak"
                                     else f"heads split {H} per GPU over {world} GPUs") + ", no collective on the data path",
-                       "l2": "inputs (2.7 GB per GPU) larger than L2, no flush"},
+                       "l2": f"inputs ({5 * 2 * B * T * C / 1e9:.2f} GB per GPU) larger than L2, no flush"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -385,13 +490,49 @@ def cpu_sample():
     return t, Bs * T * Hs, desc
 
 
+def reference_rwkv_inner():
+    """The project's own rwkv_inner (RWKV-v6/src/module/rwkv_inner.py), imported from its checkout
+    with the trainer-only packages stubbed (tests/golden/make_golden.py does the same to make the
+    fixtures), or None where the checkout is not present."""
+    root = os.environ.get("WKV_REFERENCE_ROOT", "/root/reference")
+    if not os.path.isdir(os.path.join(root, "RWKV-v6", "src", "module")):
+        return None
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+        import make_golden
+        return make_golden.load_rwkv_inner("RWKV-v6")
+    except Exception:
+        return None
+
+
 def cpu_baseline(steps: int, warmup: int) -> dict:
     from oracle import wkv_chunked_port as P
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     t, head_tokens, desc = cpu_sample()
-    run = lambda: P.run_chain("v6", t["r"], t["k"], t["v"], t["x"], t["u"], t["s"], t["gy"],
-                              WORKLOAD["seg"])
+    inner = reference_rwkv_inner()
+    if inner is None:
+        kind = "port"
+        run = lambda: P.run_chain("v6", t["r"], t["k"], t["v"], t["x"], t["u"], t["s"], t["gy"],
+                                  WORKLOAD["seg"])
+    else:
+        kind = "reference"
+        Hs, N = t["u"].shape
+
+        def run():
+            # the trainer's calling pattern (RWKV-v6/src/module/TimeMix.py:283-295): segments with the
+            # state carried, one backward over the chain
+            leaves = [t[n].clone().requires_grad_(True) for n in ("r", "k", "v", "x", "u", "s")]
+            r, k, v, x, u, state = leaves
+            w = torch.exp(-torch.exp(x))
+            B, T, C = r.shape
+            ys = []
+            for t0 in range(0, T, WORKLOAD["seg"]):
+                t1 = min(T, t0 + WORKLOAD["seg"])
+                sl = lambda a: a[:, t0:t1].reshape(B, t1 - t0, Hs, N).transpose(1, 2)
+                o, state = inner(sl(r), sl(k), sl(v), sl(w), u.view(1, Hs, 1, N), state, 128, 64)
+                ys.append(o.transpose(1, 2).reshape(B, t1 - t0, C))
+            torch.autograd.grad((torch.cat(ys, 1) * t["gy"]).sum(), leaves)
     for _ in range(warmup):
         run()
     t0 = time.perf_counter()
@@ -400,7 +541,7 @@ def cpu_baseline(steps: int, warmup: int) -> dict:
     dt = (time.perf_counter() - t0) / steps
     # tokens/s of the full-width op (all H heads) at this head-token rate
     return {"value": head_tokens / dt / WORKLOAD["H"], "unit": "tokens/s", "cores": cores,
-            "kind": "port", "sample": desc, "head_tokens_per_s": head_tokens / dt,
+            "kind": kind, "sample": desc, "head_tokens_per_s": head_tokens / dt,
             "s_per_sample": dt}
 
 
@@ -514,18 +655,188 @@ def run_side_config(args):
                       "steps": args.steps, "warmup": args.warmup}), flush=True)
 
 
+def _time_steps(step, steps, warmup):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_stream_config(args):
+    """One GPU's share of the long-context stream: v6 3B shape (C=2560, 40 heads) with the heads
+    split over 8 GPUs -> 5 heads per GPU, B=1, segments of 4096 tokens with the state carried,
+    forward plus truncated backward per segment (no state gradient across segments).  Five chains
+    cannot fill 148 SMs by themselves: the library cuts every segment's chain into time groups."""
+    import rwkv_infctx_trainer_b200 as W
+    from rwkv_infctx_trainer_b200 import wkv56
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    hbm, which = peaks()
+    B, H, seg, nseg = 1, 5, 4096, args.segments
+    C, T = H * 64, seg * args.segments
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda: torch.randn((nseg, B, seg, C), generator=g, device=device).to(torch.bfloat16)
+    r, k, v, gy = mk(), mk(), mk(), mk()
+    w = (torch.randn((nseg, B, seg, C), generator=g, device=device) * 0.5 - 0.6).to(torch.bfloat16)
+    u = (torch.rand((H, 64), generator=g, device=device) * 2 - 1).to(torch.bfloat16)
+    s0 = torch.zeros((B, H, 64, 64), device=device)
+
+    def make_step(groups):
+        def step():
+            state = s0
+            for i in range(nseg):
+                y, s_next, ck = wkv56.forward("wkv6", r[i], k[i], v[i], w[i], u, state, w_kind=W.WKV_W_RAW,
+                                              save_ckpt=True, time_groups=groups)
+                wkv56.backward("wkv6", r[i], k[i], v[i], w[i], u, state, gy[i], None, w_kind=W.WKV_W_RAW,
+                               ckpt=ck, want_gstate=False, time_groups=groups)
+                state = s_next
+        return step
+
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    ms = _time_steps(make_step(0), steps, warmup)
+    ms_uncut = _time_steps(make_step(1), 1, 1)
+    bytes_step = (FWD_ELEMS + BWD_ELEMS) * 2 * B * T * C
+    print(json.dumps({"config_index": 4, "workload": "rwkv6_3b_stream_5_heads_of_40", "metric": METRIC,
+                      "value": B * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                      "segments": nseg, "us_per_segment": ms * 1e3 / nseg,
+                      "value_chains_uncut": B * T / (ms_uncut * 1e-3),
+                      "us_per_segment_chains_uncut": ms_uncut * 1e3 / nseg,
+                      "algorithmic_bytes_per_step": bytes_step,
+                      "roofline_frac": bytes_step / (ms * 1e-3) / 1e9 / hbm, "peak_source": which,
+                      "note": "5 (batch x head) chains per GPU: launch- and latency-bound, not HBM-bound",
+                      "steps": steps, "warmup": warmup}), flush=True)
+
+
+def run_ref_kernels(args):
+    """The RWKV-infctx-trainer project's own CUDA kernels, compiled unchanged for sm_100a
+    (oracle/_ref/, test infrastructure), timed with CUDA events on the shapes and inputs they are
+    valid for: v4 (wkv_cuda_bf16.cu:160-172) on the v4 workload at bf16; v5 (wkv5_cuda.cu:348-383)
+    on the v5 workload with a zero state; v6 (wkv6state_cuda_v1.cu:295-308) on one batch row of
+    the v6 workload.  Forward + backward of every BPTT segment; prints one JSON line per variant."""
+    import ctypes
+    from oracle import build as OB
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    hbm, which = peaks()
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    g = torch.Generator(device="cuda").manual_seed(0)
+    BF = torch.bfloat16
+    steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 3))
+
+    def lib(name):
+        path = os.path.join(OB.REF_DIR, name)
+        return ctypes.CDLL(path) if os.path.exists(path) else None
+
+    def report(name, cite, B, T, C, elems, ms, note):
+        nbytes = elems * 2 * B * T * C
+        print(json.dumps({"ref_kernel": name, "source": cite, "metric": METRIC, "value": B * T / (ms * 1e-3),
+                          "unit": "tokens/s", "ms_per_step": ms, "B": B, "T": T, "C": C,
+                          "algorithmic_gbs": nbytes / (ms * 1e-3) / 1e9,
+                          "roofline_frac": nbytes / (ms * 1e-3) / 1e9 / hbm, "peak_source": which,
+                          "note": note, "steps": steps, "warmup": warmup}), flush=True)
+
+    rn = lambda *s: torch.randn(s, generator=g, device=device).to(BF)
+    # ---- v4: B=8, T=4096 as 2 x 2048, C=2048, bf16 (the only dtype the project's kernel has)
+    L4 = lib("libref_wkv4.so")
+    if L4 is not None:
+        B, T, seg, C = 8, 4096, 2048, 2048
+        k, v, gy = [[rn(B, seg, C) for _ in range(T // seg)] for _ in range(3)]
+        w = -torch.exp(torch.rand(C, generator=g, device=device) * 6 - 5)
+        u = (torch.rand(C, generator=g, device=device) * 2 - 1).to(BF)
+        st = [torch.zeros((B, C, 3), device=device) for _ in range(T // seg + 1)]
+        st[0][..., 2] = -1e38
+        gst = [torch.empty((B, C, 3), device=device) for _ in range(T // seg + 1)]
+        y, gk, gv = rn(B, seg, C), rn(B, seg, C), rn(B, seg, C)
+        gw, gu = rn(B, C), rn(B, C)
+
+        def step4():
+            n = T // seg
+            for i in range(n):
+                L4.ref_wkv4_forward(B, seg, C, P(w), P(u), P(k[i]), P(v[i]), P(st[i]), P(y), P(st[i + 1]))
+            for i in reversed(range(n)):
+                gin = None if i == n - 1 else P(gst[i + 1])
+                L4.ref_wkv4_backward(B, seg, C, P(w), P(u), P(k[i]), P(v[i]), P(st[i]), P(gy[i]), gin,
+                                     P(gw), P(gu), P(gk), P(gv), P(gst[i]))
+        report("v4", "RWKV-v4neo/cuda/wkv_cuda_bf16.cu:160-172", B, T, C, 8, _time_steps(step4, steps, warmup),
+               "bf16 I/O; state and its gradient carried over 2 segments of 2048")
+    # ---- v5: B=8, T=4096 as 2 x 2048, H=32; zero state (its backward ignores the state)
+    L5 = lib("libref_wkv5.so")
+    if L5 is not None:
+        B, T, seg, H = 8, 4096, 2048, 32
+        C = H * 64
+        r, k, v, gy = [[rn(B, seg, C) for _ in range(T // seg)] for _ in range(4)]
+        x = torch.rand((H, 64), generator=g, device=device) * 5 - 6
+        ew = -torch.exp(x)
+        eew = torch.exp(ew)
+        u = (torch.rand((H, 64), generator=g, device=device) * 2 - 1).to(BF)
+        zero = torch.zeros((B, H, 64, 64), device=device)
+        y, gr, gk, gv = rn(B, seg, C), rn(B, seg, C), rn(B, seg, C), rn(B, seg, C)
+        gw, gu = rn(B, C), rn(B, C)
+
+        def step5():
+            for i in range(T // seg):
+                zero.zero_()
+                L5.ref_wkv5_forward(1, B, seg, C, H, P(zero), P(r[i]), P(k[i]), P(v[i]), P(eew), P(u), P(y))
+            zero.zero_()
+            for i in reversed(range(T // seg)):
+                L5.ref_wkv5_backward(1, B, seg, C, H, P(zero), P(r[i]), P(k[i]), P(v[i]), P(eew), P(ew), P(u),
+                                     P(gy[i]), P(gr), P(gk), P(gv), P(gw), P(gu))
+        report("v5", "RWKV-v5/src/module/cuda/wkv5_cuda.cu:348-383", B, T, C, 11, _time_steps(step5, steps, warmup),
+               "bf16; every segment from a zero state (the kernel indexes its state without the batch "
+               "row and its backward ignores it)")
+    # ---- v6: one batch row of the 7B-shape workload, T=16384 as 4 x 4096, H=64
+    L6 = lib("libref_wkv6state.so")
+    if L6 is not None:
+        B, T, seg, H = 1, 16384, 4096, 64
+        C = H * 64
+        r, k, v, gy = [[rn(B, seg, C) for _ in range(T // seg)] for _ in range(4)]
+        ew = [(-torch.exp((torch.randn((B, seg, C), generator=g, device=device) * 0.5 - 0.6).to(BF).float()))
+              for _ in range(T // seg)]
+        u = (torch.rand((H, 64), generator=g, device=device) * 2 - 1).to(BF)
+        s = [torch.zeros((B, H, 64, 64), device=device, dtype=BF) for _ in range(T // seg + 1)]
+        y, gr, gk, gv, gw = rn(B, seg, C), rn(B, seg, C), rn(B, seg, C), rn(B, seg, C), rn(B, seg, C)
+        gu, gs = rn(B, C), rn(B, H, 64, 64)
+
+        def step6():
+            n = T // seg
+            for i in range(n):
+                s[i + 1].copy_(s[i])
+                L6.ref_wkv6_forward(B, seg, C, H, P(r[i]), P(k[i]), P(v[i]), P(ew[i]), P(u), P(s[i + 1]), P(y))
+            for i in reversed(range(n)):
+                L6.ref_wkv6_backward(B, seg, C, H, P(r[i]), P(k[i]), P(v[i]), P(ew[i]), P(u), P(s[i]), P(gy[i]),
+                                     P(gr), P(gk), P(gv), P(gw), P(gu), P(gs))
+        report("v6", "RWKV-v6/src/module/cuda/wkv6state_cuda_v1.cu:295-308", B, T, C, 14,
+               _time_steps(step6, steps, warmup),
+               "bf16, B=1 (the kernel indexes its state without the batch row): one of the workload's "
+               "4 batch rows; state carried forward, its gradient output not chained (the kernel takes none)")
+    if L4 is None and L5 is None and L6 is None:
+        print(json.dumps({"ref_kernels": "unavailable", "why": "oracle/_ref/*.so not prebuilt"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=500,
+                    help="timed steps (the default makes the timed region about 2 s)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: every GPU runs the whole workload; strong: the workload's heads "
-                         "are split across the GPUs (needs H divisible by N)")
-    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3],
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="strong (default): the workload's heads are split across the GPUs (needs H "
+                         "divisible by N); weak: every GPU runs the whole workload")
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4],
                     help="3 (default): the headline v6 7B-shape workload; 1: v4 fp32 B=8 T=4096 C=2048; "
-                         "2: v5 bf16 1.5B shape (side measurements, one GPU)")
+                         "2: v5 bf16 1.5B shape; 4: one GPU's 5-head slice of the v6 1M-token stream "
+                         "(side measurements, one GPU)")
+    ap.add_argument("--ref-kernels", action="store_true",
+                    help="side measurement: the project's own CUDA kernels (oracle/_ref/, compiled "
+                         "unchanged for sm_100a) on the shapes they are valid for")
+    ap.add_argument("--segments", type=int, default=256, help="--config 4: BPTT segments of 4096 tokens")
     ap.add_argument("--small", action="store_true",
                     help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
                          "still larger than L2) instead of the benchmark workload")
@@ -537,6 +848,10 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.ref_kernels:
+        run_ref_kernels(args)
+    elif args.config == 4:
+        run_stream_config(args)
     elif args.config != 3:
         run_side_config(args)
     else:

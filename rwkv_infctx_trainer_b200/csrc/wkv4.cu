@@ -258,10 +258,14 @@ bool g_scratch_known[kMaxDevices];
 
 // In host code `g_v4_static_scratch` names a host-side shadow, not device
 // memory; the device address has to be asked for, on the device in question.
+// The answer is remembered per device ordinal.  It belongs to the device's
+// primary context (the one the runtime API uses): after cudaDeviceReset, or with
+// another context made current through the driver API, it is no longer valid --
+// this entry point is for processes that do neither.
 int static_scratch_address(void **out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return WKV_ERR_LAUNCH;
-    if (!g_scratch_known[dev]) {
+    if (!__atomic_load_n(&g_scratch_known[dev], __ATOMIC_ACQUIRE)) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_v4_static_scratch) != cudaSuccess || p == nullptr) {
             cudaGetLastError();
@@ -293,8 +297,10 @@ extern "C" int wkv4_backward_static(int B, int T, int C, int dtype, const float 
     if (err != WKV_OK) return err;
     cudaStream_t s = (cudaStream_t)stream;
     float *ws = (float *)scratch;
-    // Nothing in the scratch has to start at zero: the kernel's forward sweep
-    // writes every tile-start state before its reverse sweep reads it.
+    // Nothing in the scratch has to start at zero: both kernel families write every word of it
+    // that they later read (tile-start states; piece summaries, scanned states and partial sums).
+    if (T >= PAR_MIN_T)   // the same time-parallel kernels wkv4_backward runs, on the built-in array
+        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
     switch (dtype) {
         case WKV_F32:
             return bwd<float>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);

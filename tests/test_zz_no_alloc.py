@@ -83,15 +83,22 @@ def test_static_scratch_backward_equals_workspace_backward_twice_in_a_row():
 
 
 def test_static_scratch_rejects_oversized_problem_without_launching():
+    """B=8, T=4096, C=2048 in bf16 needs more scratch than the built-in array holds.  The buffers
+    are real and of full size, so that if the size check ever regressed the call would run on
+    valid memory and fail this assert rather than fault the device."""
     import rwkv_infctx_trainer_b200._lib as L
     lib = L.load()
     limit = lib.wkv4_backward_static_limit()
-    B, T, C = 64, 4096, 4096
+    B, T, C = 8, 4096, 2048
     assert lib.wkv4_backward_workspace(B, T, C) > limit
-    t = torch.zeros(16, device="cuda")
-    p = t.data_ptr()
-    code = lib.wkv4_backward_static(B, T, C, L.WKV_F32, p, p, p, p, None, p, None, p, p, p, p, None,
-                                    torch.cuda.current_stream().cuda_stream)
+    bf = torch.bfloat16
+    k, v, gy, gk, gv = (torch.zeros((B, T, C), device="cuda", dtype=bf) for _ in range(5))
+    w = -torch.ones(C, device="cuda")
+    u = torch.zeros(C, device="cuda", dtype=bf)
+    gw, gu = torch.zeros((B, C), device="cuda"), torch.zeros((B, C), device="cuda")
+    code = lib.wkv4_backward_static(B, T, C, L.WKV_BF16, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                    None, gy.data_ptr(), None, gw.data_ptr(), gu.data_ptr(), gk.data_ptr(),
+                                    gv.data_ptr(), None, torch.cuda.current_stream().cuda_stream)
     assert code == 8
     assert b"built-in" in lib.wkv_error_string(code)
     torch.cuda.synchronize()
