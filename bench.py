@@ -207,62 +207,63 @@ def make_inputs(wl, device, pinned_host=False):
 
 
 class Runner:
-    """Device-resident step: raw op calls (package wrappers over the C ABI), preallocated
-    outputs are created by the wrappers; events around every backward launch."""
+    """Device-resident step.  Every call of the step is prepared once (outputs, workspaces and
+    the forward-to-backward hand-over allocated up front), so a step is 2 x segments crossings of
+    the C ABI and nothing else on the host; events around every forward and backward call."""
 
-    def __init__(self, wl, dev_inputs, device):
+    def __init__(self, wl, seg_tensors, u, device):
+        import ctypes
         import rwkv_infctx_trainer_b200 as W
         from rwkv_infctx_trainer_b200 import wkv56
-        self.W, self.wkv56, self.wl, self.d, self.device = W, wkv56, wl, dev_inputs, device
-        self.bounds = [(t0, min(wl["T"], t0 + wl["seg"])) for t0 in range(0, wl["T"], wl["seg"])]
+        self.W, self.wkv56, self.wl, self.device = W, wkv56, wl, device
         B, H, N = wl["B"], wl["H"], wl["N"]
-        self.state0 = torch.zeros((B, H, N, N), device=device)
-        self.bwd_events = []
-        self.fwd_events = []
+        n = len(seg_tensors["r"])
+        states = [torch.zeros((B, H, N, N), device=device) for _ in range(n + 1)]
+        gstates = [torch.empty((B, H, N, N), device=device) for _ in range(n + 1)]
+        self.fwd, self.bwd = [], []
+        for i in range(n):
+            t = {m: seg_tensors[m][i] for m in ("r", "k", "v", "w", "gy")}
+            f = wkv56.prepare_forward("wkv6", t["r"], t["k"], t["v"], t["w"], u, states[i], w_kind=W.WKV_W_RAW,
+                                      state_out=states[i + 1])
+            b = wkv56.prepare_backward("wkv6", t["r"], t["k"], t["v"], t["w"], u, states[i], t["gy"],
+                                       None if i == n - 1 else gstates[i + 1], w_kind=W.WKV_W_RAW,
+                                       ckpt=f.ckpt, gstate_in=gstates[i])
+            self.fwd.append(f); self.bwd.append(b)
+        self.bwd_events, self.fwd_events = [], []
         self.launches = 0
         # kernels per call: k_chunk_fwd ; k_chunk_dscan, k_chunk_bwd, k_reduce_partials -- and, when the
         # library cuts the chains into time groups (few chains per GPU), a summary pass and a group
         # scan more for the forward and for the dS scan
-        import ctypes
         a = wkv56._args("wkv6", B, wl["seg"], H, torch.bfloat16, W.WKV_W_RAW, W.WKV_STATE_KV, W.WKV_PATH_AUTO)
         split = W._lib.load().wkv6_forward_workspace(ctypes.byref(a)) > 256
         self.fwd_launches, self.bwd_launches = (3, 5) if split else (1, 3)
 
-    def seg(self, name, t0, t1):
-        return self.d[name][:, t0:t1].contiguous()     # the op takes contiguous [B, T_seg, C] tensors
-
     def step(self, record=False):
-        W, d = self.W, self.d
-        states = [self.state0]
-        ckpts = []
-        for t0, t1 in self.bounds:
+        for f in self.fwd:
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            y, s, ck = self.wkv56.forward("wkv6", self.seg("r", t0, t1), self.seg("k", t0, t1),
-                                          self.seg("v", t0, t1), self.seg("w", t0, t1), d["u"],
-                                          states[-1], w_kind=W.WKV_W_RAW, save_ckpt=True)
-            ckpts.append(ck)
+            f.run()
             if record:
                 e1.record()
                 self.fwd_events.append((e0, e1))
-            states.append(s)
             self.launches += self.fwd_launches
-        gs = None
-        out = None
-        for (t0, t1), s_in, ck in reversed(list(zip(self.bounds, states[:-1], ckpts))):
+        for b in reversed(self.bwd):
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            out = self.wkv56.backward("wkv6", self.seg("r", t0, t1), self.seg("k", t0, t1),
-                                      self.seg("v", t0, t1), self.seg("w", t0, t1), d["u"], s_in,
-                                      self.seg("gy", t0, t1), gs, w_kind=W.WKV_W_RAW, ckpt=ck)
+            b.run()
             if record:
                 e1.record()
                 self.bwd_events.append((e0, e1))
-            gs = out[5]
             self.launches += self.bwd_launches
-        return out
+
+    def status(self) -> int:
+        """OR of the status words of every call (0 = no device-side wait ran out)"""
+        code = 0
+        for c in self.fwd + self.bwd:
+            code |= c.status()
+        return code
 
 
 def contiguous_segments(t, bounds):
@@ -286,6 +287,8 @@ def run_ours(args):
         wl.update(name=wl["name"] + "_small", B=1, T=4096)
     if args.medium:
         wl.update(name=wl["name"] + "_medium", T=4096)
+    if args.heads:
+        wl.update(name=wl["name"] + f"_{args.heads}heads", H=args.heads, C=args.heads * wl["N"])
     H_total = wl["H"]
     if args.scaling is None:
         args.scaling = "strong"
@@ -301,11 +304,7 @@ def run_ours(args):
     bounds = [(t0, min(T, t0 + wl["seg"])) for t0 in range(0, T, wl["seg"])]
     segd = {n: contiguous_segments(dev[n], bounds) for n in ("r", "k", "v", "w", "gy")}
 
-    class SegRunner(Runner):
-        def seg(self, name, t0, t1):
-            return segd[name][t0 // wl["seg"]]
-
-    runner = SegRunner(wl, dev, device)
+    runner = Runner(wl, segd, dev["u"], device)
     torch.cuda.synchronize()
 
     def barrier():
@@ -338,6 +337,8 @@ def run_ours(args):
         sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     ms = t_start.elapsed_time(t_end)
+    if runner.status() != 0:
+        raise SystemExit("a device-side wait ran out during the timed region: the results are invalid")
     launches = runner.launches
     bwd_ms = [a.elapsed_time(b) for a, b in runner.bwd_events]
     fwd_ms = [a.elapsed_time(b) for a, b in runner.fwd_events]
@@ -688,14 +689,19 @@ def run_stream_config(args):
     s0 = torch.zeros((B, H, 64, 64), device=device)
 
     def make_step(groups):
+        # every call prepared once: a step is 2 * nseg crossings of the C ABI
+        states = [s0] + [torch.empty_like(s0) for _ in range(nseg)]
+        calls = []
+        for i in range(nseg):
+            f = wkv56.prepare_forward("wkv6", r[i], k[i], v[i], w[i], u, states[i], w_kind=W.WKV_W_RAW,
+                                      state_out=states[i + 1], time_groups=groups)
+            b = wkv56.prepare_backward("wkv6", r[i], k[i], v[i], w[i], u, states[i], gy[i], None,
+                                       w_kind=W.WKV_W_RAW, ckpt=f.ckpt, want_gstate=False, time_groups=groups)
+            calls += [f, b]
+
         def step():
-            state = s0
-            for i in range(nseg):
-                y, s_next, ck = wkv56.forward("wkv6", r[i], k[i], v[i], w[i], u, state, w_kind=W.WKV_W_RAW,
-                                              save_ckpt=True, time_groups=groups)
-                wkv56.backward("wkv6", r[i], k[i], v[i], w[i], u, state, gy[i], None, w_kind=W.WKV_W_RAW,
-                               ckpt=ck, want_gstate=False, time_groups=groups)
-                state = s_next
+            for c in calls:
+                c.run()
         return step
 
     steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
@@ -843,6 +849,8 @@ def main():
     ap.add_argument("--medium", action="store_true",
                     help="profiling aid: the benchmark's batch and heads but a single 4096-token segment "
                          "(under 2 GB on the device) -- the grid sizes of the benchmark's launches")
+    ap.add_argument("--heads", type=int, default=0,
+                    help="profiling aid: this many heads instead of 64 (8 = what one of 8 GPUs gets)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: no end-to-end leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline leg")
     args = ap.parse_args()

@@ -168,3 +168,73 @@ def backward(variant: str, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
         _watch_status(lib, a, variant, ws, f"{variant}_backward")
         del ws
     return gr, gk, gv, gw, gu, gsi
+
+
+class Prepared:
+    """One v5/v6 forward or backward call with every buffer (outputs, workspace, hand-over)
+    allocated up front.  ``run()`` only crosses the C ABI -- for a loop that calls the op with the
+    same buffers every step and wants no allocation and no Python bookkeeping on the way.
+    The tensors are attributes (``y``, ``state_out``, ``ckpt`` / ``gr`` ... ``gstate_in``).
+    ``status()`` synchronises and returns the call's status word (0 = ok)."""
+
+    def __init__(self, fn, what, args, dev, **tensors):
+        self._fn, self._what, self._a, self._dev = fn, what, args, dev
+        self.__dict__.update(tensors)
+
+    def run(self):
+        L.check(self._fn(ctypes.byref(self._a), L.stream_handle(self._dev)), self._what)
+
+    def status(self) -> int:
+        torch.cuda.synchronize(self._dev)
+        ws = self.workspace
+        return 0 if ws is None or ws.numel() < 4 else int(ws[:4].view(torch.int32).item())
+
+
+def prepare_forward(variant, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE_KV,
+                    path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=True, time_groups=0) -> Prepared:
+    B, T, C = r.shape
+    H = C // HEAD_SIZE
+    dev = L.require_cuda(r, k, v, w, u, state_in)
+    _check_layout(B, T, C, r=r, k=k, v=v, w=w if variant == "wkv6" else None)
+    lib = L.load()
+    y = torch.empty_like(r)
+    if state_out is None:
+        state_out = torch.empty((B, H, HEAD_SIZE, HEAD_SIZE), device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, time_groups, r=r, k=k, v=v, w=w,
+                  u=u, state_in=state_in, y=y, state_out=state_out)
+        ckpt = None
+        if save_ckpt:
+            nck = lib.wkv56_state_ckpt_bytes(ctypes.byref(a), int(variant == "wkv6"))
+            if nck:
+                ckpt = torch.empty(nck, dtype=torch.uint8, device=dev)
+                a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), nck
+        ws = _with_workspace(lib, variant, "forward", a, dev)
+    keep = (r, k, v, w, u, state_in)
+    return Prepared(getattr(lib, f"{variant}_forward"), f"{variant}_forward", a, dev, y=y,
+                    state_out=state_out, ckpt=ckpt, workspace=ws, _keep=keep)
+
+
+def prepare_backward(variant, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind,
+                     layout=L.WKV_STATE_KV, path=L.WKV_PATH_AUTO, ckpt=None, gstate_in=None,
+                     want_gstate=True, time_groups=0) -> Prepared:
+    B, T, C = r.shape
+    H = C // HEAD_SIZE
+    dev = L.require_cuda(r, k, v, w, u, state_in, gy, gstate_out)
+    _check_layout(B, T, C, r=r, k=k, v=v, gy=gy, w=w if variant == "wkv6" else None)
+    lib = L.load()
+    gr, gk, gv = torch.empty_like(r), torch.empty_like(r), torch.empty_like(r)
+    gw = torch.empty_like(r) if variant == "wkv6" else torch.empty((B, C), device=dev, dtype=torch.float32)
+    gu = torch.empty((B, C), device=dev, dtype=torch.float32)
+    if gstate_in is None and want_gstate:
+        gstate_in = torch.empty((B, H, HEAD_SIZE, HEAD_SIZE), device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        a = _args(variant, B, T, H, r.dtype, w_kind, layout, path, time_groups, r=r, k=k, v=v, w=w,
+                  u=u, state_in=state_in, gy=gy, gstate_out=gstate_out, gr=gr, gk=gk, gv=gv, gw=gw,
+                  gu=gu, gstate_in=gstate_in)
+        if ckpt is not None:
+            a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), ckpt.numel()
+        ws = _with_workspace(lib, variant, "backward", a, dev)
+    keep = (r, k, v, w, u, state_in, gy, gstate_out, ckpt)
+    return Prepared(getattr(lib, f"{variant}_backward"), f"{variant}_backward", a, dev, gr=gr, gk=gk,
+                    gv=gv, gw=gw, gu=gu, gstate_in=gstate_in, workspace=ws, _keep=keep)
