@@ -181,7 +181,20 @@ typedef struct wkv_args {
      * from B*H, T and the SM count; 1 = never split; n > 1 = n groups (at most one per chunk).
      * The *_workspace() sizes depend on it: fill it in before asking for them. */
     int time_groups;
+    /* Chunked path, forward only: fp32 states for a later re-run of the same forward call (what
+     * activation checkpointing does, RWKV-v6/src/model.py:657-665).  wkv56_group_states_bytes()
+     * bytes.  WKV_GROUP_STATES_SAVE: the call also stores the state at the start of every 8th
+     * chunk (512 tokens) there.  WKV_GROUP_STATES_USE: the call starts every 8-chunk group from the
+     * stored state instead of scanning: the groups run in parallel, no serial pass over T, and
+     * y, state_out and the hand-over are bit-identical to those of the call that saved them
+     * (same inputs). */
+    void *group_states;
+    size_t group_states_bytes;
+    int group_states_mode;
 } wkv_args_t;
+
+enum { WKV_GROUP_STATES_NONE = 0, WKV_GROUP_STATES_SAVE = 1, WKV_GROUP_STATES_USE = 2 };
+size_t wkv56_group_states_bytes(const wkv_args_t *a);
 
 /* Bytes of wkv_args_t.state_ckpt for these arguments (0 when the call would not run on
  * the chunked kernels). */

@@ -16,6 +16,7 @@ WKV_F32, WKV_BF16, WKV_F16 = 0, 1, 2
 WKV_W_RAW, WKV_W_NEGEXP = 0, 1
 WKV_STATE_KV, WKV_STATE_VK = 0, 1
 WKV_PATH_AUTO, WKV_PATH_SCALAR, WKV_PATH_CHUNKED = 0, 1, 2
+WKV_GROUP_STATES_NONE, WKV_GROUP_STATES_SAVE, WKV_GROUP_STATES_USE = 0, 1, 2
 
 DTYPE_CODE = {torch.float32: WKV_F32, torch.bfloat16: WKV_BF16, torch.float16: WKV_F16}
 
@@ -34,6 +35,7 @@ class WkvArgs(ctypes.Structure):
         ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t),
         ("state_ckpt", _vp), ("state_ckpt_bytes", ctypes.c_size_t),
         ("time_groups", ctypes.c_int),
+        ("group_states", _vp), ("group_states_bytes", ctypes.c_size_t), ("group_states_mode", ctypes.c_int),
     ]
 
 
@@ -43,7 +45,7 @@ EXPORTS = [
     "wkv4_backward_static_limit", "wkv4_backward_static",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
-    "wkv_selftest_wait_timeout", "wkv56_selftest_abort",
+    "wkv_selftest_wait_timeout", "wkv56_selftest_abort", "wkv56_group_states_bytes",
 ]
 
 _lib = None
@@ -87,6 +89,8 @@ def load() -> ctypes.CDLL:
     lib.wkv4_backward_static.argtypes = [i, i, i, i] + [f] * 12 + [_vp]
     lib.wkv56_uses_chunked.restype = i
     lib.wkv56_uses_chunked.argtypes = [ctypes.POINTER(WkvArgs), i]
+    lib.wkv56_group_states_bytes.restype = ctypes.c_size_t
+    lib.wkv56_group_states_bytes.argtypes = [ctypes.POINTER(WkvArgs)]
     lib.wkv56_state_ckpt_bytes.restype = ctypes.c_size_t
     lib.wkv56_state_ckpt_bytes.argtypes = [ctypes.POINTER(WkvArgs), i]
     lib.wkv_selftest_wait_timeout.restype = i

@@ -70,9 +70,11 @@ struct FwdParams {
     const float *wvec;        // v5: per-channel decay parameter [H*64]
     const float *state_in;    // G == 1: the caller's state (layout `layout`)
     const float *gstart;      // G > 1, pass C: [B*H*G, 64, 64] state at the start of every group ([key,value])
-    float *state_out;         // G == 1 only (with G > 1 the group scan writes it)
+    float *state_out;         // written by the CTA whose group ends the segment
     float *gU;                // pass A: [B*H*G, 64, 64] state a group builds from zero ([key,value])
     float *gD;                // pass A: [B*H*G, 64] decay of a whole group per key channel
+    float *gsave;             // or NULL: [B*H, ceil(nchunk/Lsave), 64, 64] fp32 state at the start of every
+    int Lsave;                // Lsave-th chunk ([key,value]), for a later call that restarts from them
     __nv_bfloat16 *y;
     __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
     float *dchunk;            // [B*H,nchunk,64] decay of each whole chunk, or NULL; with it the
@@ -492,6 +494,13 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                 st_tile(s.sbf, row, (vcol0 >> 3), q0);
                 st_tile(s.sbf, row, (vcol0 >> 3) + 1, q1);
             }
+            if (P.gsave && jn < n && (j0 + jn) % P.Lsave == 0) {
+                const int nsave = (P.nchunk + P.Lsave - 1) / P.Lsave;
+                float4 *dst = reinterpret_cast<float4 *>(
+                    P.gsave + ((size_t)bh * nsave + (j0 + jn) / P.Lsave) * 4096 + row * 64 + vcol0);
+#pragma unroll
+                for (int q = 0; q < 4; q++) dst[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+            }
             if (P.ckpt && (jn < n || j0 + n == P.nchunk)) {
                 uint4 *dst = reinterpret_cast<uint4 *>(
                     P.ckpt + (((size_t)bh * (P.nchunk + 1) + j0 + jn) * 64 + row) * 64 + vcol0);
@@ -581,7 +590,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 4; q++) dst[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
             if (vcol0 == 0) P.gD[(size_t)unit * 64 + row] = dprod;
-        } else if (P.state_out) {
+        } else if (P.state_out && j0 + n == P.nchunk) {
 #pragma unroll
             for (int q = 0; q < 16; q++) {
                 const int vc = vcol0 + q;
@@ -718,6 +727,22 @@ GroupPlan plan_groups(int BH, int nchunk, int requested) {
     return P;
 }
 
+// The plan of a forward call.  A call that saves group states keeps its groups a multiple of the
+// saving distance long: a restart then runs, inside every saved group, exactly the operations of
+// the call that saved (which is what makes it bit-identical).  A restart's groups are the saved ones.
+GroupPlan plan_forward(const wkv_args_t *a) {
+    const int n = (a->T + CH - 1) / CH;
+    GroupPlan gp = plan_groups(a->B * a->H, n, a->time_groups);
+    if (a->group_states && a->group_states_mode == WKV_GROUP_STATES_USE) {
+        gp.L = SAVE_EVERY;
+        gp.G = (n + SAVE_EVERY - 1) / SAVE_EVERY;
+    } else if (a->group_states && a->group_states_mode == WKV_GROUP_STATES_SAVE && gp.G > 1) {
+        gp.L = (gp.L + SAVE_EVERY - 1) / SAVE_EVERY * SAVE_EVERY;
+        gp.G = (n + gp.L - 1) / gp.L;
+    }
+    return gp;
+}
+
 GroupLayout group_layout(size_t units) {
     auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
     GroupLayout L;
@@ -740,8 +765,13 @@ int launch_group_scan(const void *group_ws, int BH, int G, const float *init, fl
 }  // namespace chunked
 
 // workspace layout: [0,256) status words; then the time-group buffers when the chains are split
+size_t chunked_group_states_bytes(const wkv_args_t *a) {
+    const size_t n = (a->T + CH - 1) / CH;
+    return (size_t)a->B * a->H * ((n + SAVE_EVERY - 1) / SAVE_EVERY) * 4096 * sizeof(float);
+}
+
 size_t chunked_forward_workspace(const wkv_args_t *a, bool per_token_w) {
-    const GroupPlan gp = plan_groups(a->B * a->H, (a->T + CH - 1) / CH, a->time_groups);
+    const GroupPlan gp = plan_forward(a);
     return 256 + (gp.G > 1 ? group_layout((size_t)a->B * a->H * gp.G).total : 0) + chunked_wconv_bytes(a, per_token_w);
 }
 
@@ -759,8 +789,12 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     }
     FwdParams p;
     p.T = T; p.H = H; p.nchunk = (T + CH - 1) / CH; p.layout = a->state_layout; p.w_kind = a->w_kind;
-    const GroupPlan gp = plan_groups(BH, p.nchunk, a->time_groups);
+    // restarting from saved group states: the groups are the saved ones, and only pass C runs
+    const bool restart = a->group_states && a->group_states_mode == WKV_GROUP_STATES_USE;
+    const GroupPlan gp = plan_forward(a);
     p.G = gp.G; p.L = gp.L;
+    p.gsave = (a->group_states && a->group_states_mode == WKV_GROUP_STATES_SAVE) ? (float *)a->group_states : nullptr;
+    p.Lsave = SAVE_EVERY;
     p.u = (const __nv_bfloat16 *)a->u;
     p.wvec = per_token_w ? nullptr : (const float *)a->w;
     p.status = (int *)a->workspace;
@@ -779,7 +813,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
 
     const GroupLayout GL = group_layout((size_t)BH * gp.G);
     char *g = (char *)group_ws;
-    if (gp.G > 1) {
+    if (gp.G > 1 && !restart) {
         // A: what every group adds to the state, from zero
         if (!set_max_smem_once(kerns[pt][FWD_SUMMARY], (int)smem, attr_done[pt][FWD_SUMMARY])) return WKV_ERR_LAUNCH;
         p.state_in = nullptr; p.gstart = nullptr; p.state_out = nullptr;
@@ -787,15 +821,16 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
         p.y = nullptr; p.ckpt = nullptr; p.dchunk = nullptr;
         kerns[pt][FWD_SUMMARY]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
-        // B: the state at the start of every group, and the state after the segment
-        if (launch_group_scan(g, BH, gp.G, a->state_in, a->state_out, a->state_layout, false, stream) != WKV_OK)
+        // B: the state at the start of every group.  (The state after the segment is left to the last
+        // group of pass C, so that a later restart from saved states reproduces it bit for bit.)
+        if (launch_group_scan(g, BH, gp.G, a->state_in, nullptr, a->state_layout, false, stream) != WKV_OK)
             return WKV_ERR_LAUNCH;
     }
     // C (or the whole job when the chains are not split)
     if (!set_max_smem_once(kerns[pt][mode], (int)smem, attr_done[pt][mode])) return WKV_ERR_LAUNCH;
     p.state_in = a->state_in;
-    p.gstart = gp.G > 1 ? (const float *)(g + GL.gstart) : nullptr;
-    p.state_out = gp.G > 1 ? nullptr : a->state_out;
+    p.gstart = restart ? (const float *)a->group_states : gp.G > 1 ? (const float *)(g + GL.gstart) : nullptr;
+    p.state_out = a->state_out;      // written by the group that ends the segment
     p.gU = nullptr; p.gD = nullptr;
     p.y = (__nv_bfloat16 *)a->y;
     const CkptLayout CL = ckpt_layout(B, T, H);

@@ -229,9 +229,11 @@ inline CkptLayout ckpt_layout(int B, int T, int H) {
 struct GroupPlan {
     int G, L;
 };
+constexpr int SAVE_EVERY = 8;     // chunks between two saved fp32 states (wkv_args_t.group_states)
 // requested: 0 = decide from the number of chains and the device's SM count, 1 = never split,
 // > 1 = that many groups (at most one per chunk)
 GroupPlan plan_groups(int BH, int nchunk, int requested);
+GroupPlan plan_forward(const wkv_args_t *a);
 
 // Scratch of the time-group passes, for `units` = chains * G (all fp32, state matrices [key,value]):
 //   gU      [units, 64, 64]  what a group adds to the state (gradient) starting from zero
@@ -256,6 +258,7 @@ struct ChunkedTest {
 };
 
 int device_sm_count();
+size_t chunked_group_states_bytes(const wkv_args_t *a);
 // v6 with the fp32 ew = -exp(x) encoding: bytes of, and conversion into, a bf16 x tensor (a no-op otherwise)
 size_t chunked_wconv_bytes(const wkv_args_t *a, bool per_token_w);
 int chunked_convert_w(wkv_args_t *a, bool per_token_w, void *scratch, cudaStream_t s);

@@ -1016,6 +1016,8 @@ int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &
         wkv_args_t f = *a;
         f.y = nullptr;
         f.state_out = nullptr;
+        f.group_states = nullptr;
+        f.group_states_mode = WKV_GROUP_STATES_NONE;
         const int err = chunked_forward_impl(&f, per_token_w, fwd_ck, ws + L.groups, tst, stream);
         if (err != WKV_OK) return err;
     }

@@ -17,6 +17,8 @@ int check_common(const wkv_args_t *a, bool backward, bool per_token_w) {
     if (a->path != WKV_PATH_AUTO && a->path != WKV_PATH_SCALAR && a->path != WKV_PATH_CHUNKED)
         return WKV_ERR_DTYPE;
     if (a->time_groups < 0) return WKV_ERR_SHAPE;
+    if (a->group_states_mode < WKV_GROUP_STATES_NONE || a->group_states_mode > WKV_GROUP_STATES_USE) return WKV_ERR_DTYPE;
+    if (a->group_states && !aligned16(a->group_states)) return WKV_ERR_ALIGN;
     if (a->B == 0 || a->H == 0) return WKV_OK;
     if (!a->u) return WKV_ERR_NULL;
     if (!per_token_w && !a->w) return WKV_ERR_NULL;
@@ -67,6 +69,10 @@ int forward(const wkv_args_t *a, bool pt, void *stream, const ChunkedTest &tst =
     const size_t need = fwd_ws(a, pt);
     if (need && (!a->workspace || a->workspace_bytes < need)) return WKV_ERR_WORKSPACE;
     if (ch && a->state_ckpt && a->state_ckpt_bytes < wkv56_state_ckpt_bytes(a, pt)) return WKV_ERR_WORKSPACE;
+    if (a->group_states && a->group_states_mode != WKV_GROUP_STATES_NONE) {
+        if (!ch) return WKV_ERR_UNSUPPORTED;
+        if (a->group_states_bytes < wkv56_group_states_bytes(a)) return WKV_ERR_WORKSPACE;
+    }
     return ch ? chunked_forward(a, pt, tst, s) : scalar_forward(a, pt, s);
 }
 
@@ -105,6 +111,11 @@ const char *wkv_error_string(int code) {
 int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
 
 const char *wkv_version(void) { return "wkv_b200 2 sm_100a"; }
+
+size_t wkv56_group_states_bytes(const wkv_args_t *a) {
+    if (!a || a->B <= 0 || a->H <= 0 || a->T <= 0 || a->N != HEAD || a->dtype != WKV_BF16) return 0;
+    return chunked_group_states_bytes(a);
+}
 
 size_t wkv56_state_ckpt_bytes(const wkv_args_t *a, int per_token_w) {
     if (!wkv56_uses_chunked(a, per_token_w)) return 0;

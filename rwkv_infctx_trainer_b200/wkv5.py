@@ -39,7 +39,7 @@ def _check_shapes(B, T, C, H, r, k, v, u, state):
 
 class WKV5(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, B, T, C, H, r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO):
+    def forward(ctx, B, T, C, H, r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO, saved=None):
         _check_shapes(B, T, C, H, r, k, v, u, state_in)
         dt = r.dtype
         r, k, v = r.contiguous(), k.to(dt).contiguous(), v.to(dt).contiguous()
@@ -47,22 +47,24 @@ class WKV5(torch.autograd.Function):
         uf = u.to(dt).contiguous()
         s_in = state_in.float().contiguous()
         y, s_out, ckpt = wkv56.forward("wkv5", r, k, v, wf, uf, s_in, w_kind=L.WKV_W_RAW, path=path,
-                                       save_ckpt=True)
-        ctx.save_for_backward(r, k, v, wf, uf, s_in)
-        ctx.ckpt = ckpt
+                                       save_ckpt=any(ctx.needs_input_grad), saved=saved)
+        ctx.has_ckpt = ckpt is not None
+        ctx.save_for_backward(*((r, k, v, wf, uf, s_in) + ((ckpt,) if ckpt is not None else ())))
         ctx.meta = (B, T, C, H, path, w.dtype, u.dtype, w.shape, u.shape, state_in.dtype)
         return y, s_out.view(B, H, N, N)
 
     @staticmethod
     def backward(ctx, gy, gstate_out):
-        r, k, v, wf, uf, s_in = ctx.saved_tensors
+        st = ctx.saved_tensors          # (one access: saved-tensor hooks unpack once)
+        r, k, v, wf, uf, s_in = st[:6]
+        ckpt = st[6] if ctx.has_ckpt else None
         B, T, C, H, path, wdt, udt, wshape, ushape, sdt = ctx.meta
         gy = gy.to(r.dtype).contiguous()
         gso = None if gstate_out is None else gstate_out.float().contiguous()
         gr, gk, gv, gw, gu, gsi = wkv56.backward("wkv5", r, k, v, wf, uf, s_in, gy, gso,
-                                                 w_kind=L.WKV_W_RAW, path=path, ckpt=ctx.ckpt)
+                                                 w_kind=L.WKV_W_RAW, path=path, ckpt=ckpt)
         return (None, None, None, None, gr, gk, gv, gw.sum(0).view(wshape).to(wdt),
-                gu.sum(0).view(ushape).to(udt), gsi.to(sdt), None)
+                gu.sum(0).view(ushape).to(udt), gsi.to(sdt), None, None)
 
 
 def wkv5(r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO):

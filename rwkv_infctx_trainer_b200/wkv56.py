@@ -97,12 +97,14 @@ def _with_workspace(lib, variant, direction, a, dev):
 
 
 def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE_KV,
-            path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=False, time_groups=0):
+            path=L.WKV_PATH_AUTO, state_out=None, save_ckpt=False, time_groups=0, saved=None):
     """Launch wkv5_forward / wkv6_forward.  All tensors contiguous, on one device.
     Returns (y, state_out); ``state_out`` may be given (it may be ``state_in`` itself).
     With ``save_ckpt`` a third value is returned: the chunk-start states to hand to
     ``backward(..., ckpt=...)`` (None when the call did not run on the chunked kernels).
-    ``time_groups``: see ``wkv_args_t.time_groups`` (0 = the library decides)."""
+    ``time_groups``: see ``wkv_args_t.time_groups`` (0 = the library decides).
+    ``saved``: a ``SavedStates``; empty, the call fills it; filled (by a call with the same
+    inputs), the call restarts from it instead of scanning over T."""
     B, T, C = r.shape
     H = C // HEAD_SIZE
     dev = L.require_cuda(r, k, v, w, u, state_in)
@@ -124,9 +126,13 @@ def forward(variant: str, r, k, v, w, u, state_in, *, w_kind, layout=L.WKV_STATE
             if nck:
                 ckpt = torch.empty(nck, dtype=torch.uint8, device=dev)
                 a.state_ckpt, a.state_ckpt_bytes = L.ptr(ckpt), nck
+        if saved is not None and lib.wkv56_uses_chunked(ctypes.byref(a), int(variant == "wkv6")):
+            saved._attach(lib, a, (variant, B, T, H, r.dtype, w_kind, layout), dev)
         ws = _with_workspace(lib, variant, "forward", a, dev)
         L.check(getattr(lib, f"{variant}_forward")(ctypes.byref(a), L.stream_handle(dev)),
                 f"{variant}_forward")
+        if saved is not None:
+            saved._done(a, state_out)
         _watch_status(lib, a, variant, ws, f"{variant}_forward")
         del ws
     if save_ckpt:
@@ -238,3 +244,38 @@ def prepare_backward(variant, r, k, v, w, u, state_in, gy, gstate_out, *, w_kind
     keep = (r, k, v, w, u, state_in, gy, gstate_out, ckpt)
     return Prepared(getattr(lib, f"{variant}_backward"), f"{variant}_backward", a, dev, gr=gr, gk=gk,
                     gv=gv, gw=gw, gu=gu, gstate_in=gstate_in, workspace=ws, _keep=keep)
+
+
+class SavedStates:
+    """What a forward call leaves for a later re-run of the SAME call (same inputs): the fp32
+    state at the start of every 8th chunk (512 tokens) -- 16 KB per (batch, head) per 512 tokens.
+
+    Made for activation checkpointing (RWKV-v6/src/model.py:657-665 wraps every block in
+    ``deepspeed.checkpointing.checkpoint``): the block's forward runs once without autograd and
+    once more, inside backward, to rebuild what autograd needs.  Keep one ``SavedStates`` per
+    (layer, segment) outside the checkpointed function and pass it to the op in both runs: the
+    first run fills it; the second finds it filled and starts every 8-chunk group from its stored
+    state, all groups in parallel, with no serial pass over T -- and gives bit-identical y,
+    state_out and hand-over.  ``clear()`` it when the inputs change (next training step)."""
+
+    def __init__(self):
+        self.clear()
+
+    def clear(self):
+        self.buf, self.key, self.filled, self.restarts = None, None, False, 0
+
+    def _attach(self, lib, a, key, dev):
+        n = lib.wkv56_group_states_bytes(ctypes.byref(a))
+        if self.filled and self.key == key and self.buf is not None and self.buf.device == dev:
+            a.group_states, a.group_states_bytes = L.ptr(self.buf), n
+            a.group_states_mode = L.WKV_GROUP_STATES_USE
+            self.restarts += 1
+        else:
+            self.buf = torch.empty(n, dtype=torch.uint8, device=dev)
+            self.key, self.filled = key, False
+            a.group_states, a.group_states_bytes = L.ptr(self.buf), n
+            a.group_states_mode = L.WKV_GROUP_STATES_SAVE
+
+    def _done(self, a, state_out):
+        if a.group_states_mode == L.WKV_GROUP_STATES_SAVE:
+            self.filled = True

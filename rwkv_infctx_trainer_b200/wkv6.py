@@ -27,7 +27,7 @@ N = wkv56.HEAD_SIZE
 
 class WKV6(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, B, T, C, H, r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO):
+    def forward(ctx, B, T, C, H, r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO, saved=None):
         if C != H * N:
             raise ValueError(f"C must equal H*{N}")
         for name, t in (("r", r), ("k", k), ("v", v), ("w", w)):
@@ -40,29 +40,34 @@ class WKV6(torch.autograd.Function):
         wx = w.to(dt).contiguous()
         uf = u.to(dt).contiguous()
         s_in = state_in.float().contiguous()
+        # the hand-over to backward is only built when something asks for a gradient (not in the
+        # first, autograd-free run of a checkpointed block)
         y, s_out, ckpt = wkv56.forward("wkv6", r, k, v, wx, uf, s_in, w_kind=L.WKV_W_RAW, path=path,
-                                       save_ckpt=True)
-        ctx.save_for_backward(r, k, v, wx, uf, s_in)
-        ctx.ckpt = ckpt
+                                       save_ckpt=any(ctx.needs_input_grad), saved=saved)
+        ctx.has_ckpt = ckpt is not None
+        ctx.save_for_backward(*((r, k, v, wx, uf, s_in) + ((ckpt,) if ckpt is not None else ())))
         ctx.meta = (B, T, C, H, path, w.dtype, u.dtype, u.shape, state_in.dtype)
         return y, s_out.view(B, H, N, N)
 
     @staticmethod
     def backward(ctx, gy, gstate_out):
-        r, k, v, wx, uf, s_in = ctx.saved_tensors
+        st = ctx.saved_tensors          # (one access: saved-tensor hooks unpack once)
+        r, k, v, wx, uf, s_in = st[:6]
+        ckpt = st[6] if ctx.has_ckpt else None
         B, T, C, H, path, wdt, udt, ushape, sdt = ctx.meta
         gy = gy.to(r.dtype).contiguous()
         gso = None if gstate_out is None else gstate_out.float().contiguous()
         gr, gk, gv, gw, gu, gsi = wkv56.backward("wkv6", r, k, v, wx, uf, s_in, gy, gso,
-                                                 w_kind=L.WKV_W_RAW, path=path, ckpt=ctx.ckpt)
+                                                 w_kind=L.WKV_W_RAW, path=path, ckpt=ckpt)
         return (None, None, None, None, gr, gk, gv, gw.to(wdt), gu.sum(0).view(ushape).to(udt),
-                gsi.to(sdt), None)
+                gsi.to(sdt), None, None)
 
 
-def wkv6(r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO):
-    """Convenience form of ``WKV6.apply`` taking the sizes from ``r``."""
+def wkv6(r, k, v, w, u, state_in, path=L.WKV_PATH_AUTO, saved=None):
+    """Convenience form of ``WKV6.apply`` taking the sizes from ``r``.  ``saved``: a
+    ``wkv56.SavedStates`` shared by the two forward runs of an activation-checkpointed block."""
     B, T, C = r.shape
-    return WKV6.apply(B, T, C, C // N, r, k, v, w, u, state_in, path)
+    return WKV6.apply(B, T, C, C // N, r, k, v, w, u, state_in, path, saved)
 
 
 # ----------------------------------------------------------------------------
@@ -139,8 +144,9 @@ class WKV6STATE_CUDA(torch.autograd.Function):
                                        layout=L.WKV_STATE_VK, state_out=s32, save_ckpt=True)
             if s32.data_ptr() != s.data_ptr():
                 s.copy_(s32.view_as(s))
-            ctx.save_for_backward(r, k, v, wx, u, s_in)
-            ctx.ckpt, ctx.s_dtype, ctx.w_dtype = ckpt, s.dtype, w.dtype
+            ctx.has_ckpt = ckpt is not None
+            ctx.save_for_backward(*((r, k, v, wx, u, s_in) + ((ckpt,) if ckpt is not None else ())))
+            ctx.s_dtype, ctx.w_dtype = s.dtype, w.dtype
             return y
 
     @staticmethod
@@ -148,10 +154,12 @@ class WKV6STATE_CUDA(torch.autograd.Function):
         with torch.no_grad():
             B, T, C, H, dtype = ctx.B, ctx.T, ctx.C, ctx.H, ctx.dtype
             gy = gy.to(dtype).contiguous()
-            r, k, v, wx, u, s_in = ctx.saved_tensors
+            st = ctx.saved_tensors          # (one access: saved-tensor hooks unpack once)
+            r, k, v, wx, u, s_in = st[:6]
+            ckpt = st[6] if ctx.has_ckpt else None
             gr, gk, gv, gw, gu, gs = wkv56.backward("wkv6", r, k, v, wx, u, s_in, gy, None,
                                                     w_kind=L.WKV_W_RAW, layout=L.WKV_STATE_VK,
-                                                    ckpt=ctx.ckpt)
+                                                    ckpt=ckpt)
             gu = torch.sum(gu, 0).view(H, C // H).to(dtype)
             return (None, None, None, None, gr, gk, gv, gw.to(ctx.w_dtype), gu,
                     gs.view(B, H, C // H, C // H).to(ctx.s_dtype))
