@@ -825,6 +825,54 @@ def run_ref_kernels(args):
         print(json.dumps({"ref_kernels": "unavailable", "why": "oracle/_ref/*.so not prebuilt"}), flush=True)
 
 
+def run_neighbours(args):
+    """The fused elementwise neighbours of the op (group-norm * gate, token-shift mixes) on one
+    4096-token segment of the v6 7B-shape workload, forward and backward, next to the PyTorch
+    expressions the trainer runs (RWKV-v6/src/module/TimeMix.py:262-273, 296-298) on the same GPU."""
+    import torch.nn.functional as F
+    import rwkv_infctx_trainer_b200 as W
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    hbm, which = peaks()
+    B, T, H = 4, 4096, 64
+    C = H * 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf = torch.bfloat16
+    rn = lambda *s: torch.randn(s, generator=g, device=device).to(bf)
+    steps, warmup = max(3, min(args.steps, 20)), max(3, min(args.warmup, 5))
+    eps = 64e-5
+    y, gt, gout = rn(B, T, C).requires_grad_(True), rn(B, T, C).requires_grad_(True), rn(B, T, C)
+    wt = torch.ones(C, device=device, dtype=bf).requires_grad_(True)
+    bs = torch.zeros(C, device=device, dtype=bf).requires_grad_(True)
+    x, sh = rn(B, T, C).requires_grad_(True), rn(B, C).requires_grad_(True)
+    maa = torch.rand((5, C), generator=g, device=device).to(bf).requires_grad_(True)
+    m = (rn(5, B, T, C) * 0.3).detach().requires_grad_(True)
+    gout5 = rn(5, B, T, C)
+
+    def fb(fn, grad):
+        def step():
+            fn().backward(grad)
+        return step
+
+    def eager_lnx():
+        return F.group_norm(y.view(-1, C), H, wt, bs, eps).view(B, T, C) * gt
+
+    def eager_mix():
+        dx = torch.cat((sh.unsqueeze(1), x[:, :-1]), 1) - x
+        return x.unsqueeze(0) + dx.unsqueeze(0) * (maa.view(5, 1, 1, C) + m)
+
+    n = B * T * C * 2
+    rows = [("lnx_gate", fb(lambda: W.lnx_gate(y, gt, wt, bs, eps, H), gout), fb(eager_lnx, gout), 8 * n),
+            ("ddlerp5", fb(lambda: W.ddlerp(x, sh, maa, m), gout5), fb(eager_mix, gout5), (1 + 5 + 5 + 1 + 5 + 5 + 1) * n)]
+    for name, ours, eager, nbytes in rows:
+        ms_o, ms_e = _time_steps(ours, steps, warmup), _time_steps(eager, steps, warmup)
+        print(json.dumps({"fused_neighbour": name, "shape": [B, T, C], "ms_fwd_bwd": ms_o,
+                          "algorithmic_gbs": nbytes / (ms_o * 1e-3) / 1e9,
+                          "roofline_frac": nbytes / (ms_o * 1e-3) / 1e9 / hbm, "peak_source": which,
+                          "pytorch_eager_ms_fwd_bwd": ms_e, "speedup_vs_eager": ms_e / ms_o,
+                          "steps": steps, "warmup": warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -842,6 +890,9 @@ def main():
     ap.add_argument("--ref-kernels", action="store_true",
                     help="side measurement: the project's own CUDA kernels (oracle/_ref/, compiled "
                          "unchanged for sm_100a) on the shapes they are valid for")
+    ap.add_argument("--neighbours", action="store_true",
+                    help="side measurement: the fused group-norm*gate and token-shift-mix kernels next to "
+                         "the PyTorch expressions, one 4096-token segment of the v6 7B shape")
     ap.add_argument("--segments", type=int, default=256, help="--config 4: BPTT segments of 4096 tokens")
     ap.add_argument("--small", action="store_true",
                     help="profiling aid: one batch row, one 4096-token segment (170 MB of inputs, "
@@ -858,6 +909,8 @@ def main():
         run_reference(args)
     elif args.ref_kernels:
         run_ref_kernels(args)
+    elif args.neighbours:
+        run_neighbours(args)
     elif args.config == 4:
         run_stream_config(args)
     elif args.config != 3:

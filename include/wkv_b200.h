@@ -223,6 +223,37 @@ int wkv6_backward(const wkv_args_t *a, void *stream);
  * 0 = ok, non-zero = a bounded device-side wait ran out and the results are invalid. */
 int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
 
+/* ------------------------------------------- neighbours of the op in TimeMix --
+ * The elementwise stages on either side of the WKV op, each fused into one pass over its
+ * [B,T,C] tensors (bf16 tensors, fp32 parameters and parameter gradients, fp32 arithmetic).
+ *
+ * wkv_lnx_gate_*: out = ln_x(y) * g of RWKV-v6/src/module/TimeMix.py:296-298 (v5:
+ *   RWKV-v5/src/module/TimeMix.py:318-320), ln_x = GroupNorm(H groups of 64 channels, eps),
+ *   gamma/beta its weight and bias [C], tokens = B*T.  Backward returns gy, gg and the
+ *   parameter gradients ggamma, gbeta [C] (summed over all tokens in a fixed order).
+ *
+ * wkv_ddlerp_*: the token-shift mixes of RWKV-v6/src/module/TimeMix.py:262-273,
+ *   out_i = x + (x_prev - x) * (maa_i + m_i),  i < nmix,  nmix = 1 (the first mix, m = NULL)
+ *   or 5 (xw,xk,xv,xr,xg in the order of m).  x [B,T,C]; x_prev of a row's first token is
+ *   shift [B,C] (last token of the previous segment); maa fp32 [nmix,C]; m, out [nmix,B,T,C].
+ *   Backward: gx [B,T,C], gm [nmix,B,T,C] (when m is given), gmaa fp32 [nmix,C], and
+ *   gshift_out [B,C] = gradient w.r.t. shift; gshift_in [B,C] (or NULL) = what the next
+ *   segment's gshift_out sends back to this segment's last token. */
+int wkv_lnx_gate_forward(int tokens, int H, const void *y, const void *g, const float *gamma,
+                         const float *beta, float eps, void *out, void *stream);
+size_t wkv_lnx_gate_backward_workspace(int tokens, int H);
+int wkv_lnx_gate_backward(int tokens, int H, const void *y, const void *g, const float *gamma,
+                          const float *beta, float eps, const void *gout, void *gy, void *gg,
+                          float *ggamma, float *gbeta, void *workspace, size_t workspace_bytes,
+                          void *stream);
+int wkv_ddlerp_forward(int B, int T, int C, int nmix, const void *x, const void *shift,
+                       const float *maa, const void *m, void *out, void *stream);
+size_t wkv_ddlerp_backward_workspace(int B, int T, int C, int nmix);
+int wkv_ddlerp_backward(int B, int T, int C, int nmix, const void *x, const void *shift,
+                        const float *maa, const void *m, const void *gout, const void *gshift_in,
+                        void *gx, void *gm, void *gshift_out, float *gmaa, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
 /* Library build identification: "wkv_b200 <n> sm_100a". */
 const char *wkv_version(void);
 

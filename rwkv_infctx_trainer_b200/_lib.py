@@ -46,6 +46,8 @@ EXPORTS = [
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
     "wkv_selftest_wait_timeout", "wkv56_selftest_abort", "wkv56_group_states_bytes",
+    "wkv_lnx_gate_forward", "wkv_lnx_gate_backward_workspace", "wkv_lnx_gate_backward",
+    "wkv_ddlerp_forward", "wkv_ddlerp_backward_workspace", "wkv_ddlerp_backward",
 ]
 
 _lib = None
@@ -97,6 +99,19 @@ def load() -> ctypes.CDLL:
     lib.wkv_selftest_wait_timeout.argtypes = [_vp, ctypes.c_uint, _vp]
     lib.wkv56_selftest_abort.restype = i
     lib.wkv56_selftest_abort.argtypes = [ctypes.POINTER(WkvArgs), i, i, i, i, ctypes.c_uint, _vp]
+    fl, sz = ctypes.c_float, ctypes.c_size_t
+    lib.wkv_lnx_gate_forward.restype = i
+    lib.wkv_lnx_gate_forward.argtypes = [i, i, f, f, f, f, fl, f, _vp]
+    lib.wkv_lnx_gate_backward_workspace.restype = sz
+    lib.wkv_lnx_gate_backward_workspace.argtypes = [i, i]
+    lib.wkv_lnx_gate_backward.restype = i
+    lib.wkv_lnx_gate_backward.argtypes = [i, i, f, f, f, f, fl, f, f, f, f, f, _vp, sz, _vp]
+    lib.wkv_ddlerp_forward.restype = i
+    lib.wkv_ddlerp_forward.argtypes = [i, i, i, i, f, f, f, f, f, _vp]
+    lib.wkv_ddlerp_backward_workspace.restype = sz
+    lib.wkv_ddlerp_backward_workspace.argtypes = [i, i, i, i]
+    lib.wkv_ddlerp_backward.restype = i
+    lib.wkv_ddlerp_backward.argtypes = [i, i, i, i] + [f] * 10 + [_vp, sz, _vp]
     for v in ("wkv5", "wkv6"):
         for d in ("forward", "backward"):
             fn = getattr(lib, f"{v}_{d}")

@@ -14,7 +14,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libwkv_b200.so")
 STAMP = LIB + ".digest"
-SOURCES = ["wkv_api.cu", "wkv4.cu", "wkv4_par.cu", "wkv56_scalar.cu", "wkv56_chunked.cu", "wkv56_chunked_bwd.cu"]
+SOURCES = ["wkv_api.cu", "wkv4.cu", "wkv4_par.cu", "wkv56_scalar.cu", "wkv56_chunked.cu", "wkv56_chunked_bwd.cu",
+           "timemix_fused.cu"]
 HEADERS = ["wkv_common.cuh", os.path.join("..", "..", "include", "wkv_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC"]
