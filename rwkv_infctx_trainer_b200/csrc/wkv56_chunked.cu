@@ -114,7 +114,10 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
             const __grid_constant__ CUtensorMap map_rh, const FwdParams P) {
     extern __shared__ unsigned char smem_raw[];
-    FwdSmem &s = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the swizzled tiles want a 1024-byte aligned base.  The padding is added to the __shared__ array
+    // itself (not to an integer copy of its address), so the compiler still knows that everything
+    // behind `s` is shared memory and uses shared-memory loads and stores for the tiles.
+    FwdSmem &s = *reinterpret_cast<FwdSmem *>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // tells the compiler it is uniform across the warp
     // this CTA's group of chunks: global chunk index = j0 + local index, n of them

@@ -88,7 +88,10 @@ __global__ void __launch_bounds__(160)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant__ CUtensorMap map_gy,
               const __grid_constant__ CUtensorMap map_s, const DscanParams P) {
     extern __shared__ unsigned char smem_raw[];
-    DscanSmem &s = *reinterpret_cast<DscanSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the swizzled tiles want a 1024-byte aligned base.  The padding is added to the __shared__ array
+    // itself (not to an integer copy of its address), so the compiler still knows that everything
+    // behind `s` is shared memory and uses shared-memory loads and stores for the tiles.
+    DscanSmem &s = *reinterpret_cast<DscanSmem *>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x, bh = unit / P.G, grp = unit - bh * P.G, b = bh / P.H, h = bh % P.H;
     const int j0 = grp * P.L, n = min(P.L, P.nchunk - j0), N = P.nchunk;
