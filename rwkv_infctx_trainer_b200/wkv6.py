@@ -117,6 +117,30 @@ class _Wkv6StateKernel:
 wkv6state_cuda_kernel = _Wkv6StateKernel()
 
 
+class _Wkv6Kernel:
+    """Stand-in for the stateless extension module ``wkv6``
+    (RWKV-v6/src/module/cuda/wkv6_op.cpp:8-22): ``forward(B,T,C,H,r,k,v,w,u,y)`` and
+    ``backward(B,T,C,H,r,k,v,w,u,gy,gr,gk,gv,gw,gu)`` with ``w`` the fp32 ``ew = -exp(x)``; the
+    state starts from zero, is not returned, and takes no gradient."""
+
+    @staticmethod
+    def forward(B, T, C, H, r, k, v, w, u, y):
+        if w.dtype != torch.float32:
+            raise TypeError("w must be float32 (ew = -exp(x))")
+        y_new, _ = wkv56.forward("wkv6", r, k, v, w.contiguous(), u, None, w_kind=L.WKV_W_NEGEXP,
+                                 layout=L.WKV_STATE_VK)
+        y.copy_(y_new)
+
+    @staticmethod
+    def backward(B, T, C, H, r, k, v, w, u, gy, gr, gk, gv, gw, gu):
+        a, b, c, d, e, _ = wkv56.backward("wkv6", r, k, v, w.float().contiguous(), u, None, gy, None,
+                                          w_kind=L.WKV_W_NEGEXP, layout=L.WKV_STATE_VK, want_gstate=False)
+        gr.copy_(a); gk.copy_(b); gv.copy_(c); gw.copy_(d); gu.copy_(e.view_as(gu))
+
+
+wkv6_cuda_kernel = _Wkv6Kernel()
+
+
 class WKV6STATE_CUDA(torch.autograd.Function):
     """RWKV-v6/src/module/TimeMix.py:19-109: ``apply(B,T,C,H,r,k,v,w,u,s) -> y`` with
     ``s`` updated in place ([value,key] layout, any float dtype, indexed per batch row);

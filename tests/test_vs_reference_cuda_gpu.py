@@ -165,3 +165,27 @@ def test_v6_matches_reference_state_kernels_b1(path):
     TL.assert_close("gw", gw, TL.back(rgw), TOL)
     TL.assert_close("gu", gu, TL.back(rgu), TOL)
     TL.assert_close("gs", gs, TL.back(rgs), TOL)
+
+
+def test_v6_stateless_alias_module():
+    """the ``wkv6`` module of RWKV-v6/src/module/cuda/wkv6_op.cpp:8-22 (no state in, none out):
+    equals the stateful call from a zero state"""
+    W = _pkg()
+    from rwkv_infctx_trainer_b200 import wkv56
+    B, T, H = 2, 200, 2
+    C = H * 64
+    q = TL.case56("v6", B, T, H, BF, seed=65, state=False, gstate=False)
+    r, k, v, u, gy = (TL.to_dev(q[n], BF) for n in ("r", "k", "v", "u", "gy"))
+    ew = (-torch.exp(TL.to_dev(q["x"], BF).float())).contiguous()
+    y = torch.empty_like(r)
+    W.wkv6_cuda_kernel.forward(B, T, C, H, r, k, v, ew, u, y)
+    mk = lambda *s: torch.empty(s, device="cuda", dtype=BF)
+    gr, gk, gv, gw, gu = mk(B, T, C), mk(B, T, C), mk(B, T, C), mk(B, T, C), mk(B, C)
+    W.wkv6_cuda_kernel.backward(B, T, C, H, r, k, v, ew, u, gy, gr, gk, gv, gw, gu)
+    want = TL.oracle56("v6", q)
+    TL.assert_close("y", y, want["y"], TOL)
+    TL.assert_close("gr", gr, want["gr"], TOL)
+    TL.assert_close("gk", gk, want["gk"], TOL)
+    TL.assert_close("gv", gv, want["gv"], TOL)
+    TL.assert_close("gw", gw, want["gw"], TOL)
+    TL.assert_close("gu", gu, want["gu"], TOL)
