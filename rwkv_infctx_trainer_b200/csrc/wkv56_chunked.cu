@@ -79,6 +79,7 @@ struct FwdParams {
     __nv_bfloat16 *ckpt;      // [B,H,nchunk+1,64,64] chunk-start states, or NULL
     float *dchunk;            // [B*H,nchunk,64] decay of each whole chunk, or NULL; with it the
                               // kernel also stores r e^{cp} of every chunk through map_rh
+    unsigned char *mildflag;  // with dchunk: [B*H*nchunk], 1 = the chunk is mild
     int *status;
     uint32_t wait_limit;      // polls before a wait gives up
     int skip_load;            // -1; a local chunk index leaves that chunk's TMA load out (wait-timeout test)
@@ -177,6 +178,10 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
                                d_kh = make_desc(smem_u32(&s.khat[st]));
                 if (!mbar_wait_or_abort(&s.ops_bar[c & 1], (uint32_t)((c >> 1) & 1), &s.abort_flag, P.wait_limit)) { fail = 1; break; }
                 tc_fence_after();
+                // the per-chunk backward kernel comes in two builds: tell it which one this chunk needs
+                // (written from here: this lane has time, the compute warps do not)
+                if (P.dchunk)
+                    P.mildflag[bh * P.nchunk + j0 + c] = *reinterpret_cast<volatile int *>(&s.mild_flag[c & 1]) != 0;
                 if (full) {
                     // scores: A1 = Rt Kt^T (column halves), A2 = X X[0:32]^T.  In a mild chunk Rt and Kt are
                     // scaled around one point, A1's rows 32..63 of columns 0..31 ARE the cross-block scores:
@@ -801,6 +806,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
     p.u = (const __nv_bfloat16 *)a->u;
     p.wvec = per_token_w ? nullptr : (const float *)a->w;
     p.status = (int *)a->workspace;
+    p.mildflag = nullptr;
     p.wait_limit = tst.wait_limit;
     p.skip_load = tst.kernel == 0 ? tst.skip_load : -1;
     const size_t smem = sizeof(FwdSmem) + 1024;
@@ -842,6 +848,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
         char *ck = (char *)state_ckpt;
         p.ckpt = (__nv_bfloat16 *)(ck + CL.sck);
         p.dchunk = (float *)(ck + CL.dchunk);
+        p.mildflag = (unsigned char *)(ck + CL.mild);
         if (!make_btc_map(&mrh, ck + CL.rhat, B, T, C)) return WKV_ERR_LAUNCH;
     }
     kerns[pt][mode]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);

@@ -211,8 +211,10 @@ __device__ __forceinline__ void st_tile4(Tile &t, int row, int chunk, int half, 
 //   sck     bf16 [B*H, nchunk+1, 64, 64]  state at the start of every chunk (key rows, value columns)
 //   rhat    bf16 [B, T, C]                r_t * (decay accumulated from the chunk start to before t)
 //   dchunk  fp32 [B*H, nchunk, 64]        decay of each whole chunk per key channel
+//   mild    u8   [B*H * nchunk]           1 = the chunk is mild (see decay_scan8), 0 = steep: which build of
+//                                         the per-chunk backward kernel the chunk needs
 struct CkptLayout {
-    size_t sck, rhat, dchunk, total;
+    size_t sck, rhat, dchunk, mild, total;
 };
 inline CkptLayout ckpt_layout(int B, int T, int H) {
     const size_t n = (size_t)(T + CH - 1) / CH, bh = (size_t)B * H;
@@ -221,7 +223,8 @@ inline CkptLayout ckpt_layout(int B, int T, int H) {
     L.sck = 0;
     L.rhat = al(bh * (n + 1) * 64 * 64 * 2);
     L.dchunk = L.rhat + al((size_t)B * T * H * 64 * 2);
-    L.total = L.dchunk + al(bh * n * 64 * 4);
+    L.mild = L.dchunk + al(bh * n * 64 * 4);
+    L.total = L.mild + al(bh * n);
     return L;
 }
 

@@ -266,6 +266,7 @@ struct BwdSmem {
     uint64_t bar_grad;         // phase 2 except gv
     uint64_t bar_gv;           // gv
     uint32_t tmem_base;
+    int not_mine;              // mild-only build: the chunk turned out to be a steep one
 };
 
 static_assert(sizeof(BwdSmem) <= 115712, "two CTAs per SM need <= 113 KiB each");
@@ -281,6 +282,7 @@ struct BwdParams {
     int *status;
     uint32_t wait_limit;
     int skip_load;        // -1; a chunk index whose CTAs leave their TMA loads out (wait-timeout test)
+    const unsigned char *mildflag;   // [B*H*nchunk] from the forward kernel: 1 = the chunk is mild
 };
 
 // tensor-memory columns; "lo" = lanes 0..15 of each 32-lane quarter, "hi" = lanes 16..31.
@@ -333,21 +335,24 @@ __device__ __forceinline__ float halving_sum8(const float *v, int l16) {
 // reaches token 31.  (Walking group 1 backward from the chunk-end constant would need no offset,
 // but that constant comes from a separately rounded bf16 state and the small residuals of
 // strongly decaying channels do not survive the mismatch.)
-template <bool PER_TOKEN>
-__global__ void __launch_bounds__(256, 2)
-k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
-            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
-            const __grid_constant__ CUtensorMap map_gy, const __grid_constant__ CUtensorMap map_s,
-            const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_gr,
-            const __grid_constant__ CUtensorMap map_gk, const __grid_constant__ CUtensorMap map_gv,
-            const __grid_constant__ CUtensorMap map_gw, const BwdParams P) {
+//
+// The body is compiled twice.  MILD_ONLY = true: the chunk is known to be mild (the forward kernel
+// said so), every cross-block code path is left out -- a smaller, leaner kernel (96 instead of 125
+// registers) that serves every chunk of ordinary data.  MILD_ONLY = false: the general body, run
+// only for the chunks the forward kernel listed as steep.
+template <bool PER_TOKEN, bool MILD_ONLY>
+__device__ __forceinline__ void
+bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap &map_v, const CUtensorMap &map_w,
+          const CUtensorMap &map_gy, const CUtensorMap &map_s, const CUtensorMap &map_d, const CUtensorMap &map_gr,
+          const CUtensorMap &map_gk, const CUtensorMap &map_gv, const CUtensorMap &map_gw, const BwdParams &P,
+          const int chunk_id) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     BwdSmem &s = *reinterpret_cast<BwdSmem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // tells the compiler it is uniform across the warp
     const int wg = warp >> 2, w4 = warp & 3;
     const int n = P.nchunk;
-    const int bh = blockIdx.x / n, j = blockIdx.x % n, b = bh / P.H, h = bh % P.H;
+    const int bh = chunk_id / n, j = chunk_id % n, b = bh / P.H, h = bh % P.H;
     const bool lo = (lane & 16) == 0;
     const int row = w4 * 16 + (lane & 15);   // accumulator row owned (token in phase 1, channel in phase 2)
     const uint32_t lane_base = (uint32_t)(w4 * 32);
@@ -374,9 +379,9 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             tma_load_3d(&s.in[T_D], &map_d, &s.load_bar, 0, 0, bh * (n + 1) + j + 1);
         }
     }
-    if (tid == 32) {
+    if (MILD_ONLY && tid == 32) {
         // the CTA that will take this one's place on the SM finds its tiles in L2
-        const int nb = blockIdx.x + P.prefetch_dist;
+        const int nb = chunk_id + P.prefetch_dist;
         if (nb < (int)gridDim.x) {
             const int bh2 = nb / n, j2 = nb % n, b2 = bh2 / P.H, h2 = bh2 % P.H;
             tma_prefetch_l2_3d(&map_r, h2 * 64, j2 * CH, b2);
@@ -388,12 +393,21 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             tma_prefetch_l2_3d(&map_d, 0, 0, bh2 * (n + 1) + j2 + 1);
         }
     }
+    // (the flag is read while the loads are in flight: asking first would put a DRAM round trip in front of them)
+    if (MILD_ONLY && tid == 64) s.not_mine = P.mildflag[chunk_id] == 0;
     if (warp == 0) { tmem_alloc(&s.tmem_base, BWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = s.tmem_base;
     const uint32_t tm_lo = tm, tm_hi = tm + (16u << 16);
+    if (MILD_ONLY && s.not_mine) {
+        // a steep chunk: the other kernel computes it.  Let this CTA's loads land, give the tensor memory back.
+        if (tid == 0 && chunk_id % P.nchunk != P.skip_load) mbar_wait(&s.load_bar, 0, LIM);
+        __syncthreads();
+        if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
+        return;
+    }
 
     // operand-pass coordinates (see decay_scan8): 4 tokens x 4 channels per thread, a half-warp per tile row
     const int pblk = warp >> 2, pcc = (lane & 15) >> 1, phf = lane & 1, ptok0 = 8 * warp + 4 * (lane >> 4);
@@ -580,6 +594,7 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             }
         }
     }
+    if (MILD_ONLY) mild = true;      // (what the scan just found as well; as a constant it removes the steep code)
     fence_async_smem();
     tc_fence_before();
     const int abort1 = __syncthreads_or(fail);
@@ -964,6 +979,43 @@ k_chunk_bwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
     if (warp == 0) tmem_dealloc(tm, BWD_TMEM_COLS);
 }
 
+#define BWD_MAPS                                                                                              \
+    const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,                    \
+        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,                \
+        const __grid_constant__ CUtensorMap map_gy, const __grid_constant__ CUtensorMap map_s,               \
+        const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_gr,               \
+        const __grid_constant__ CUtensorMap map_gk, const __grid_constant__ CUtensorMap map_gv,              \
+        const __grid_constant__ CUtensorMap map_gw
+#define BWD_MAP_ARGS map_r, map_k, map_v, map_w, map_gy, map_s, map_d, map_gr, map_gk, map_gv, map_gw
+
+// one CTA per (batch, head, chunk); CTAs of steep chunks leave early (the other kernel has them)
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(256, 2) k_chunk_bwd(BWD_MAPS, const BwdParams P) {
+    bwd_chunk<PER_TOKEN, true>(BWD_MAP_ARGS, P, (int)blockIdx.x);
+}
+
+// A fixed, small grid that looks through the mild flags for steep chunks (usually there is none and
+// every CTA leaves after one load) and runs the general body on them.  CTA c looks at chunks
+// c, c + grid, c + 2 grid, ...: 256 of them per round, one flag per thread.
+// One CTA per SM: the general body inside a loop wants more than the 128 registers two CTAs leave.
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(256, 1) k_chunk_bwd_steep(BWD_MAPS, const BwdParams P, const int total) {
+    __shared__ unsigned char is_steep[256];
+    for (int base = blockIdx.x; base < total; base += 256 * gridDim.x) {
+        const int mine = base + threadIdx.x * gridDim.x;
+        const bool steep = mine < total && P.mildflag[mine] == 0;
+        is_steep[threadIdx.x] = steep ? 1 : 0;
+        if (!__syncthreads_or(steep)) continue;
+        for (int t = 0; t < 256; t++) {
+            if (is_steep[t]) {      // (the same for every thread of the CTA)
+                bwd_chunk<PER_TOKEN, false>(BWD_MAP_ARGS, P, base + t * gridDim.x);
+                __syncthreads();    // the barriers and the tensor memory of this chunk are done with
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // sum the per-chunk partials: out[bh*64 + k] = sum_j part[(bh*n + j)*64 + k]
 __global__ void k_reduce_partials(const float *__restrict__ part, float *__restrict__ out, int n, int total) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1076,11 +1128,21 @@ int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &
         p.e0 = e0; p.gu_part = gu_part; p.gw_part = gw_part; p.status = (int *)ws;
         p.wait_limit = tst.wait_limit;
         p.skip_load = tst.kernel == 2 ? tst.skip_load : -1;
+        p.mildflag = (const unsigned char *)(fwd_ck + CL.mild);
         const size_t smem = sizeof(BwdSmem);
         auto kern = per_token_w ? k_chunk_bwd<true> : k_chunk_bwd<false>;
-        static unsigned char attr_done[2][64];
-        if (!set_max_smem_once(kern, (int)smem, attr_done[per_token_w ? 1 : 0])) return WKV_ERR_LAUNCH;
+        auto kern_steep = per_token_w ? k_chunk_bwd_steep<true> : k_chunk_bwd_steep<false>;
+        static unsigned char attr_done[2][2][64];
+        const int pt = per_token_w ? 1 : 0;
+        if (!set_max_smem_once(kern, (int)smem, attr_done[0][pt]) ||
+            !set_max_smem_once(kern_steep, (int)smem, attr_done[1][pt]))
+            return WKV_ERR_LAUNCH;
+        // every chunk the forward kernel found mild (all of them, on ordinary data) ...
         kern<<<BH * n, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
+        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        // ... and the ones it flagged as steep
+        const int steep_grid = BH * n < device_sm_count() ? BH * n : device_sm_count();
+        kern_steep<<<steep_grid, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p, BH * n);
         if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
     }
     // 4. fold the per-chunk partial sums

@@ -70,14 +70,15 @@ def test_struct_matches_header_field_order():
 
 
 def test_handover_buffer_size_without_gpu():
-    """wkv56_state_ckpt_bytes: chunk-start states + scaled r + chunk decays, each 256-byte
-    aligned; 0 when the call would not run on the chunked kernels"""
+    """wkv56_state_ckpt_bytes: chunk-start states + scaled r + chunk decays + the per-chunk mild
+    flags, each 256-byte aligned; 0 when the call would not run on the chunked kernels"""
     lib = L.load()
     a = L.WkvArgs()
     a.B, a.T, a.H, a.N, a.dtype, a.w_kind = 2, 200, 3, 64, L.WKV_BF16, L.WKV_W_RAW
     al = lambda x: (x + 255) // 256 * 256
     n = (200 + 63) // 64
-    want = al(2 * 3 * (n + 1) * 64 * 64 * 2) + al(2 * 200 * 3 * 64 * 2) + al(2 * 3 * n * 64 * 4)
+    want = (al(2 * 3 * (n + 1) * 64 * 64 * 2) + al(2 * 200 * 3 * 64 * 2) + al(2 * 3 * n * 64 * 4)
+            + al(2 * 3 * n))
     assert lib.wkv56_state_ckpt_bytes(ctypes.byref(a), 1) == want
     a.dtype = L.WKV_F32          # fp32 I/O runs on the token-serial kernels: nothing to hand over
     assert lib.wkv56_state_ckpt_bytes(ctypes.byref(a), 1) == 0

@@ -32,7 +32,11 @@ def test_restart_from_saved_states_is_bit_identical(variant, B, T, H, groups):
     assert saved.restarts == 1
     torch.cuda.synchronize()
     assert torch.equal(y0, y1) and torch.equal(s0, s1)
-    assert torch.equal(c0, c1)          # the hand-over to backward as well
+    # the hand-over to backward as well: states, scaled r, chunk decays, mild flags (then padding)
+    al = lambda x: (x + 255) // 256 * 256
+    n = (T + 63) // 64
+    used = al(B * H * (n + 1) * 8192) + al(B * T * H * 128) + al(B * H * n * 256) + B * H * n
+    assert torch.equal(c0[:used], c1[:used])
     want = CG.floored_oracle(variant, q)
     TL.assert_close("y", y1, want["y"], 2e-2)
     TL.assert_close("state_out", s1, want["state_out"], 2e-2)
