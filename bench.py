@@ -579,8 +579,10 @@ def run_side_config(args):
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(0)
     hbm, which = peaks()
+    small = 2 if args.small else 8          # --small: two batch rows (profiling aid)
     if args.config == 1:
-        B, T, seg, C, dt = 8, 4096, 2048, 2048, torch.float32
+        B, T, seg, C = small, 4096, 2048, 2048
+        dt = {"fp32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
         k, v, gy = (torch.randn((B, T, C), generator=g).to(dt).to(device) for _ in range(3))
         w = (-torch.exp(torch.rand(C, generator=g) * 6 - 5)).to(device)
         u = (torch.rand(C, generator=g) * 2 - 1).to(dt).to(device)
@@ -601,22 +603,26 @@ def run_side_config(args):
         states = [torch.zeros((B, C, 3), device=device) for _ in range(len(segs) + 1)]
         states[0][..., 2] = -1e38
         gst = [torch.empty((B, C, 3), device=device) for _ in range(len(segs) + 1)]
+        nck = lib.wkv4_state_ckpt_bytes(B, seg, C)      # piece-start states handed from forward to backward
+        cks = [torch.empty(max(nck, 16), dtype=torch.uint8, device=device) for _ in segs]
 
         def step():
             for i in range(len(segs)):
-                L.check(lib.wkv4_forward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
-                                         vv[i].data_ptr(), states[i].data_ptr(), ys[i].data_ptr(),
-                                         states[i + 1].data_ptr(), wsf.data_ptr(), nwf, st), "wkv4_forward")
+                L.check(lib.wkv4_forward_ckpt(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
+                                              vv[i].data_ptr(), states[i].data_ptr(), ys[i].data_ptr(),
+                                              states[i + 1].data_ptr(), wsf.data_ptr(), nwf, cks[i].data_ptr(), nck,
+                                              st), "wkv4_forward")
             for i in reversed(range(len(segs))):
                 gin = None if i == len(segs) - 1 else gst[i + 1].data_ptr()
-                L.check(lib.wkv4_backward(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
-                                          vv[i].data_ptr(), states[i].data_ptr(), gg[i].data_ptr(), gin,
-                                          gw.data_ptr(), gu.data_ptr(), gk[i].data_ptr(), gv[i].data_ptr(),
-                                          gst[i].data_ptr(), ws.data_ptr(), nws, st), "wkv4_backward")
-        bytes_step = 8 * 4 * B * T * C
-        name = "rwkv4_wkv_fwd_bwd_fp32"
+                L.check(lib.wkv4_backward_ckpt(B, seg, C, code, w.data_ptr(), u.data_ptr(), kk[i].data_ptr(),
+                                               vv[i].data_ptr(), states[i].data_ptr(), gg[i].data_ptr(), gin,
+                                               gw.data_ptr(), gu.data_ptr(), gk[i].data_ptr(), gv[i].data_ptr(),
+                                               gst[i].data_ptr(), ws.data_ptr(), nws, cks[i].data_ptr(), nck, st),
+                        "wkv4_backward")
+        bytes_step = 8 * k.element_size() * B * T * C
+        name = "rwkv4_wkv_fwd_bwd_" + args.dtype
     else:
-        B, T, seg, C, H = 8, 4096, 2048, 2048, 32
+        B, T, seg, C, H = small, 4096, 2048, 2048, 32
         dt = torch.bfloat16
         r, k, v, gy = (torch.randn((B, T, C), generator=g).to(dt).to(device) for _ in range(4))
         w = (torch.rand((H, 64), generator=g) * 5 - 6).to(device)
@@ -900,6 +906,9 @@ def main():
     ap.add_argument("--medium", action="store_true",
                     help="profiling aid: the benchmark's batch and heads but a single 4096-token segment "
                          "(under 2 GB on the device) -- the grid sizes of the benchmark's launches")
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"],
+                    help="--config 1 only: I/O dtype of the v4 workload (the benchmark names fp32; the "
+                         "project's own v4 kernel is bf16 only)")
     ap.add_argument("--heads", type=int, default=0,
                     help="profiling aid: this many heads instead of 64 (8 = what one of 8 GPUs gets)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: no end-to-end leg")

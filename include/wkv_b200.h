@@ -105,6 +105,21 @@ int wkv4_backward(int B, int T, int C, int dtype, const float *w, const void *u,
                   void *gk, void *gv, float *gstate_in, void *workspace,
                   size_t workspace_bytes, void *stream);
 
+/* Optional hand-over from forward to backward of the same segment (no counterpart in the project,
+ * whose backward recomputes everything): wkv4_state_ckpt_bytes() bytes that receive the state at
+ * the start of every 64-token piece.  Backward given the buffer skips rebuilding those states (one
+ * pass over k and v less).  0 bytes / NULL for segments under 128 tokens; NULL is always allowed and
+ * makes the _ckpt entry points identical to the plain ones. */
+size_t wkv4_state_ckpt_bytes(int B, int T, int C);
+int wkv4_forward_ckpt(int B, int T, int C, int dtype, const float *w, const void *u, const void *k,
+                      const void *v, const float *state_in, void *y, float *state_out, void *workspace,
+                      size_t workspace_bytes, void *state_ckpt, size_t state_ckpt_bytes, void *stream);
+int wkv4_backward_ckpt(int B, int T, int C, int dtype, const float *w, const void *u, const void *k,
+                       const void *v, const float *state_in, const void *gy, const float *gstate_out,
+                       float *gw, float *gu, void *gk, void *gv, float *gstate_in, void *workspace,
+                       size_t workspace_bytes, const void *state_ckpt, size_t state_ckpt_bytes,
+                       void *stream);
+
 /* wkv4_backward for callers that cannot supply a workspace.  (No counterpart in
  * RWKV-infctx-trainer: its kernels keep their scratch in per-thread arrays.)
  *

@@ -43,6 +43,7 @@ EXPORTS = [
     "wkv_error_string", "wkv_version", "wkv56_uses_chunked", "wkv56_state_ckpt_bytes",
     "wkv4_forward_workspace", "wkv4_forward", "wkv4_backward_workspace", "wkv4_backward",
     "wkv4_backward_static_limit", "wkv4_backward_static",
+    "wkv4_state_ckpt_bytes", "wkv4_forward_ckpt", "wkv4_backward_ckpt",
     "wkv5_forward_workspace", "wkv5_backward_workspace", "wkv5_forward", "wkv5_backward",
     "wkv6_forward_workspace", "wkv6_backward_workspace", "wkv6_forward", "wkv6_backward",
     "wkv_selftest_wait_timeout", "wkv56_selftest_abort", "wkv56_group_states_bytes",
@@ -85,6 +86,12 @@ def load() -> ctypes.CDLL:
     lib.wkv4_backward_workspace.argtypes = [i, i, i]
     lib.wkv4_backward.restype = i
     lib.wkv4_backward.argtypes = [i, i, i, i] + [f] * 12 + [_vp, ctypes.c_size_t, _vp]
+    lib.wkv4_state_ckpt_bytes.restype = ctypes.c_size_t
+    lib.wkv4_state_ckpt_bytes.argtypes = [i, i, i]
+    lib.wkv4_forward_ckpt.restype = i
+    lib.wkv4_forward_ckpt.argtypes = [i, i, i, i, f, f, f, f, f, f, f, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _vp]
+    lib.wkv4_backward_ckpt.restype = i
+    lib.wkv4_backward_ckpt.argtypes = [i, i, i, i] + [f] * 12 + [_vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _vp]
     lib.wkv4_backward_static_limit.restype = ctypes.c_size_t
     lib.wkv4_backward_static_limit.argtypes = []
     lib.wkv4_backward_static.restype = i

@@ -167,11 +167,12 @@ size_t serial_backward_workspace(int B, int T, int C) {
 // time-parallel kernels, wkv4_par.cu
 size_t v4_par_forward_workspace(int B, int T, int C);
 size_t v4_par_backward_workspace(int B, int T, int C);
+size_t v4_par_ckpt_bytes(int B, int T, int C);
 int v4_par_forward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
-                   const float *si, void *y, float *so, float *ws, cudaStream_t s);
+                   const float *si, void *y, float *so, float *ws, float *ckpt, cudaStream_t s);
 int v4_par_backward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
                     const float *si, const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv,
-                    float *gsi, float *ws, cudaStream_t s);
+                    float *gsi, float *ws, const float *ckpt, cudaStream_t s);
 }  // namespace wkv
 
 using namespace wkv;
@@ -181,9 +182,22 @@ extern "C" size_t wkv4_forward_workspace(int B, int T, int C) {
     return v4_par_forward_workspace(B, T, C);
 }
 
+extern "C" size_t wkv4_state_ckpt_bytes(int B, int T, int C) {
+    if (B <= 0 || C <= 0 || T < PAR_MIN_T) return 0;
+    return v4_par_ckpt_bytes(B, T, C);
+}
+
 extern "C" int wkv4_forward(int B, int T, int C, int dtype, const float *w, const void *u,
                             const void *k, const void *v, const float *state_in, void *y,
                             float *state_out, void *workspace, size_t workspace_bytes, void *stream) {
+    return wkv4_forward_ckpt(B, T, C, dtype, w, u, k, v, state_in, y, state_out, workspace, workspace_bytes,
+                             nullptr, 0, stream);
+}
+
+extern "C" int wkv4_forward_ckpt(int B, int T, int C, int dtype, const float *w, const void *u,
+                                 const void *k, const void *v, const float *state_in, void *y,
+                                 float *state_out, void *workspace, size_t workspace_bytes,
+                                 void *state_ckpt, size_t state_ckpt_bytes, void *stream) {
     if (B < 0 || T < 0 || C < 0) return WKV_ERR_SHAPE;
     if (B == 0 || C == 0) return WKV_OK;
     if (!w || !u) return WKV_ERR_NULL;
@@ -192,7 +206,9 @@ extern "C" int wkv4_forward(int B, int T, int C, int dtype, const float *w, cons
     cudaStream_t s = (cudaStream_t)stream;
     if (T >= PAR_MIN_T) {
         if (!workspace || workspace_bytes < wkv4_forward_workspace(B, T, C)) return WKV_ERR_WORKSPACE;
-        return v4_par_forward(B, T, C, dtype, w, u, k, v, state_in, y, state_out, (float *)workspace, s);
+        if (state_ckpt && state_ckpt_bytes < wkv4_state_ckpt_bytes(B, T, C)) return WKV_ERR_WORKSPACE;
+        return v4_par_forward(B, T, C, dtype, w, u, k, v, state_in, y, state_out, (float *)workspace,
+                              (float *)state_ckpt, s);
     }
     switch (dtype) {
         case WKV_F32: return fwd<float>(B, T, C, w, u, k, v, state_in, y, state_out, s);
@@ -214,6 +230,15 @@ extern "C" int wkv4_backward(int B, int T, int C, int dtype, const float *w, con
                              const float *gstate_out, float *gw, float *gu, void *gk, void *gv,
                              float *gstate_in, void *workspace, size_t workspace_bytes,
                              void *stream) {
+    return wkv4_backward_ckpt(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in,
+                              workspace, workspace_bytes, nullptr, 0, stream);
+}
+
+extern "C" int wkv4_backward_ckpt(int B, int T, int C, int dtype, const float *w, const void *u,
+                                  const void *k, const void *v, const float *state_in, const void *gy,
+                                  const float *gstate_out, float *gw, float *gu, void *gk, void *gv,
+                                  float *gstate_in, void *workspace, size_t workspace_bytes,
+                                  const void *state_ckpt, size_t state_ckpt_bytes, void *stream) {
     if (B < 0 || T < 0 || C < 0) return WKV_ERR_SHAPE;
     if (B == 0 || C == 0) return WKV_OK;
     if (!w || !u || !gw || !gu) return WKV_ERR_NULL;
@@ -223,8 +248,11 @@ extern "C" int wkv4_backward(int B, int T, int C, int dtype, const float *w, con
     if (dtype != WKV_F32 && dtype != WKV_BF16 && dtype != WKV_F16) return WKV_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
     float *ws = (float *)workspace;
-    if (T >= PAR_MIN_T)
-        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
+    if (T >= PAR_MIN_T) {
+        if (state_ckpt && state_ckpt_bytes < wkv4_state_ckpt_bytes(B, T, C)) return WKV_ERR_WORKSPACE;
+        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws,
+                               (const float *)state_ckpt, s);
+    }
     switch (dtype) {
         case WKV_F32:
             return bwd<float>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
@@ -300,7 +328,8 @@ extern "C" int wkv4_backward_static(int B, int T, int C, int dtype, const float 
     // Nothing in the scratch has to start at zero: both kernel families write every word of it
     // that they later read (tile-start states; piece summaries, scanned states and partial sums).
     if (T >= PAR_MIN_T)   // the same time-parallel kernels wkv4_backward runs, on the built-in array
-        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);
+        return v4_par_backward(B, T, C, dtype, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws,
+                               nullptr, s);
     switch (dtype) {
         case WKV_F32:
             return bwd<float>(B, T, C, w, u, k, v, state_in, gy, gstate_out, gw, gu, gk, gv, gstate_in, ws, s);

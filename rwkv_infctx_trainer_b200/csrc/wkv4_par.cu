@@ -292,11 +292,12 @@ k_seg_reduce(Dims d, const float *__restrict__ gw_part, const float *__restrict_
 
 inline unsigned blocks(long long n) { return (unsigned)((n + THREADS - 1) / THREADS); }
 
+// `ckpt` (or NULL): where the piece-start states go instead of the workspace, for the backward call to reuse
 template <typename F>
 int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v, const float *si, void *y,
-            float *so, float *ws, cudaStream_t s) {
+            float *so, float *ws, float *ckpt, cudaStream_t s) {
     const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C;
-    float *loc = ws, *st = ws + n3;
+    float *loc = ws, *st = ckpt ? ckpt : ws + n3;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     k_seg_summary<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
     k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
@@ -307,13 +308,17 @@ int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v,
 template <typename F>
 int par_bwd(Dims d, const float *w, const void *u, const void *k, const void *v, const float *si,
             const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv, float *gsi, float *ws,
-            cudaStream_t s) {
+            const float *ckpt, cudaStream_t s) {
     const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C, n1 = (size_t)d.B * d.nseg * d.C;
-    float *loc = ws, *st = loc + n3, *rloc = st + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
+    float *loc = ws, *stw = loc + n3, *rloc = stw + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     const unsigned nb = blocks(nthr), nc = blocks((long long)d.B * d.C);
-    k_seg_summary<F><<<nb, THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
-    k_seg_scan<<<nc, THREADS, 0, s>>>(d, w, si, loc, st, nullptr);
+    const float *st = ckpt;
+    if (!ckpt) {      // the forward call did not hand the piece-start states over: rebuild them
+        k_seg_summary<F><<<nb, THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
+        k_seg_scan<<<nc, THREADS, 0, s>>>(d, w, si, loc, stw, nullptr);
+        st = stw;
+    }
     k_seg_backward<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy, st,
                                                     nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
     k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
@@ -334,25 +339,29 @@ size_t v4_par_backward_workspace(int B, int T, int C) {
     return (4 * 3 + 2) * (size_t)B * nseg * C * sizeof(float);
 }
 
+size_t v4_par_ckpt_bytes(int B, int T, int C) {
+    return (size_t)B * ((T + SEG - 1) / SEG) * 3 * C * sizeof(float);
+}
+
 int v4_par_forward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
-                   const float *si, void *y, float *so, float *ws, cudaStream_t s) {
+                   const float *si, void *y, float *so, float *ws, float *ckpt, cudaStream_t s) {
     const Dims d{B, T, C, (T + SEG - 1) / SEG};
     switch (dtype) {
-        case WKV_F32: return par_fwd<float>(d, w, u, k, v, si, y, so, ws, s);
-        case WKV_BF16: return par_fwd<__nv_bfloat16>(d, w, u, k, v, si, y, so, ws, s);
-        case WKV_F16: return par_fwd<__half>(d, w, u, k, v, si, y, so, ws, s);
+        case WKV_F32: return par_fwd<float>(d, w, u, k, v, si, y, so, ws, ckpt, s);
+        case WKV_BF16: return par_fwd<__nv_bfloat16>(d, w, u, k, v, si, y, so, ws, ckpt, s);
+        case WKV_F16: return par_fwd<__half>(d, w, u, k, v, si, y, so, ws, ckpt, s);
     }
     return WKV_ERR_DTYPE;
 }
 
 int v4_par_backward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
                     const float *si, const void *gy, const float *gso, float *gw, float *gu, void *gk, void *gv,
-                    float *gsi, float *ws, cudaStream_t s) {
+                    float *gsi, float *ws, const float *ckpt, cudaStream_t s) {
     const Dims d{B, T, C, (T + SEG - 1) / SEG};
     switch (dtype) {
-        case WKV_F32: return par_bwd<float>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
-        case WKV_BF16: return par_bwd<__nv_bfloat16>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
-        case WKV_F16: return par_bwd<__half>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, s);
+        case WKV_F32: return par_bwd<float>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, ckpt, s);
+        case WKV_BF16: return par_bwd<__nv_bfloat16>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, ckpt, s);
+        case WKV_F16: return par_bwd<__half>(d, w, u, k, v, si, gy, gso, gw, gu, gk, gv, gsi, ws, ckpt, s);
     }
     return WKV_ERR_DTYPE;
 }

@@ -46,16 +46,23 @@ class WKVFunction(torch.autograd.Function):
         with torch.cuda.device(dev):
             nbytes = lib.wkv4_forward_workspace(B, T, C)
             ws = _ws(nbytes, dev)
-            L.check(lib.wkv4_forward(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
-                                     L.ptr(v), L.ptr(last_state), L.ptr(y), L.ptr(new_state),
-                                     L.ptr(ws), nbytes, L.stream_handle(dev)), "wkv4_forward")
-        ctx.save_for_backward(w, u, k, v, last_state)
+            # the states at the start of every 64-token piece go to backward (when there will be one)
+            nck = lib.wkv4_state_ckpt_bytes(B, T, C) if any(ctx.needs_input_grad) else 0
+            ckpt = _ws(nck, dev)
+            L.check(lib.wkv4_forward_ckpt(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
+                                          L.ptr(v), L.ptr(last_state), L.ptr(y), L.ptr(new_state),
+                                          L.ptr(ws), nbytes, L.ptr(ckpt), nck, L.stream_handle(dev)),
+                    "wkv4_forward")
+        ctx.has_ckpt = ckpt is not None
+        ctx.save_for_backward(*((w, u, k, v, last_state) + ((ckpt,) if ckpt is not None else ())))
         ctx.u_dtype = raw_u.dtype
         return y, new_state
 
     @staticmethod
     def backward(ctx, gy, gnew_state):
-        w, u, k, v, last_state = ctx.saved_tensors
+        st = ctx.saved_tensors
+        w, u, k, v, last_state = st[:5]
+        ckpt = st[5] if ctx.has_ckpt else None
         B, T, C = k.shape
         dev = k.device
         dt = k.dtype
@@ -70,10 +77,11 @@ class WKVFunction(torch.autograd.Function):
         with torch.cuda.device(dev):
             nbytes = lib.wkv4_backward_workspace(B, T, C)
             ws = _ws(nbytes, dev)
-            L.check(lib.wkv4_backward(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
-                                      L.ptr(v), L.ptr(last_state), L.ptr(gy), L.ptr(gns),
-                                      L.ptr(gw), L.ptr(gu), L.ptr(gk), L.ptr(gv), L.ptr(glast),
-                                      L.ptr(ws), nbytes, L.stream_handle(dev)), "wkv4_backward")
+            L.check(lib.wkv4_backward_ckpt(B, T, C, L.DTYPE_CODE[dt], L.ptr(w), L.ptr(u), L.ptr(k),
+                                           L.ptr(v), L.ptr(last_state), L.ptr(gy), L.ptr(gns),
+                                           L.ptr(gw), L.ptr(gu), L.ptr(gk), L.ptr(gv), L.ptr(glast),
+                                           L.ptr(ws), nbytes, L.ptr(ckpt), 0 if ckpt is None else ckpt.numel(),
+                                           L.stream_handle(dev)), "wkv4_backward")
         return gw.sum(0), gu.sum(0).to(ctx.u_dtype), gk, gv, glast
 
 

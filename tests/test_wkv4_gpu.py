@@ -145,3 +145,34 @@ def test_v4_op_called_from_torchscript():
     TL.assert_close("gv", v.grad, want["gv"], tol)
     TL.assert_close("gw", td.grad, want["gw"], tol)
     TL.assert_close("gu", u.grad, want["gu"], tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_v4_handover_equals_recompute(dtype):
+    """backward given the piece-start states that forward left == backward rebuilding them, bit for bit"""
+    import rwkv_infctx_trainer_b200._lib as L
+    lib = L.load()
+    B, T, C = 2, 300, 128
+    q = v4_inputs(B, T, C, dtype, seed=13)
+    d = {n: TL.to_dev(q[n], dtype) for n in ("u", "k", "v", "gy")}
+    w = TL.to_dev(q["w"], torch.float32)
+    s0 = torch.zeros((B, C, 3), device="cuda"); s0[..., 2] = -1e38
+    st, code = torch.cuda.current_stream().cuda_stream, L.DTYPE_CODE[dtype]
+    nf, nb, nck = lib.wkv4_forward_workspace(B, T, C), lib.wkv4_backward_workspace(B, T, C), lib.wkv4_state_ckpt_bytes(B, T, C)
+    assert nck > 0 and lib.wkv4_state_ckpt_bytes(B, 100, C) == 0
+    wsf, wsb = torch.empty(nf, dtype=torch.uint8, device="cuda"), torch.empty(nb, dtype=torch.uint8, device="cuda")
+    ck = torch.empty(nck, dtype=torch.uint8, device="cuda")
+    y, s1 = torch.empty_like(d["k"]), torch.empty_like(s0)
+    L.check(lib.wkv4_forward_ckpt(B, T, C, code, w.data_ptr(), d["u"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+                                  s0.data_ptr(), y.data_ptr(), s1.data_ptr(), wsf.data_ptr(), nf, ck.data_ptr(), nck, st), "fwd")
+    outs = []
+    for ckp, n in ((ck.data_ptr(), nck), (None, 0)):
+        gw, gu = torch.empty((B, C), device="cuda"), torch.empty((B, C), device="cuda")
+        gk, gv, gsi = torch.empty_like(d["k"]), torch.empty_like(d["k"]), torch.empty_like(s0)
+        L.check(lib.wkv4_backward_ckpt(B, T, C, code, w.data_ptr(), d["u"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+                                       s0.data_ptr(), d["gy"].data_ptr(), None, gw.data_ptr(), gu.data_ptr(), gk.data_ptr(),
+                                       gv.data_ptr(), gsi.data_ptr(), wsb.data_ptr(), nb, ckp, n, st), "bwd")
+        outs.append((gw, gu, gk, gv, gsi))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
