@@ -106,9 +106,10 @@ int wkv4_backward(int B, int T, int C, int dtype, const float *w, const void *u,
                   size_t workspace_bytes, void *stream);
 
 /* Optional hand-over from forward to backward of the same segment (no counterpart in the project,
- * whose backward recomputes everything): wkv4_state_ckpt_bytes() bytes that receive the state at
- * the start of every 64-token piece.  Backward given the buffer skips rebuilding those states (one
- * pass over k and v less).  0 bytes / NULL for segments under 128 tokens; NULL is always allowed and
+ * whose backward recomputes everything): wkv4_state_ckpt_bytes() bytes (2.5 per token-channel) that
+ * receive, for every 8th token, the state and its derivative w.r.t. the decay.  Backward given the
+ * buffer skips rebuilding the states and the forward sweeps of its two passes (three passes over k
+ * and v less).  0 bytes / NULL for segments under 128 tokens; NULL is always allowed and
  * makes the _ckpt entry points identical to the plain ones. */
 size_t wkv4_state_ckpt_bytes(int B, int T, int C);
 int wkv4_forward_ckpt(int B, int T, int C, int dtype, const float *w, const void *u, const void *k,

@@ -112,17 +112,33 @@ k_seg_scan(Dims d, const float *__restrict__ w_, const float *__restrict__ state
     if (state_out) { state_out[(size_t)idx * 3] = p; state_out[(size_t)idx * 3 + 1] = q; state_out[(size_t)idx * 3 + 2] = o; }
 }
 
+// What forward leaves for backward (optional): at the start of every CK-token tile of every piece the
+// state (p,q,o) and its derivative w.r.t. the decay accumulated since the piece start (dpdw,dqdw) --
+// [B][nseg][SEG/CK][5][C] floats, 2.5 bytes per token-channel.  With it neither backward pass needs its
+// forward sweep over the piece (which is there only to find the tile-start values).
+constexpr int CK = 8;
+constexpr int NCK = SEG / CK;
+__device__ __forceinline__ size_t cidx(const Dims &d, int b, int seg, int tile, int c) {
+    return (((size_t)(b * d.nseg + seg) * NCK + tile) * 5) * d.C + c;
+}
+
 template <typename F>
 __global__ void __launch_bounds__(THREADS)
 k_seg_forward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
-              const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_) {
+              const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_, float *__restrict__ ck) {
     int b, seg, c, t0, len;
     if (!locate(d, b, seg, c, t0, len)) return;
     const float w = w_[c], u = Elem<F>::ld(u_ + c);
     const size_t off = ((size_t)b * d.T + t0) * d.C + c;
     const size_t s = sidx(d, b, seg, c);
     float p = st[s], q = st[s + d.C], o = st[s + 2 * (size_t)d.C];
+    float dpdw = 0.f, dqdw = 0.f;
     for (int t8 = 0; t8 < len; t8 += 8) {
+        if (ck) {      // (8 = CK: every load batch starts a tile)
+            const size_t i = cidx(d, b, seg, t8 / CK, c);
+            ck[i] = p; ck[i + d.C] = q; ck[i + 2 * (size_t)d.C] = o;
+            ck[i + 3 * (size_t)d.C] = dpdw; ck[i + 4 * (size_t)d.C] = dqdw;
+        }
         float kk[8], vv[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
@@ -137,6 +153,7 @@ k_seg_forward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, co
                 exp_pair(o, u + kk[j], A, E, m);
                 Elem<F>::st(y_ + off + (size_t)(t8 + j) * d.C, __fdividef(A * p + E * vv[j], A * q + E));
                 exp_pair(w + o, kk[j], A, E, m);
+                if (ck) { dpdw = A * (p + dpdw); dqdw = A * (q + dqdw); }
                 p = A * p + E * vv[j]; q = A * q + E; o = m;
             }
         }
@@ -253,6 +270,86 @@ k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, c
     }
 }
 
+// The same two passes when the forward call left its tile checkpoints: no forward sweep.  Tiles of CK
+// tokens are taken in reverse; each starts from its checkpoint, recomputes y, 1/denominator and the
+// exponent for its tokens (FINAL: and adds the tile's share of gw, gu, whose running derivatives
+// dpdw, dqdw come from the checkpoint too), then runs the reverse recurrence over them.
+template <typename F, bool FINAL>
+__global__ void __launch_bounds__(THREADS)
+k_seg_backward_ck(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
+                  const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ ck,
+                  const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
+                  F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    int b, seg, c, t0, len;
+    if (!locate(d, b, seg, c, t0, len)) return;
+    const float w = w_[c], u = Elem<F>::ld(u_ + c);
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    const size_t s = sidx(d, b, seg, c);
+    float gw = 0.f, gu = 0.f;
+    float gp = 0.f, gq = 0.f, go = MIN_VALUE;
+    if (FINAL) { gp = gend[s]; gq = gend[s + d.C]; go = gend[s + 2 * (size_t)d.C]; }
+    const int last = (len - 1) / CK;
+#pragma unroll 1
+    for (int tile = last; tile >= 0; tile--) {
+        const size_t ci = cidx(d, b, seg, tile, c);
+        float p = ck[ci], q = ck[ci + d.C], o = ck[ci + 2 * (size_t)d.C];
+        float dpdw = 0.f, dqdw = 0.f;
+        if (FINAL) { dpdw = ck[ci + 3 * (size_t)d.C]; dqdw = ck[ci + 4 * (size_t)d.C]; }
+        float kk[CK], vv[CK], gg[CK];
+#pragma unroll
+        for (int j = 0; j < CK; j++) {
+            const int t = tile * CK + j;
+            const bool in = t < len;
+            kk[j] = in ? Elem<F>::ld(k_ + off + (size_t)t * d.C) : 0.f;
+            vv[j] = in ? Elem<F>::ld(v_ + off + (size_t)t * d.C) : 0.f;
+            gg[j] = in ? Elem<F>::ld(gy_ + off + (size_t)t * d.C) : 0.f;
+        }
+        float ys[CK], zs[CK], ze[CK];
+#pragma unroll
+        for (int j = 0; j < CK; j++) {
+            if (tile * CK + j < len) {
+                float A, E, m;
+                exp_pair(o, u + kk[j], A, E, m);
+                const float iden = __fdividef(1.f, A * q + E);
+                ys[j] = (A * p + E * vv[j]) * iden; zs[j] = iden; ze[j] = kk[j] + u - m;
+                if (FINAL) {
+                    gw += gg[j] * (dpdw - dqdw * ys[j]) * iden * A;
+                    gu += gg[j] * (vv[j] - ys[j]) * E * iden;
+                }
+                exp_pair(w + o, kk[j], A, E, m);
+                if (FINAL) { dpdw = A * (p + dpdw); dqdw = A * (q + dqdw); }
+                p = A * p + E * vv[j]; q = A * q + E; o = m;
+            }
+        }
+        // the piece's end: what the incoming gradient sees of the decay through the whole piece
+        if (FINAL && tile == last) gw += (gp * dpdw + gq * dqdw) * __expf(o + go);
+#pragma unroll
+        for (int j = CK - 1; j >= 0; j--) {
+            const int t = tile * CK + j;
+            if (t < len) {
+                const size_t ii = off + (size_t)t * d.C;
+                const float gz = gg[j] * zs[j];
+                float A, E, m;
+                if (FINAL) {
+                    A = gz * __expf(ze[j]);
+                    E = __expf(kk[j] + go);
+                    Elem<F>::st(gk_ + ii, A * (vv[j] - ys[j]) + E * (gp * vv[j] + gq));
+                    Elem<F>::st(gv_ + ii, A + E * gp);
+                }
+                exp_pair(w + go, ze[j] - kk[j] - u, A, E, m);
+                E *= gz;
+                gp = A * gp + E; gq = A * gq - E * ys[j]; go = m;
+            }
+        }
+    }
+    if (FINAL) {
+        gw_part[(size_t)(b * d.nseg + seg) * d.C + c] = gw * w;
+        gu_part[(size_t)(b * d.nseg + seg) * d.C + c] = gu;
+    } else {
+        rloc[s] = gp; rloc[s + d.C] = gq; rloc[s + 2 * (size_t)d.C] = go;
+    }
+}
+
 // per chain, in reverse: incoming gradient at the end of every segment, and the chain's glast_state
 __global__ void __launch_bounds__(THREADS)
 k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gstate_out,
@@ -299,11 +396,11 @@ template <typename F>
 int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v, const float *si, void *y,
             float *so, float *ws, float *ckpt, cudaStream_t s) {
     const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C;
-    float *loc = ws, *st = ckpt ? ckpt : ws + n3;
+    float *loc = ws, *st = ws + n3;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     k_seg_summary<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
     k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
-    k_seg_forward<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st, (F *)y);
+    k_seg_forward<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st, (F *)y, ckpt);
     return launch_status();
 }
 
@@ -315,17 +412,23 @@ int par_bwd(Dims d, const float *w, const void *u, const void *k, const void *v,
     float *loc = ws, *stw = loc + n3, *rloc = stw + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     const unsigned nb = blocks(nthr), nc = blocks((long long)d.B * d.C);
-    const float *st = ckpt;
-    if (!ckpt) {      // the forward call did not hand the piece-start states over: rebuild them
+    if (ckpt) {
+        // the forward call left its tile checkpoints: neither pass needs a forward sweep
+        k_seg_backward_ck<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
+                                                           ckpt, nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
+        k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
+        k_seg_backward_ck<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
+                                                          ckpt, gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
+    } else {
+        // rebuild the piece-start states, then the two passes with their own forward sweeps
         k_seg_summary<F><<<nb, THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
         k_seg_scan<<<nc, THREADS, 0, s>>>(d, w, si, loc, stw, nullptr);
-        st = stw;
+        k_seg_backward<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
+                                                        stw, nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
+        k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
+        k_seg_backward<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
+                                                       stw, gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
     }
-    k_seg_backward<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy, st,
-                                                    nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
-    k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
-    k_seg_backward<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy, st,
-                                                   gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
     k_seg_reduce<<<nc, THREADS, 0, s>>>(d, gwp, gup, gw, gu);
     return launch_status();
 }
@@ -342,7 +445,7 @@ size_t v4_par_backward_workspace(int B, int T, int C) {
 }
 
 size_t v4_par_ckpt_bytes(int B, int T, int C) {
-    return (size_t)B * ((T + SEG - 1) / SEG) * 3 * C * sizeof(float);
+    return (size_t)B * ((T + SEG - 1) / SEG) * NCK * 5 * C * sizeof(float);
 }
 
 int v4_par_forward(int B, int T, int C, int dtype, const float *w, const void *u, const void *k, const void *v,
