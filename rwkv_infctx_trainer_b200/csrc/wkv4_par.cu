@@ -350,6 +350,229 @@ k_seg_backward_ck(Dims d, const float *__restrict__ w_, const F *__restrict__ u_
     }
 }
 
+// ---------------------------------------------------------------------------
+// 16-bit I/O: the same three hot kernels with TWO adjacent channels per thread.  A 2-byte access per
+// lane moves 64 bytes per warp instruction; these kernels are bound by latency, so what counts is
+// the bytes each instruction in flight carries.  With a channel pair per thread every k, v, gy, y,
+// gk, gv access is 4 bytes per lane (128 bytes per warp), half as many threads run the same number
+// of chains, and every thread has two independent chains to interleave.  (C must be even.)
+template <typename F> struct Pair;
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 ld(const __nv_bfloat16 *p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+    }
+    static __device__ __forceinline__ void st(__nv_bfloat16 *p, float a, float b) {
+        *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b);
+    }
+};
+template <> struct Pair<__half> {
+    static __device__ __forceinline__ float2 ld(const __half *p) {
+        return __half22float2(*reinterpret_cast<const __half2 *>(p));
+    }
+    static __device__ __forceinline__ void st(__half *p, float a, float b) {
+        *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(a, b);
+    }
+};
+
+// thread -> (b, seg, channel pair c, c+1)
+__device__ __forceinline__ bool locate2(const Dims &d, int &b, int &seg, int &c, int &t0, int &len) {
+    const long long idx = (long long)blockIdx.x * THREADS + threadIdx.x;
+    const int half = d.C / 2;
+    if (idx >= (long long)d.B * d.nseg * half) return false;
+    c = 2 * (int)(idx % half);
+    seg = (int)((idx / half) % d.nseg);
+    b = (int)(idx / ((long long)half * d.nseg));
+    t0 = seg * SEG;
+    len = min(SEG, d.T - t0);
+    return true;
+}
+
+template <typename F>
+__global__ void __launch_bounds__(THREADS)
+k_seg_summary2(Dims d, const float *__restrict__ w_, const F *__restrict__ k_, const F *__restrict__ v_,
+               float *__restrict__ loc) {
+    int b, seg, c, t0, len;
+    if (!locate2(d, b, seg, c, t0, len)) return;
+    const float w[2] = {w_[c], w_[c + 1]};
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    float p[2] = {0.f, 0.f}, q[2] = {0.f, 0.f}, o[2] = {MIN_VALUE, MIN_VALUE};
+    for (int t8 = 0; t8 < len; t8 += 8) {
+        float2 kk[8], vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = t8 + j < len;
+            kk[j] = in ? Pair<F>::ld(k_ + off + (size_t)(t8 + j) * d.C) : make_float2(0.f, 0.f);
+            vv[j] = in ? Pair<F>::ld(v_ + off + (size_t)(t8 + j) * d.C) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (t8 + j < len) {
+                const float kj[2] = {kk[j].x, kk[j].y}, vj[2] = {vv[j].x, vv[j].y};
+#pragma unroll
+                for (int n = 0; n < 2; n++) {
+                    float A, E, m;
+                    exp_pair(w[n] + o[n], kj[n], A, E, m);
+                    p[n] = A * p[n] + E * vj[n]; q[n] = A * q[n] + E; o[n] = m;
+                }
+            }
+        }
+    }
+    const size_t s = sidx(d, b, seg, c);
+    *reinterpret_cast<float2 *>(loc + s) = make_float2(p[0], p[1]);
+    *reinterpret_cast<float2 *>(loc + s + d.C) = make_float2(q[0], q[1]);
+    *reinterpret_cast<float2 *>(loc + s + 2 * (size_t)d.C) = make_float2(o[0], o[1]);
+}
+
+template <typename F>
+__global__ void __launch_bounds__(THREADS)
+k_seg_forward2(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
+               const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_, float *__restrict__ ck) {
+    int b, seg, c, t0, len;
+    if (!locate2(d, b, seg, c, t0, len)) return;
+    const float w[2] = {w_[c], w_[c + 1]};
+    const float2 u2 = Pair<F>::ld(u_ + c);
+    const float u[2] = {u2.x, u2.y};
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    const size_t s = sidx(d, b, seg, c);
+    float p[2], q[2], o[2], dpdw[2] = {0.f, 0.f}, dqdw[2] = {0.f, 0.f};
+    {
+        const float2 a = *reinterpret_cast<const float2 *>(st + s), e = *reinterpret_cast<const float2 *>(st + s + d.C),
+                     f = *reinterpret_cast<const float2 *>(st + s + 2 * (size_t)d.C);
+        p[0] = a.x; p[1] = a.y; q[0] = e.x; q[1] = e.y; o[0] = f.x; o[1] = f.y;
+    }
+    for (int t8 = 0; t8 < len; t8 += 8) {
+        if (ck) {
+            const size_t i = cidx(d, b, seg, t8 / CK, c);
+            *reinterpret_cast<float2 *>(ck + i) = make_float2(p[0], p[1]);
+            *reinterpret_cast<float2 *>(ck + i + d.C) = make_float2(q[0], q[1]);
+            *reinterpret_cast<float2 *>(ck + i + 2 * (size_t)d.C) = make_float2(o[0], o[1]);
+            *reinterpret_cast<float2 *>(ck + i + 3 * (size_t)d.C) = make_float2(dpdw[0], dpdw[1]);
+            *reinterpret_cast<float2 *>(ck + i + 4 * (size_t)d.C) = make_float2(dqdw[0], dqdw[1]);
+        }
+        float2 kk[8], vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = t8 + j < len;
+            kk[j] = in ? Pair<F>::ld(k_ + off + (size_t)(t8 + j) * d.C) : make_float2(0.f, 0.f);
+            vv[j] = in ? Pair<F>::ld(v_ + off + (size_t)(t8 + j) * d.C) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (t8 + j < len) {
+                const float kj[2] = {kk[j].x, kk[j].y}, vj[2] = {vv[j].x, vv[j].y};
+                float yo[2];
+#pragma unroll
+                for (int n = 0; n < 2; n++) {
+                    float A, E, m;
+                    exp_pair(o[n], u[n] + kj[n], A, E, m);
+                    yo[n] = __fdividef(A * p[n] + E * vj[n], A * q[n] + E);
+                    exp_pair(w[n] + o[n], kj[n], A, E, m);
+                    if (ck) { dpdw[n] = A * (p[n] + dpdw[n]); dqdw[n] = A * (q[n] + dqdw[n]); }
+                    p[n] = A * p[n] + E * vj[n]; q[n] = A * q[n] + E; o[n] = m;
+                }
+                Pair<F>::st(y_ + off + (size_t)(t8 + j) * d.C, yo[0], yo[1]);
+            }
+        }
+    }
+}
+
+template <typename F, bool FINAL>
+__global__ void __launch_bounds__(THREADS)
+k_seg_backward_ck2(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
+                   const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ ck,
+                   const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
+                   F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    int b, seg, c, t0, len;
+    if (!locate2(d, b, seg, c, t0, len)) return;
+    const float w[2] = {w_[c], w_[c + 1]};
+    const float2 u2 = Pair<F>::ld(u_ + c);
+    const float u[2] = {u2.x, u2.y};
+    const size_t off = ((size_t)b * d.T + t0) * d.C + c;
+    const size_t s = sidx(d, b, seg, c);
+    auto ld2 = [](const float *p, float (&x)[2]) { const float2 a = *reinterpret_cast<const float2 *>(p); x[0] = a.x; x[1] = a.y; };
+    float gw[2] = {0.f, 0.f}, gu[2] = {0.f, 0.f};
+    float gp[2] = {0.f, 0.f}, gq[2] = {0.f, 0.f}, go[2] = {MIN_VALUE, MIN_VALUE};
+    if (FINAL) { ld2(gend + s, gp); ld2(gend + s + d.C, gq); ld2(gend + s + 2 * (size_t)d.C, go); }
+    const int last = (len - 1) / CK;
+#pragma unroll 1
+    for (int tile = last; tile >= 0; tile--) {
+        const size_t ci = cidx(d, b, seg, tile, c);
+        float p[2], q[2], o[2], dpdw[2] = {0.f, 0.f}, dqdw[2] = {0.f, 0.f};
+        ld2(ck + ci, p); ld2(ck + ci + d.C, q); ld2(ck + ci + 2 * (size_t)d.C, o);
+        if (FINAL) { ld2(ck + ci + 3 * (size_t)d.C, dpdw); ld2(ck + ci + 4 * (size_t)d.C, dqdw); }
+        float2 kk[CK], vv[CK], gg[CK];
+#pragma unroll
+        for (int j = 0; j < CK; j++) {
+            const int t = tile * CK + j;
+            const bool in = t < len;
+            kk[j] = in ? Pair<F>::ld(k_ + off + (size_t)t * d.C) : make_float2(0.f, 0.f);
+            vv[j] = in ? Pair<F>::ld(v_ + off + (size_t)t * d.C) : make_float2(0.f, 0.f);
+            gg[j] = in ? Pair<F>::ld(gy_ + off + (size_t)t * d.C) : make_float2(0.f, 0.f);
+        }
+        float ys[CK][2], zs[CK][2], ze[CK][2];
+#pragma unroll
+        for (int j = 0; j < CK; j++) {
+            if (tile * CK + j < len) {
+                const float kj[2] = {kk[j].x, kk[j].y}, vj[2] = {vv[j].x, vv[j].y}, gj[2] = {gg[j].x, gg[j].y};
+#pragma unroll
+                for (int n = 0; n < 2; n++) {
+                    float A, E, m;
+                    exp_pair(o[n], u[n] + kj[n], A, E, m);
+                    const float iden = __fdividef(1.f, A * q[n] + E);
+                    ys[j][n] = (A * p[n] + E * vj[n]) * iden; zs[j][n] = iden; ze[j][n] = kj[n] + u[n] - m;
+                    if (FINAL) {
+                        gw[n] += gj[n] * (dpdw[n] - dqdw[n] * ys[j][n]) * iden * A;
+                        gu[n] += gj[n] * (vj[n] - ys[j][n]) * E * iden;
+                    }
+                    exp_pair(w[n] + o[n], kj[n], A, E, m);
+                    if (FINAL) { dpdw[n] = A * (p[n] + dpdw[n]); dqdw[n] = A * (q[n] + dqdw[n]); }
+                    p[n] = A * p[n] + E * vj[n]; q[n] = A * q[n] + E; o[n] = m;
+                }
+            }
+        }
+        if (FINAL && tile == last) {
+#pragma unroll
+            for (int n = 0; n < 2; n++) gw[n] += (gp[n] * dpdw[n] + gq[n] * dqdw[n]) * __expf(o[n] + go[n]);
+        }
+#pragma unroll
+        for (int j = CK - 1; j >= 0; j--) {
+            const int t = tile * CK + j;
+            if (t < len) {
+                const size_t ii = off + (size_t)t * d.C;
+                const float kj[2] = {kk[j].x, kk[j].y}, vj[2] = {vv[j].x, vv[j].y}, gj[2] = {gg[j].x, gg[j].y};
+                float ok[2], ov[2];
+#pragma unroll
+                for (int n = 0; n < 2; n++) {
+                    const float gz = gj[n] * zs[j][n];
+                    float A, E, m;
+                    if (FINAL) {
+                        A = gz * __expf(ze[j][n]);
+                        E = __expf(kj[n] + go[n]);
+                        ok[n] = A * (vj[n] - ys[j][n]) + E * (gp[n] * vj[n] + gq[n]);
+                        ov[n] = A + E * gp[n];
+                    }
+                    exp_pair(w[n] + go[n], ze[j][n] - kj[n] - u[n], A, E, m);
+                    E *= gz;
+                    gp[n] = A * gp[n] + E; gq[n] = A * gq[n] - E * ys[j][n]; go[n] = m;
+                }
+                if (FINAL) {
+                    Pair<F>::st(gk_ + ii, ok[0], ok[1]);
+                    Pair<F>::st(gv_ + ii, ov[0], ov[1]);
+                }
+            }
+        }
+    }
+    if (FINAL) {
+        const size_t gi = (size_t)(b * d.nseg + seg) * d.C + c;
+        *reinterpret_cast<float2 *>(gw_part + gi) = make_float2(gw[0] * w[0], gw[1] * w[1]);
+        *reinterpret_cast<float2 *>(gu_part + gi) = make_float2(gu[0], gu[1]);
+    } else {
+        *reinterpret_cast<float2 *>(rloc + s) = make_float2(gp[0], gp[1]);
+        *reinterpret_cast<float2 *>(rloc + s + d.C) = make_float2(gq[0], gq[1]);
+        *reinterpret_cast<float2 *>(rloc + s + 2 * (size_t)d.C) = make_float2(go[0], go[1]);
+    }
+}
+
 // per chain, in reverse: incoming gradient at the end of every segment, and the chain's glast_state
 __global__ void __launch_bounds__(THREADS)
 k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gstate_out,
@@ -398,6 +621,15 @@ int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v,
     const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C;
     float *loc = ws, *st = ws + n3;
     const long long nthr = (long long)d.B * d.nseg * d.C;
+    if constexpr (sizeof(F) == 2) {
+        if (d.C % 2 == 0) {      // a channel pair per thread
+            k_seg_summary2<F><<<blocks(nthr / 2), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
+            k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
+            k_seg_forward2<F><<<blocks(nthr / 2), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st,
+                                                                   (F *)y, ckpt);
+            return launch_status();
+        }
+    }
     k_seg_summary<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
     k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
     k_seg_forward<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st, (F *)y, ckpt);
@@ -412,6 +644,20 @@ int par_bwd(Dims d, const float *w, const void *u, const void *k, const void *v,
     float *loc = ws, *stw = loc + n3, *rloc = stw + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     const unsigned nb = blocks(nthr), nc = blocks((long long)d.B * d.C);
+    if constexpr (sizeof(F) == 2) {
+        if (ckpt && d.C % 2 == 0) {      // tile checkpoints and a channel pair per thread
+            const unsigned nb2 = blocks(nthr / 2);
+            k_seg_backward_ck2<F, false><<<nb2, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v,
+                                                                 (const F *)gy, ckpt, nullptr, rloc, nullptr, nullptr,
+                                                                 nullptr, nullptr);
+            k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
+            k_seg_backward_ck2<F, true><<<nb2, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v,
+                                                                (const F *)gy, ckpt, gend, nullptr, (F *)gk, (F *)gv, gwp,
+                                                                gup);
+            k_seg_reduce<<<nc, THREADS, 0, s>>>(d, gwp, gup, gw, gu);
+            return launch_status();
+        }
+    }
     if (ckpt) {
         // the forward call left its tile checkpoints: neither pass needs a forward sweep
         k_seg_backward_ck<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
