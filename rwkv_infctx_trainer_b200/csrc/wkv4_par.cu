@@ -101,13 +101,27 @@ k_seg_scan(Dims d, const float *__restrict__ w_, const float *__restrict__ state
     const float w = w_[c];
     float p = 0.f, q = 0.f, o = MIN_VALUE;
     if (state_in) { p = state_in[(size_t)idx * 3]; q = state_in[(size_t)idx * 3 + 1]; o = state_in[(size_t)idx * 3 + 2]; }
-    for (int seg = 0; seg < d.nseg; seg++) {
-        const size_t s = sidx(d, b, seg, c);
-        st[s] = p; st[s + d.C] = q; st[s + 2 * (size_t)d.C] = o;
-        const int len = min(SEG, d.T - seg * SEG);
-        float A, E, m;
-        exp_pair(o + len * w, loc[s + 2 * (size_t)d.C], A, E, m);
-        p = A * p + E * loc[s]; q = A * q + E * loc[s + d.C]; o = m;
+    // (the summaries of 8 pieces are fetched together: the chain is short, the loads are what takes time)
+    for (int s8 = 0; s8 < d.nseg; s8 += 8) {
+        float lp[8], lq[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = s8 + j < d.nseg;
+            const size_t s = sidx(d, b, in ? s8 + j : s8, c);
+            lp[j] = in ? loc[s] : 0.f; lq[j] = in ? loc[s + d.C] : 0.f; lo[j] = in ? loc[s + 2 * (size_t)d.C] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int seg = s8 + j;
+            if (seg < d.nseg) {
+                const size_t s = sidx(d, b, seg, c);
+                st[s] = p; st[s + d.C] = q; st[s + 2 * (size_t)d.C] = o;
+                const int len = min(SEG, d.T - seg * SEG);
+                float A, E, m;
+                exp_pair(o + len * w, lo[j], A, E, m);
+                p = A * p + E * lp[j]; q = A * q + E * lq[j]; o = m;
+            }
+        }
     }
     if (state_out) { state_out[(size_t)idx * 3] = p; state_out[(size_t)idx * 3 + 1] = q; state_out[(size_t)idx * 3 + 2] = o; }
 }
@@ -591,13 +605,26 @@ k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gsta
         gp = gstate_out[(size_t)idx * 3]; gq = gstate_out[(size_t)idx * 3 + 1]; go = gstate_out[(size_t)idx * 3 + 2];
         if (gp == 0.f && gq == 0.f) go = MIN_VALUE;
     }
-    for (int seg = d.nseg - 1; seg >= 0; seg--) {
-        const size_t s = sidx(d, b, seg, c);
-        gend[s] = gp; gend[s + d.C] = gq; gend[s + 2 * (size_t)d.C] = go;
-        const int len = min(SEG, d.T - seg * SEG);
-        float A, E, m;
-        exp_pair(go + len * w, rloc[s + 2 * (size_t)d.C], A, E, m);
-        gp = A * gp + E * rloc[s]; gq = A * gq + E * rloc[s + d.C]; go = m;
+    for (int s8 = d.nseg - 1; s8 >= 0; s8 -= 8) {
+        float lp[8], lq[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const bool in = s8 - j >= 0;
+            const size_t s = sidx(d, b, in ? s8 - j : 0, c);
+            lp[j] = in ? rloc[s] : 0.f; lq[j] = in ? rloc[s + d.C] : 0.f; lo[j] = in ? rloc[s + 2 * (size_t)d.C] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int seg = s8 - j;
+            if (seg >= 0) {
+                const size_t s = sidx(d, b, seg, c);
+                gend[s] = gp; gend[s + d.C] = gq; gend[s + 2 * (size_t)d.C] = go;
+                const int len = min(SEG, d.T - seg * SEG);
+                float A, E, m;
+                exp_pair(go + len * w, lo[j], A, E, m);
+                gp = A * gp + E * lp[j]; gq = A * gq + E * lq[j]; go = m;
+            }
+        }
     }
     if (gstate_in) { gstate_in[(size_t)idx * 3] = gp; gstate_in[(size_t)idx * 3 + 1] = gq; gstate_in[(size_t)idx * 3 + 2] = go; }
 }
@@ -609,6 +636,7 @@ k_seg_reduce(Dims d, const float *__restrict__ gw_part, const float *__restrict_
     if (idx >= d.B * d.C) return;
     const int b = idx / d.C, c = idx % d.C;
     float a = 0.f, e = 0.f;
+#pragma unroll 8
     for (int seg = 0; seg < d.nseg; seg++) {
         a += gw_part[(size_t)(b * d.nseg + seg) * d.C + c];
         e += gu_part[(size_t)(b * d.nseg + seg) * d.C + c];
