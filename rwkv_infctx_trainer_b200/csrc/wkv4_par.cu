@@ -64,6 +64,8 @@ template <typename F>
 __global__ void __launch_bounds__(THREADS)
 k_seg_summary(Dims d, const float *__restrict__ w_, const F *__restrict__ k_, const F *__restrict__ v_,
               float *__restrict__ loc) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate(d, b, seg, c, t0, len)) return;
     const float w = w_[c];
@@ -95,6 +97,8 @@ k_seg_summary(Dims d, const float *__restrict__ w_, const F *__restrict__ k_, co
 __global__ void __launch_bounds__(THREADS)
 k_seg_scan(Dims d, const float *__restrict__ w_, const float *__restrict__ state_in,
            const float *__restrict__ loc, float *__restrict__ st, float *__restrict__ state_out) {
+    pdl_wait();
+    pdl_trigger();
     const int idx = blockIdx.x * THREADS + threadIdx.x;
     if (idx >= d.B * d.C) return;
     const int b = idx / d.C, c = idx % d.C;
@@ -140,6 +144,8 @@ template <typename F>
 __global__ void __launch_bounds__(THREADS)
 k_seg_forward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
               const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_, float *__restrict__ ck) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate(d, b, seg, c, t0, len)) return;
     const float w = w_[c], u = Elem<F>::ld(u_ + c);
@@ -183,6 +189,8 @@ k_seg_backward(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, c
                const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ st,
                const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
                F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate(d, b, seg, c, t0, len)) return;
     const float w = w_[c], u = Elem<F>::ld(u_ + c);
@@ -294,6 +302,8 @@ k_seg_backward_ck(Dims d, const float *__restrict__ w_, const F *__restrict__ u_
                   const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ ck,
                   const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
                   F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate(d, b, seg, c, t0, len)) return;
     const float w = w_[c], u = Elem<F>::ld(u_ + c);
@@ -410,6 +420,8 @@ template <typename F>
 __global__ void __launch_bounds__(THREADS)
 k_seg_summary2(Dims d, const float *__restrict__ w_, const F *__restrict__ k_, const F *__restrict__ v_,
                float *__restrict__ loc) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate2(d, b, seg, c, t0, len)) return;
     const float w[2] = {w_[c], w_[c + 1]};
@@ -446,6 +458,8 @@ template <typename F>
 __global__ void __launch_bounds__(THREADS)
 k_seg_forward2(Dims d, const float *__restrict__ w_, const F *__restrict__ u_, const F *__restrict__ k_,
                const F *__restrict__ v_, const float *__restrict__ st, F *__restrict__ y_, float *__restrict__ ck) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate2(d, b, seg, c, t0, len)) return;
     const float w[2] = {w_[c], w_[c + 1]};
@@ -501,6 +515,8 @@ k_seg_backward_ck2(Dims d, const float *__restrict__ w_, const F *__restrict__ u
                    const F *__restrict__ v_, const F *__restrict__ gy_, const float *__restrict__ ck,
                    const float *__restrict__ gend, float *__restrict__ rloc, F *__restrict__ gk_,
                    F *__restrict__ gv_, float *__restrict__ gw_part, float *__restrict__ gu_part) {
+    pdl_wait();
+    pdl_trigger();
     int b, seg, c, t0, len;
     if (!locate2(d, b, seg, c, t0, len)) return;
     const float w[2] = {w_[c], w_[c + 1]};
@@ -596,6 +612,8 @@ k_seg_backward_ck2(Dims d, const float *__restrict__ w_, const F *__restrict__ u
 __global__ void __launch_bounds__(THREADS)
 k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gstate_out,
             const float *__restrict__ rloc, float *__restrict__ gend, float *__restrict__ gstate_in) {
+    pdl_wait();
+    pdl_trigger();
     const int idx = blockIdx.x * THREADS + threadIdx.x;
     if (idx >= d.B * d.C) return;
     const int b = idx / d.C, c = idx % d.C;
@@ -632,6 +650,8 @@ k_seg_rscan(Dims d, const float *__restrict__ w_, const float *__restrict__ gsta
 __global__ void __launch_bounds__(THREADS)
 k_seg_reduce(Dims d, const float *__restrict__ gw_part, const float *__restrict__ gu_part,
              float *__restrict__ gw, float *__restrict__ gu) {
+    pdl_wait();
+    pdl_trigger();
     const int idx = blockIdx.x * THREADS + threadIdx.x;
     if (idx >= d.B * d.C) return;
     const int b = idx / d.C, c = idx % d.C;
@@ -654,19 +674,25 @@ int par_fwd(Dims d, const float *w, const void *u, const void *k, const void *v,
     const size_t n3 = (size_t)d.B * d.nseg * 3 * d.C;
     float *loc = ws, *st = ws + n3;
     const long long nthr = (long long)d.B * d.nseg * d.C;
+    int err = WKV_OK;
     if constexpr (sizeof(F) >= 2) {
         if (d.C % 2 == 0) {      // a channel pair per thread (every dtype)
-            k_seg_summary2<F><<<blocks(nthr / 2), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
-            k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
-            k_seg_forward2<F><<<blocks(nthr / 2), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st,
-                                                                   (F *)y, ckpt);
-            return launch_status();
+            err |= launch_chained(k_seg_summary2<F>, dim3(blocks(nthr / 2)), dim3(THREADS), 0, s, d, w,
+                                  (const F *)k, (const F *)v, loc);
+            err |= launch_chained(k_seg_scan, dim3(blocks((long long)d.B * d.C)), dim3(THREADS), 0, s, d, w, si,
+                                  loc, st, so);
+            err |= launch_chained(k_seg_forward2<F>, dim3(blocks(nthr / 2)), dim3(THREADS), 0, s, d, w,
+                                  (const F *)u, (const F *)k, (const F *)v, st, (F *)y, ckpt);
+            return err ? WKV_ERR_LAUNCH : WKV_OK;
         }
     }
-    k_seg_summary<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
-    k_seg_scan<<<blocks((long long)d.B * d.C), THREADS, 0, s>>>(d, w, si, loc, st, so);
-    k_seg_forward<F><<<blocks(nthr), THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, st, (F *)y, ckpt);
-    return launch_status();
+    err |= launch_chained(k_seg_summary<F>, dim3(blocks(nthr)), dim3(THREADS), 0, s, d, w, (const F *)k,
+                          (const F *)v, loc);
+    err |= launch_chained(k_seg_scan, dim3(blocks((long long)d.B * d.C)), dim3(THREADS), 0, s, d, w, si, loc, st,
+                          so);
+    err |= launch_chained(k_seg_forward<F>, dim3(blocks(nthr)), dim3(THREADS), 0, s, d, w, (const F *)u,
+                          (const F *)k, (const F *)v, st, (F *)y, ckpt);
+    return err ? WKV_ERR_LAUNCH : WKV_OK;
 }
 
 template <typename F>
@@ -677,39 +703,45 @@ int par_bwd(Dims d, const float *w, const void *u, const void *k, const void *v,
     float *loc = ws, *stw = loc + n3, *rloc = stw + n3, *gend = rloc + n3, *gwp = gend + n3, *gup = gwp + n1;
     const long long nthr = (long long)d.B * d.nseg * d.C;
     const unsigned nb = blocks(nthr), nc = blocks((long long)d.B * d.C);
+    int err = WKV_OK;
     if constexpr (sizeof(F) >= 2) {
         if (ckpt && d.C % 2 == 0) {      // tile checkpoints and a channel pair per thread
             const unsigned nb2 = blocks(nthr / 2);
-            k_seg_backward_ck2<F, false><<<nb2, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v,
-                                                                 (const F *)gy, ckpt, nullptr, rloc, nullptr, nullptr,
-                                                                 nullptr, nullptr);
-            k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
-            k_seg_backward_ck2<F, true><<<nb2, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v,
-                                                                (const F *)gy, ckpt, gend, nullptr, (F *)gk, (F *)gv, gwp,
-                                                                gup);
-            k_seg_reduce<<<nc, THREADS, 0, s>>>(d, gwp, gup, gw, gu);
-            return launch_status();
+            err |= launch_chained(k_seg_backward_ck2<F, false>, dim3(nb2), dim3(THREADS), 0, s, d, w, (const F *)u,
+                                  (const F *)k, (const F *)v, (const F *)gy, ckpt, nullptr, rloc, nullptr, nullptr,
+                                  nullptr, nullptr);
+            err |= launch_chained(k_seg_rscan, dim3(nc), dim3(THREADS), 0, s, d, w, gso, rloc, gend, gsi);
+            err |= launch_chained(k_seg_backward_ck2<F, true>, dim3(nb2), dim3(THREADS), 0, s, d, w, (const F *)u,
+                                  (const F *)k, (const F *)v, (const F *)gy, ckpt, gend, nullptr, (F *)gk, (F *)gv,
+                                  gwp, gup);
+            err |= launch_chained(k_seg_reduce, dim3(nc), dim3(THREADS), 0, s, d, gwp, gup, gw, gu);
+            return err ? WKV_ERR_LAUNCH : WKV_OK;
         }
     }
     if (ckpt) {
         // the forward call left its tile checkpoints: neither pass needs a forward sweep
-        k_seg_backward_ck<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
-                                                           ckpt, nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
-        k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
-        k_seg_backward_ck<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
-                                                          ckpt, gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
+        err |= launch_chained(k_seg_backward_ck<F, false>, dim3(nb), dim3(THREADS), 0, s, d, w, (const F *)u,
+                              (const F *)k, (const F *)v, (const F *)gy, ckpt, nullptr, rloc, nullptr, nullptr,
+                              nullptr, nullptr);
+        err |= launch_chained(k_seg_rscan, dim3(nc), dim3(THREADS), 0, s, d, w, gso, rloc, gend, gsi);
+        err |= launch_chained(k_seg_backward_ck<F, true>, dim3(nb), dim3(THREADS), 0, s, d, w, (const F *)u,
+                              (const F *)k, (const F *)v, (const F *)gy, ckpt, gend, nullptr, (F *)gk, (F *)gv, gwp,
+                              gup);
     } else {
         // rebuild the piece-start states, then the two passes with their own forward sweeps
-        k_seg_summary<F><<<nb, THREADS, 0, s>>>(d, w, (const F *)k, (const F *)v, loc);
-        k_seg_scan<<<nc, THREADS, 0, s>>>(d, w, si, loc, stw, nullptr);
-        k_seg_backward<F, false><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
-                                                        stw, nullptr, rloc, nullptr, nullptr, nullptr, nullptr);
-        k_seg_rscan<<<nc, THREADS, 0, s>>>(d, w, gso, rloc, gend, gsi);
-        k_seg_backward<F, true><<<nb, THREADS, 0, s>>>(d, w, (const F *)u, (const F *)k, (const F *)v, (const F *)gy,
-                                                       stw, gend, nullptr, (F *)gk, (F *)gv, gwp, gup);
+        err |= launch_chained(k_seg_summary<F>, dim3(nb), dim3(THREADS), 0, s, d, w, (const F *)k, (const F *)v,
+                              loc);
+        err |= launch_chained(k_seg_scan, dim3(nc), dim3(THREADS), 0, s, d, w, si, loc, stw, nullptr);
+        err |= launch_chained(k_seg_backward<F, false>, dim3(nb), dim3(THREADS), 0, s, d, w, (const F *)u,
+                              (const F *)k, (const F *)v, (const F *)gy, stw, nullptr, rloc, nullptr, nullptr,
+                              nullptr, nullptr);
+        err |= launch_chained(k_seg_rscan, dim3(nc), dim3(THREADS), 0, s, d, w, gso, rloc, gend, gsi);
+        err |= launch_chained(k_seg_backward<F, true>, dim3(nb), dim3(THREADS), 0, s, d, w, (const F *)u,
+                              (const F *)k, (const F *)v, (const F *)gy, stw, gend, nullptr, (F *)gk, (F *)gv, gwp,
+                              gup);
     }
-    k_seg_reduce<<<nc, THREADS, 0, s>>>(d, gwp, gup, gw, gu);
-    return launch_status();
+    err |= launch_chained(k_seg_reduce, dim3(nc), dim3(THREADS), 0, s, d, gwp, gup, gw, gu);
+    return err ? WKV_ERR_LAUNCH : WKV_OK;
 }
 
 }  // namespace

@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 2)
 k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
             const __grid_constant__ CUtensorMap map_rh, const FwdParams P) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ unsigned char smem_raw[];
     // the swizzled tiles want a 1024-byte aligned base.  The padding is added to the __shared__ array
     // itself (not to an integer copy of its address), so the compiler still knows that everything
@@ -621,6 +623,8 @@ static_assert(sizeof(FwdSmem) + 1024 <= 115712, "two CTAs per SM need <= 113 KiB
 __global__ void __launch_bounds__(256)
 k_group_scan(const float *__restrict__ U, const float *__restrict__ dG, const float *__restrict__ init,
              float *__restrict__ starts, float *__restrict__ final_out, int G, int layout, int reverse) {
+    pdl_wait();
+    pdl_trigger();
     const int idx = blockIdx.x * 256 + threadIdx.x, bh = idx >> 12, e = idx & 4095, row = e >> 6, vc = e & 63;
     const size_t lidx = (size_t)bh * 4096 + (layout == WKV_STATE_KV ? e : vc * 64 + row);
     float S = init ? init[lidx] : 0.f;
@@ -680,6 +684,8 @@ bool chunked_supported(const wkv_args_t *a, bool) {
 // a bf16 x is seen at bf16 resolution of x -- the resolution the activation has in bf16 training.
 namespace {
 __global__ void __launch_bounds__(256) k_ew_to_x(const float4 *__restrict__ ew, uint2 *__restrict__ x, size_t n4) {
+    pdl_wait();
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n4) return;
     const float4 e = ew[i];
@@ -695,10 +701,11 @@ size_t chunked_wconv_bytes(const wkv_args_t *a, bool per_token_w) {
 int chunked_convert_w(wkv_args_t *a, bool per_token_w, void *scratch, cudaStream_t stream) {
     if (!per_token_w || a->w_kind != WKV_W_NEGEXP) return WKV_OK;
     const size_t n4 = (size_t)a->B * a->T * a->H * 16;
-    k_ew_to_x<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float4 *)a->w, (uint2 *)scratch, n4);
+    const int err = launch_chained(k_ew_to_x, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream,
+                                   (const float4 *)a->w, (uint2 *)scratch, n4);
     a->w = scratch;
     a->w_kind = WKV_W_RAW;
-    return launch_status();
+    return err;
 }
 
 int device_sm_count() {
@@ -765,9 +772,9 @@ int launch_group_scan(const void *group_ws, int BH, int G, const float *init, fl
                       bool reverse, cudaStream_t stream) {
     const GroupLayout GL = group_layout((size_t)BH * G);
     const char *g = (const char *)group_ws;
-    k_group_scan<<<BH * 16, 256, 0, stream>>>((const float *)(g + GL.gU), (const float *)(g + GL.gD), init,
-                                              (float *)(g + GL.gstart), final_out, G, layout, reverse ? 1 : 0);
-    return launch_status();
+    return launch_chained(k_group_scan, dim3(BH * 16), dim3(256), 0, stream, (const float *)(g + GL.gU),
+                          (const float *)(g + GL.gD), init, (float *)(g + GL.gstart), final_out, G, layout,
+                          reverse ? 1 : 0);
 }
 
 }  // namespace chunked
@@ -828,8 +835,9 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
         p.state_in = nullptr; p.gstart = nullptr; p.state_out = nullptr;
         p.gU = (float *)(g + GL.gU); p.gD = (float *)(g + GL.gD);
         p.y = nullptr; p.ckpt = nullptr; p.dchunk = nullptr;
-        kerns[pt][FWD_SUMMARY]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
-        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        if (launch_chained(kerns[pt][FWD_SUMMARY], dim3(gp.G, BH), dim3(FWD_THREADS), smem, stream, mr, mk, mv, mw,
+                           mrh, p) != WKV_OK)
+            return WKV_ERR_LAUNCH;
         // B: the state at the start of every group.  (The state after the segment is left to the last
         // group of pass C, so that a later restart from saved states reproduces it bit for bit.)
         if (launch_group_scan(g, BH, gp.G, a->state_in, nullptr, a->state_layout, false, stream) != WKV_OK)
@@ -851,8 +859,7 @@ int chunked_forward_impl(const wkv_args_t *a, bool per_token_w, void *state_ckpt
         p.mildflag = (unsigned char *)(ck + CL.mild);
         if (!make_btc_map(&mrh, ck + CL.rhat, B, T, C)) return WKV_ERR_LAUNCH;
     }
-    kerns[pt][mode]<<<dim3(gp.G, BH), FWD_THREADS, smem, stream>>>(mr, mk, mv, mw, mrh, p);
-    return launch_status();
+    return launch_chained(kerns[pt][mode], dim3(gp.G, BH), dim3(FWD_THREADS), smem, stream, mr, mk, mv, mw, mrh, p);
 }
 
 int chunked_forward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &tst, cudaStream_t stream) {

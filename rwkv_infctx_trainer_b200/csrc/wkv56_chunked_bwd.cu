@@ -87,6 +87,8 @@ struct DscanParams {
 __global__ void __launch_bounds__(160)
 k_chunk_dscan(const __grid_constant__ CUtensorMap map_rh, const __grid_constant__ CUtensorMap map_gy,
               const __grid_constant__ CUtensorMap map_s, const DscanParams P) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ unsigned char smem_raw[];
     // the swizzled tiles want a 1024-byte aligned base.  The padding is added to the __shared__ array
     // itself (not to an integer copy of its address), so the compiler still knows that everything
@@ -991,6 +993,8 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
 // one CTA per (batch, head, chunk); CTAs of steep chunks leave early (the other kernel has them)
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(256, 2) k_chunk_bwd(BWD_MAPS, const BwdParams P) {
+    pdl_wait();
+    pdl_trigger();
     bwd_chunk<PER_TOKEN, true>(BWD_MAP_ARGS, P, (int)blockIdx.x);
 }
 
@@ -1000,6 +1004,8 @@ __global__ void __launch_bounds__(256, 2) k_chunk_bwd(BWD_MAPS, const BwdParams 
 // One CTA per SM: the general body inside a loop wants more than the 128 registers two CTAs leave.
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(256, 1) k_chunk_bwd_steep(BWD_MAPS, const BwdParams P, const int total) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ unsigned char is_steep[256];
     for (int base = blockIdx.x; base < total; base += 256 * gridDim.x) {
         const int mine = base + threadIdx.x * gridDim.x;
@@ -1018,6 +1024,8 @@ __global__ void __launch_bounds__(256, 1) k_chunk_bwd_steep(BWD_MAPS, const BwdP
 
 // sum the per-chunk partials: out[bh*64 + k] = sum_j part[(bh*n + j)*64 + k]
 __global__ void k_reduce_partials(const float *__restrict__ part, float *__restrict__ out, int n, int total) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int bh = i >> 6, k = i & 63;
@@ -1105,8 +1113,8 @@ int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &
             p.summary = 1;
             p.gstate_out = nullptr; p.gstart = nullptr; p.gstate_in = nullptr;
             p.gU = (float *)(g + GL.gU); p.gD = (float *)(g + GL.gD);
-            k_chunk_dscan<<<BH * gp.G, 160, smem, stream>>>(mrh, mgy, ms, p);
-            if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+            if (launch_chained(k_chunk_dscan, dim3(BH * gp.G), dim3(160), smem, stream, mrh, mgy, ms, p) != WKV_OK)
+                return WKV_ERR_LAUNCH;
             if (launch_group_scan(g, BH, gp.G, a->gstate_out, a->gstate_in, a->state_layout, true, stream) != WKV_OK)
                 return WKV_ERR_LAUNCH;
         }
@@ -1115,8 +1123,8 @@ int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &
         p.gstart = gp.G > 1 ? (const float *)(g + GL.gstart) : nullptr;
         p.gstate_in = gp.G > 1 ? nullptr : a->gstate_in;
         p.gU = nullptr; p.gD = nullptr;
-        k_chunk_dscan<<<BH * gp.G, 160, smem, stream>>>(mrh, mgy, ms, p);
-        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        if (launch_chained(k_chunk_dscan, dim3(BH * gp.G), dim3(160), smem, stream, mrh, mgy, ms, p) != WKV_OK)
+            return WKV_ERR_LAUNCH;
     }
     // 3. per-chunk gradients
     {
@@ -1138,20 +1146,26 @@ int chunked_backward(const wkv_args_t *a0, bool per_token_w, const ChunkedTest &
             !set_max_smem_once(kern_steep, (int)smem, attr_done[1][pt]))
             return WKV_ERR_LAUNCH;
         // every chunk the forward kernel found mild (all of them, on ordinary data) ...
-        kern<<<BH * n, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p);
-        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        if (launch_chained(kern, dim3(BH * n), dim3(256), smem, stream, mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv,
+                           mgw, p) != WKV_OK)
+            return WKV_ERR_LAUNCH;
         // ... and the ones it flagged as steep
         const int steep_grid = BH * n < device_sm_count() ? BH * n : device_sm_count();
-        kern_steep<<<steep_grid, 256, smem, stream>>>(mr, mk, mv, mw, mgy, ms, md, mgr, mgk, mgv, mgw, p, BH * n);
-        if (launch_status() != WKV_OK) return WKV_ERR_LAUNCH;
+        if (launch_chained(kern_steep, dim3(steep_grid), dim3(256), smem, stream, mr, mk, mv, mw, mgy, ms, md, mgr,
+                           mgk, mgv, mgw, p, BH * n) != WKV_OK)
+            return WKV_ERR_LAUNCH;
     }
     // 4. fold the per-chunk partial sums
     {
         const int total = BH * 64;
-        k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gu_part, a->gu, n, total);
-        if (!per_token_w) k_reduce_partials<<<(total + 255) / 256, 256, 0, stream>>>(gw_part, (float *)a->gw, n, total);
+        if (launch_chained(k_reduce_partials, dim3((total + 255) / 256), dim3(256), 0, stream, (const float *)gu_part,
+                           (float *)a->gu, n, total) != WKV_OK)
+            return WKV_ERR_LAUNCH;
+        if (!per_token_w && launch_chained(k_reduce_partials, dim3((total + 255) / 256), dim3(256), 0, stream,
+                                           (const float *)gw_part, (float *)a->gw, n, total) != WKV_OK)
+            return WKV_ERR_LAUNCH;
     }
-    return launch_status();
+    return WKV_OK;
 }
 
 }  // namespace wkv

@@ -29,6 +29,33 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? WKV_OK : WKV_ERR_LAUNCH; }
 
+// Programmatic dependent launch.  A kernel launched through launch_chained() may be scheduled
+// while the kernel before it in the stream is still running, which hides its launch latency
+// behind that kernel's last CTAs.  pdl_wait() returns once every earlier kernel of the stream
+// has finished and its writes are visible: it is the first statement of every kernel launched
+// this way, in every thread, before anything touches global memory -- and before any tensor
+// memory is allocated, so that a waiting CTA never holds what a CTA of the earlier kernel still
+// needs.  pdl_trigger() lets the next kernel be scheduled once every CTA of this one has called
+// it or left.  Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...) == cudaSuccess ? WKV_OK : WKV_ERR_LAUNCH;
+}
+
 // scalar (token-serial) v5/v6 kernels, wkv56_scalar.cu
 size_t scalar_backward_workspace(const wkv_args_t *a);
 int scalar_forward(const wkv_args_t *a, bool per_token_w, cudaStream_t s);
