@@ -231,12 +231,12 @@ class Runner:
             self.fwd.append(f); self.bwd.append(b)
         self.bwd_events, self.fwd_events = [], []
         self.launches = 0
-        # kernels per call: k_chunk_fwd ; k_chunk_dscan, k_chunk_bwd, k_reduce_partials -- and, when the
-        # library cuts the chains into time groups (few chains per GPU), a summary pass and a group
-        # scan more for the forward and for the dS scan
+        # kernels per call: k_chunk_fwd ; k_chunk_dscan, k_chunk_bwd, k_chunk_bwd_steep, k_reduce_partials
+        # -- and, when the library cuts the chains into time groups (few chains per GPU), a summary pass
+        # and a group scan more for the forward and for the dS scan
         a = wkv56._args("wkv6", B, wl["seg"], H, torch.bfloat16, W.WKV_W_RAW, W.WKV_STATE_KV, W.WKV_PATH_AUTO)
         split = W._lib.load().wkv6_forward_workspace(ctypes.byref(a)) > 256
-        self.fwd_launches, self.bwd_launches = (3, 5) if split else (1, 3)
+        self.fwd_launches, self.bwd_launches = (3, 6) if split else (1, 4)
 
     def step(self, record=False):
         for f in self.fwd:
@@ -453,7 +453,7 @@ def run_ours(args):
             "gpu_launches": launches,
             "roofline": {"bound": "hbm",
                          "kernel": "wkv6 backward of one BPTT segment: k_chunk_dscan + k_chunk_bwd "
-                                   "(+ k_reduce_partials), timed as one launch group",
+                                   "(+ k_chunk_bwd_steep, k_reduce_partials), timed as one launch group",
                          "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": which + " HBM copy bandwidth",
                          "algorithmic_bytes_per_launch": bwd_bytes,
