@@ -877,6 +877,42 @@ def run_neighbours(args):
                           "roofline_frac": nbytes / (ms_o * 1e-3) / 1e9 / hbm, "peak_source": which,
                           "pytorch_eager_ms_fwd_bwd": ms_e, "speedup_vs_eager": ms_e / ms_o,
                           "steps": steps, "warmup": warmup}), flush=True)
+    del y, gt, gout, x, sh, maa, m, gout5, rows
+    torch.cuda.empty_cache()
+
+    # the whole v6 time-mix block, forward + backward of one segment: the library's block next to
+    # the same block with the mixes and the norm-gate written as PyTorch expressions (both use
+    # the library's WKV op and cuBLAS projections)
+    class EagerNeighbours(W.RWKV_TimeMix6_0):
+        def forward(self, x, last_state):
+            shift, wkv_state = last_state
+            Bx, Tx, Cx = x.shape
+            dx = torch.cat((shift.unsqueeze(1), x[:, :-1]), 1) - x
+            xxx = torch.tanh((x + dx * self.time_maa_x) @ self.time_maa_w1).view(Bx * Tx, 5, -1).transpose(0, 1)
+            mw, mk, mv, mr, mg = torch.bmm(xxx, self.time_maa_w2).view(5, Bx, Tx, Cx).unbind(0)
+            xw, xk, xv = x + dx * (self.time_maa_w + mw), x + dx * (self.time_maa_k + mk), x + dx * (self.time_maa_v + mv)
+            xr, xg = x + dx * (self.time_maa_r + mr), x + dx * (self.time_maa_g + mg)
+            r, k, v, gg = self.receptance(xr), self.key(xk), self.value(xv), F.silu(self.gate(xg))
+            w = self.time_decay + torch.tanh(xw @ self.time_decay_w1) @ self.time_decay_w2
+            yy, wkv_state = W.WKV6.apply(Bx, Tx, Cx, self.n_head, r, k, v, w, self.time_faaaa, wkv_state)
+            yy = self.ln_x(yy.view(-1, Cx)).view(Bx, Tx, Cx)
+            return self.output(yy * gg), (x[:, -1], wkv_state)
+
+    torch.manual_seed(0)
+    blocks = {}
+    for name, cls in (("fused", W.RWKV_TimeMix6_0), ("pytorch_expressions", EagerNeighbours)):
+        blk = cls(1, 4, C, H, 64, C)
+        with torch.no_grad():     # (the default initialisation leaves the low-rank maps at zero)
+            blk.time_maa_w2.normal_(0, 0.02); blk.time_decay_w2.normal_(0, 0.02)
+        blocks[name] = blk.to(device=device, dtype=bf)
+    xb = rn(B, T, C).requires_grad_(True)
+    state = (rn(B, C), torch.zeros((B, H, 64, 64), device=device))
+    gob = rn(B, T, C)
+    res = {name: _time_steps(fb(lambda blk=blk: blk(xb, state)[0], gob), steps, warmup) for name, blk in blocks.items()}
+    print(json.dumps({"time_mix_block": "RWKV_TimeMix6_0", "shape": [B, T, C], "ms_fwd_bwd": res["fused"],
+                      "ms_fwd_bwd_with_pytorch_expressions": res["pytorch_expressions"],
+                      "speedup": res["pytorch_expressions"] / res["fused"],
+                      "tokens_per_s": B * T / (res["fused"] * 1e-3), "steps": steps, "warmup": warmup}), flush=True)
 
 
 def main():
