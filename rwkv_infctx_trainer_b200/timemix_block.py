@@ -142,7 +142,7 @@ class RWKV_TimeMix(_TimeMixBase):
         H = self.n_head
         # x*mix + x_prev*(1-mix)  =  x + (x_prev - x)*(1-mix)
         maa = 1.0 - torch.cat((self.time_mix_k, self.time_mix_v, self.time_mix_r, self.time_mix_g), 0).view(4, C)
-        xk, xv, xr, xg = (ddlerp(x, shift, maa[i:i + 1])[0] for i in range(4))
+        xk, xv, xr, xg = ddlerp(x, shift, maa).unbind(0)
         r, k, v = _lin(xr, self.receptance), _lin(xk, self.key), _lin(xv, self.value)
         g = F.silu(_lin(xg, self.gate))
         y, wkv_state = WKV5.apply(B, T, self.dim_att, H, r, k, v, self.time_decay, self.time_faaaa, wkv_state)
