@@ -768,9 +768,12 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
     const int t = row, hh = lane >> 4, l16 = lane & 15;
     const float ptt_t = s.ptt[t];
     const bool tvalid = j * CH + t < P.T;
-    float *wtot = reinterpret_cast<float *>(s.in[T_V].b);        // [4][64] per-warp totals of the token scan
-    float *gup = wtot + 4 * CH, *gwp = gup + 4 * CH;             // [4][64] per-warp sums for gu / the static gw
-    float keep[16];   // group 0: a_t of its first 16 channels; group 1: b_t of its last 16 channels
+    // [4][64] totals of the token scan, and [4][64] partial sums for gu / the static gw.  General build:
+    // per warp, in the v tile.  Mild-only build: per quarter of the chunk's tokens, in the A~ tile (free
+    // once gv is done; the v tile holds part of the a/b exchange there).
+    float *wtot = reinterpret_cast<float *>(MILD_ONLY ? s.atil.b : s.in[T_V].b);
+    float *gup = wtot + 4 * CH, *gwp = gup + 4 * CH;
+    float keep[16];   // (general build) group 0: a_t of its first 16 channels; group 1: b_t of its last 16 channels
 
     // decay-gradient constant sum_v S[k,v] D[k,v] at the chunk start (consumed after two more barriers)
     if (tid < CH) s.kb[tid] = P.e0[((size_t)bh * (n + 1) + j) * 64 + tid];
@@ -831,9 +834,18 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
                 }
                 out[q] = o;
                 ab[q] = GR ? -qq : qq;
-                if (!GR) gue[q] = ptt_t * raw[q] * oth[q];
+                if (!GR && !MILD_ONLY) gue[q] = ptt_t * raw[q] * oth[q];
             }
             st_tile(o_main, t, c8, pack8(out));
+            if constexpr (MILD_ONLY) {
+                // a_t (gr side) / b_t (gk side) of the lane half's 32 channels: one fp32 row of a tile of
+                // their own (a: S and P~ tiles, b: v and x tiles -- all consumed by now), read back
+                // channel-major by the token scan below
+                Tile &dstt = GR ? (hh ? s.ptil : s.in[T_S]) : (hh ? s.x : s.in[T_V]);
+                *reinterpret_cast<float4 *>(dstt.b + tile_off(t, 2 * bt)) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+                *reinterpret_cast<float4 *>(dstt.b + tile_off(t, 2 * bt + 1)) = make_float4(ab[4], ab[5], ab[6], ab[7]);
+                continue;
+            }
             const bool mine = GR ? (bt < 2) : (bt >= 2);
             if (mine) {
                 if (bt & 1) {
@@ -873,80 +885,130 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
         for (int c8 = 0; c8 < 4; c8++) st_tile(o_gv, t, 4 * hh + c8, pack8(gv + 8 * c8));
     }
     __syncthreads();
-    // the token scan of z = a + b for this thread's 16 channels: 32*hh + 16*wg .. +15
-    float bsub[16];
-    {
-        const Tile &got = wg ? s.in[T_S] : s.ptil;         // what the other group left for this one
+    if constexpr (MILD_ONLY) {
+        // Token scan, channel-major: thread = one channel c and one quarter q4 of the chunk's tokens.
+        // a and b of its 16 tokens come from the exchange tiles (a warp reads 32 consecutive floats of
+        // a row: no bank conflict); the exclusive prefix of z = a + b is a serial sum in registers, the
+        // quarters meet through `wtot`.  gu's partial sum p_tt r k rides along.
+        const int c = tid & 63, q4 = tid >> 6, cl = c & 31;
+        const Tile &ta = (c & 32) ? s.ptil : s.in[T_S], &tb = (c & 32) ? s.x : s.in[T_V];
+        float av[16], pre[16];
+        float run = 0.f, gus = 0.f;
 #pragma unroll
-        for (int c4 = 0; c4 < 4; c4++) {
-            const float4 o = *reinterpret_cast<const float4 *>(got.b + tile_off(t, 4 * hh + c4));
-            const float ov[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int i = 4 * c4 + q;
-                bsub[i] = wg ? keep[i] : ov[q];            // b_t
-                keep[i] += ov[q];                          // z_t
-            }
+        for (int i = 0; i < 16; i++) {
+            const int tt = 16 * q4 + i;
+            const uint32_t off = tile_off(tt, cl >> 2) + (cl & 3) * 4;
+            const float a = *reinterpret_cast<const float *>(ta.b + off);
+            const float b = *reinterpret_cast<const float *>(tb.b + off);
+            av[i] = a;
+            pre[i] = run;
+            run += a + b;
+            const uint32_t boff = tile_off(tt, c >> 3) + (c & 7) * 2;
+            const float rr = __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(s.in[T_R].b + boff));
+            const float kk = __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(s.in[T_K].b + boff));
+            gus = fmaf(s.ptt[tt] * rr, kk, gus);
         }
-#pragma unroll
-        for (int off = 1; off < 16; off <<= 1) {
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const float o = __shfl_up_sync(0xffffffffu, keep[i], off, 16);
-                if (l16 >= off) keep[i] += o;
-            }
-        }
-        if (l16 == 15) {
-#pragma unroll
-            for (int c4 = 0; c4 < 4; c4++)
-                *reinterpret_cast<float4 *>(wtot + w4 * CH + 32 * hh + 16 * wg + 4 * c4) =
-                    make_float4(keep[4 * c4], keep[4 * c4 + 1], keep[4 * c4 + 2], keep[4 * c4 + 3]);
-        }
-    }
-    __syncthreads();
-    {
-        const int kb0 = 32 * hh + 16 * wg;                 // first of the 16 channels
-        float glw[16];
-        // the constant of the chunk start plus the earlier warps' totals
-#pragma unroll
-        for (int c4 = 0; c4 < 4; c4++) {
-            float4 o = *reinterpret_cast<const float4 *>(s.kb + kb0 + 4 * c4);
-            for (int w = 0; w < w4; w++) {
-                const float4 p = *reinterpret_cast<const float4 *>(wtot + w * CH + kb0 + 4 * c4);
-                o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-            }
-            glw[4 * c4] = o.x + keep[4 * c4] - bsub[4 * c4];
-            glw[4 * c4 + 1] = o.y + keep[4 * c4 + 1] - bsub[4 * c4 + 1];
-            glw[4 * c4 + 2] = o.z + keep[4 * c4 + 2] - bsub[4 * c4 + 2];
-            glw[4 * c4 + 3] = o.w + keep[4 * c4 + 3] - bsub[4 * c4 + 3];
-        }
+        wtot[q4 * CH + c] = run;
+        gup[q4 * CH + c] = gus;
+        __syncthreads();
+        float base = s.kb[c];      // the constant of the chunk start plus the earlier quarters' totals
+        for (int w = 0; w < q4; w++) base += wtot[w * CH + c];
         if (PER_TOKEN) {
             // times the floored log-decay of the token, zero where the floor was hit (no gradient)
+            auto ctab1 = [&](int tt) { return reinterpret_cast<const float *>(ctab_ptr4(ct_lo, ct_hi, tt, c >> 2))[c & 3]; };
+            float cprev = q4 ? ctab1(16 * q4 - 1) : 0.f;
 #pragma unroll
-            for (int c2 = 0; c2 < 2; c2++) {
-                const int c8 = (kb0 >> 3) + c2;
-                float c[8], cp[8];
-                ld_ctab8(ct_lo, ct_hi, t, c8, c);
-                if (t > 0) {
-                    ld_ctab8(ct_lo, ct_hi, t - 1, c8, cp);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 8; q++) cp[q] = 0.f;
-                }
-                float o[8];
-#pragma unroll
-                for (int q = 0; q < 8; q++)
-                    o[q] = (__float_as_uint(c[q]) & 1u) ? glw[8 * c2 + q] * (c[q] - cp[q]) * LN2 : 0.f;
-                st_tile(o_gw, t, c8, pack8(o));
+            for (int i = 0; i < 16; i++) {
+                const int tt = 16 * q4 + i;
+                const float cc = ctab1(tt);
+                const float glw = base + pre[i] + av[i];
+                const float o = (__float_as_uint(cc) & 1u) ? glw * (cc - cprev) * LN2 : 0.f;
+                cprev = cc;
+                *reinterpret_cast<__nv_bfloat16 *>(o_gw.b + tile_off(tt, c >> 3) + (c & 7) * 2) = __float2bfloat16_rn(o);
             }
         } else {
+            float tot = 0.f;
 #pragma unroll
-            for (int c2 = 0; c2 < 2; c2++) {
-                float e[8];
-#pragma unroll
-                for (int q = 0; q < 8; q++) e[q] = tvalid ? glw[8 * c2 + q] : 0.f;
-                const float tot = halving_sum8(e, l16);
-                if ((l16 & 1) == 0) gwp[w4 * CH + kb0 + 8 * c2 + (l16 >> 1)] = tot;
+            for (int i = 0; i < 16; i++)
+                if (j * CH + 16 * q4 + i < P.T) tot += base + pre[i] + av[i];
+            gwp[q4 * CH + c] = tot;
+        }
+    } else {
+        // the token scan of z = a + b for this thread's 16 channels: 32*hh + 16*wg .. +15
+        float bsub[16];
+        {
+            const Tile &got = wg ? s.in[T_S] : s.ptil;         // what the other group left for this one
+    #pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                const float4 o = *reinterpret_cast<const float4 *>(got.b + tile_off(t, 4 * hh + c4));
+                const float ov[4] = {o.x, o.y, o.z, o.w};
+    #pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int i = 4 * c4 + q;
+                    bsub[i] = wg ? keep[i] : ov[q];            // b_t
+                    keep[i] += ov[q];                          // z_t
+                }
+            }
+    #pragma unroll
+            for (int off = 1; off < 16; off <<= 1) {
+    #pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float o = __shfl_up_sync(0xffffffffu, keep[i], off, 16);
+                    if (l16 >= off) keep[i] += o;
+                }
+            }
+            if (l16 == 15) {
+    #pragma unroll
+                for (int c4 = 0; c4 < 4; c4++)
+                    *reinterpret_cast<float4 *>(wtot + w4 * CH + 32 * hh + 16 * wg + 4 * c4) =
+                        make_float4(keep[4 * c4], keep[4 * c4 + 1], keep[4 * c4 + 2], keep[4 * c4 + 3]);
+            }
+        }
+        __syncthreads();
+        {
+            const int kb0 = 32 * hh + 16 * wg;                 // first of the 16 channels
+            float glw[16];
+            // the constant of the chunk start plus the earlier warps' totals
+    #pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                float4 o = *reinterpret_cast<const float4 *>(s.kb + kb0 + 4 * c4);
+                for (int w = 0; w < w4; w++) {
+                    const float4 p = *reinterpret_cast<const float4 *>(wtot + w * CH + kb0 + 4 * c4);
+                    o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                glw[4 * c4] = o.x + keep[4 * c4] - bsub[4 * c4];
+                glw[4 * c4 + 1] = o.y + keep[4 * c4 + 1] - bsub[4 * c4 + 1];
+                glw[4 * c4 + 2] = o.z + keep[4 * c4 + 2] - bsub[4 * c4 + 2];
+                glw[4 * c4 + 3] = o.w + keep[4 * c4 + 3] - bsub[4 * c4 + 3];
+            }
+            if (PER_TOKEN) {
+                // times the floored log-decay of the token, zero where the floor was hit (no gradient)
+    #pragma unroll
+                for (int c2 = 0; c2 < 2; c2++) {
+                    const int c8 = (kb0 >> 3) + c2;
+                    float c[8], cp[8];
+                    ld_ctab8(ct_lo, ct_hi, t, c8, c);
+                    if (t > 0) {
+                        ld_ctab8(ct_lo, ct_hi, t - 1, c8, cp);
+                    } else {
+    #pragma unroll
+                        for (int q = 0; q < 8; q++) cp[q] = 0.f;
+                    }
+                    float o[8];
+    #pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        o[q] = (__float_as_uint(c[q]) & 1u) ? glw[8 * c2 + q] * (c[q] - cp[q]) * LN2 : 0.f;
+                    st_tile(o_gw, t, c8, pack8(o));
+                }
+            } else {
+    #pragma unroll
+                for (int c2 = 0; c2 < 2; c2++) {
+                    float e[8];
+    #pragma unroll
+                    for (int q = 0; q < 8; q++) e[q] = tvalid ? glw[8 * c2 + q] : 0.f;
+                    const float tot = halving_sum8(e, l16);
+                    if ((l16 & 1) == 0) gwp[w4 * CH + kb0 + 8 * c2 + (l16 >> 1)] = tot;
+                }
             }
         }
     }
