@@ -262,6 +262,7 @@ struct BwdSmem {
     Tile ctab_hi;              // rows 32..63 of the cumulative-decay table
     float ptt[CH];
     float kb[CH];              // decay-gradient constant of the chunk start, per channel
+    __align__(16) float uf[CH];   // the head's bonus u in fp32
     uint64_t load_bar;
     uint64_t bar_early;        // P and the state products (need the raw tiles only)
     uint64_t bar_score;        // A1, A2
@@ -397,6 +398,7 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
     }
     // (the flag is read while the loads are in flight: asking first would put a DRAM round trip in front of them)
     if (MILD_ONLY && tid == 64) s.not_mine = P.mildflag[chunk_id] == 0;
+    if (tid >= 128 && tid < 128 + CH) s.uf[tid - 128] = __bfloat162float(P.u[h * 64 + tid - 128]);
     if (warp == 0) { tmem_alloc(&s.tmem_base, BWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -631,7 +633,10 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
             float a[8], d[8], uq[8];
             unpack8(ld_tile(s.in[T_R], row, c8), a);
             unpack8(ld_tile(s.in[T_K], row, c8), d);
-            unpack8(__ldg(reinterpret_cast<const uint4 *>(P.u + h * 64) + c8), uq);
+            {
+                const float4 u0 = *reinterpret_cast<const float4 *>(s.uf + 8 * c8), u1 = *reinterpret_cast<const float4 *>(s.uf + 8 * c8 + 4);
+                uq[0] = u0.x; uq[1] = u0.y; uq[2] = u0.z; uq[3] = u0.w; uq[4] = u1.x; uq[5] = u1.y; uq[6] = u1.z; uq[7] = u1.w;
+            }
 #pragma unroll
             for (int q = 0; q < 8; q++) diag += a[q] * uq[q] * d[q];
         }
@@ -805,7 +810,10 @@ bwd_chunk(const CUtensorMap &map_r, const CUtensorMap &map_k, const CUtensorMap 
             unpack8(ld_tile(t_own, t, c8), own);
             unpack8(ld_tile(t_raw, t, c8), raw);
             unpack8(ld_tile(t_oth, t, c8), oth);
-            unpack8(__ldg(reinterpret_cast<const uint4 *>(P.u + h * 64) + c8), uu);
+            {
+                const float4 u0 = *reinterpret_cast<const float4 *>(s.uf + 8 * c8), u1 = *reinterpret_cast<const float4 *>(s.uf + 8 * c8 + 4);
+                uu[0] = u0.x; uu[1] = u0.y; uu[2] = u0.z; uu[3] = u0.w; uu[4] = u1.x; uu[5] = u1.y; uu[6] = u1.z; uu[7] = u1.w;
+            }
             ld_ctab8(ct_lo, ct_hi, mrow, c8, mb);
             if (zrow >= 0) {
                 ld_ctab8(ct_lo, ct_hi, zrow, c8, z);
