@@ -51,6 +51,7 @@ struct FwdSmem {
     float dpart[4][CH];    // score-diagonal partials per token
     float dvec[2][CH];     // decay of the whole chunk per key channel, by chunk parity
     float wtot[8][CH];     // log2-decay total of each warp's 8 tokens, per channel
+    __align__(16) float uf[CH];   // the head's bonus u in fp32
     uint64_t load_bar[2];  // TMA: a stage has landed
     uint64_t ops_bar[2];   // compute warps -> feeder: the operands of a chunk are in place (by chunk parity:
                            // in a state-only pass the compute warps may run a chunk ahead of the feeder)
@@ -137,6 +138,7 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
         s.abort_flag = 0;
         fence_mbar_init();
     }
+    if (full && tid >= 64 && tid < 64 + CH) s.uf[tid - 64] = __bfloat162float(P.u[h * 64 + tid - 64]);
     if (warp == 0) { tmem_alloc(&s.tmem_base, FWD_TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -331,7 +333,10 @@ k_chunk_fwd(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ C
             __syncwarp();
             // the bonus u of the thread's 4 channels (read again for every chunk: registers are scarce here)
             float uu[4];
-            if (full) unpack4(__ldg(reinterpret_cast<const uint2 *>(P.u + h * 64 + ch0)), uu);
+            if (full) {
+                const float4 u4 = *reinterpret_cast<const float4 *>(s.uf + ch0);
+                uu[0] = u4.x; uu[1] = u4.y; uu[2] = u4.z; uu[3] = u4.w;
+            }
             float other[4];          // 2^{total of the other block}
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) other[ch] = exp2f(other_l2[ch]);
