@@ -250,8 +250,9 @@ int wkv56_uses_chunked(const wkv_args_t *a, int per_token_w);
  *
  * wkv_ddlerp_*: the token-shift mixes of RWKV-v6/src/module/TimeMix.py:262-273,
  *   out_i = x + (x_prev - x) * (maa_i + m_i),  i < nmix,  nmix = 1 (the first mix, m = NULL),
- *   5 (xw,xk,xv,xr,xg in the order of m) or 4 (the static mixes of the v5 block,
- *   RWKV-v5/src/module/TimeMix.py:293-300, with maa = 1 - time_mix and m = NULL).
+ *   5 (xw,xk,xv,xr,xg in the order of m), 4 (the static mixes of the v5 block,
+ *   RWKV-v5/src/module/TimeMix.py:293-300, with maa = 1 - time_mix and m = NULL) or 3 (those
+ *   of the v4 block, RWKV-v4neo/src/model.py:240-244).
  *   x [B,T,C]; x_prev of a row's first token is
  *   shift [B,C] (last token of the previous segment); maa fp32 [nmix,C]; m, out [nmix,B,T,C].
  *   Backward: gx [B,T,C], gm [nmix,B,T,C] (when m is given), gmaa fp32 [nmix,C], and

@@ -368,7 +368,7 @@ int wkv_lnx_gate_backward(int tokens, int H, const void *y, const void *g, const
 int wkv_ddlerp_forward(int B, int T, int C, int nmix, const void *x, const void *shift, const float *maa,
                        const void *m, void *out, void *stream) {
     if (B < 0 || T < 0 || C < 0 || C % 8 != 0) return WKV_ERR_SHAPE;
-    if (nmix != 1 && nmix != 4 && nmix != 5) return WKV_ERR_UNSUPPORTED;
+    if (nmix != 1 && nmix != 3 && nmix != 4 && nmix != 5) return WKV_ERR_UNSUPPORTED;
     if (B == 0 || T == 0 || C == 0) return WKV_OK;
     if (!x || !shift || !maa || !out) return WKV_ERR_NULL;
     for (const void *p : {x, shift, (const void *)maa, (const void *)out})
@@ -382,6 +382,9 @@ int wkv_ddlerp_forward(int B, int T, int C, int nmix, const void *x, const void 
                                                                            maa, (const uint4 *)m, (uint4 *)out);
     else if (nmix == 4)
         k_ddlerp_fwd<4><<<(unsigned)blocks, TPB, 0, (cudaStream_t)stream>>>(B, T, C, (const uint4 *)x, (const uint4 *)shift,
+                                                                           maa, (const uint4 *)m, (uint4 *)out);
+    else if (nmix == 3)
+        k_ddlerp_fwd<3><<<(unsigned)blocks, TPB, 0, (cudaStream_t)stream>>>(B, T, C, (const uint4 *)x, (const uint4 *)shift,
                                                                            maa, (const uint4 *)m, (uint4 *)out);
     else
         k_ddlerp_fwd<1><<<(unsigned)blocks, TPB, 0, (cudaStream_t)stream>>>(B, T, C, (const uint4 *)x, (const uint4 *)shift,
@@ -399,7 +402,7 @@ int wkv_ddlerp_backward(int B, int T, int C, int nmix, const void *x, const void
                         const void *gout, const void *gshift_in, void *gx, void *gm, void *gshift_out, float *gmaa,
                         void *workspace, size_t workspace_bytes, void *stream) {
     if (B < 0 || T < 0 || C < 0 || C % 8 != 0) return WKV_ERR_SHAPE;
-    if (nmix != 1 && nmix != 4 && nmix != 5) return WKV_ERR_UNSUPPORTED;
+    if (nmix != 1 && nmix != 3 && nmix != 4 && nmix != 5) return WKV_ERR_UNSUPPORTED;
     if (!gmaa) return WKV_ERR_NULL;
     cudaStream_t s = (cudaStream_t)stream;
     if (B == 0 || T == 0 || C == 0) {
@@ -420,6 +423,10 @@ int wkv_ddlerp_backward(int B, int T, int C, int nmix, const void *x, const void
                                                (uint4 *)gm, (uint4 *)gshift_out, (float *)workspace);
     else if (nmix == 4)
         k_ddlerp_bwd<4><<<blocks, TPB, 0, s>>>(B, T, C, DDLERP_PIECE, (const uint4 *)x, (const uint4 *)shift, maa,
+                                               (const uint4 *)m, (const uint4 *)gout, (const uint4 *)gshift_in, (uint4 *)gx,
+                                               (uint4 *)gm, (uint4 *)gshift_out, (float *)workspace);
+    else if (nmix == 3)
+        k_ddlerp_bwd<3><<<blocks, TPB, 0, s>>>(B, T, C, DDLERP_PIECE, (const uint4 *)x, (const uint4 *)shift, maa,
                                                (const uint4 *)m, (const uint4 *)gout, (const uint4 *)gshift_in, (uint4 *)gx,
                                                (uint4 *)gm, (uint4 *)gshift_out, (float *)workspace);
     else

@@ -8,7 +8,7 @@
     the token-shift mixes of RWKV-v6/src/module/TimeMix.py:262-273:
     ``x + (x_prev - x) * (maa[i] + m[i])`` for every i, with ``x_prev`` the previous token
     (``shift`` [B,C] before a row's first token).  ``maa`` [n,C], ``m`` [n,B,T,C] or None,
-    n = 1, 4 or 5; returns [n,B,T,C].  Differentiable w.r.t. x, shift, maa, m.
+    n = 1, 3, 4 or 5; returns [n,B,T,C].  Differentiable w.r.t. x, shift, maa, m.
 
 bf16 tensors only (the dtype the trainer runs these in); parameters may have any float dtype.
 """

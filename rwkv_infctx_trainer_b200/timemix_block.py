@@ -3,6 +3,8 @@ library's kernels.
 
 ``RWKV_TimeMix6_0``  mirrors RWKV-v6/src/module/TimeMix.py:121-300 (``_forward_cuda``)
 ``RWKV_TimeMix``     mirrors RWKV-v5/src/module/TimeMix.py:161-323 (``_forward_cuda``)
+``RWKV_TimeMix_v4``  mirrors ``RWKV_TimeMix`` of RWKV-v4neo/src/model.py:197-279, with its
+                     ``TimeMixState`` (RWKV-v4neo/src/model.py:138-142)
 
 Same constructor arguments, same parameter names and shapes (a state_dict of the project's
 module loads), same ``forward(x, last_state) -> (out, (shift_state, wkv_state))``.  What is
@@ -23,6 +25,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .timemix import ddlerp, lnx_gate
+from .wkv4 import wkv_op
 from .wkv5 import WKV5
 from .wkv6 import WKV6
 
@@ -149,3 +152,46 @@ class RWKV_TimeMix(_TimeMixBase):
         # ln_x(y / 8) with eps  ==  GroupNorm(y) with eps * 64
         y = lnx_gate(y, g, self.ln_x.weight, self.ln_x.bias, self.ln_x.eps * HEAD_SIZE_DIVISOR ** 2, H)
         return _lin(y, self.output), (x[:, -1], wkv_state)
+
+
+class TimeMixState:
+    """(shift_state [B,C], wkv_state [B,C,3]) of the v4 block."""
+
+    def __init__(self, shift_state: torch.Tensor, wkv_state: torch.Tensor):
+        self.shift_state = shift_state
+        self.wkv_state = wkv_state
+
+
+class RWKV_TimeMix_v4(nn.Module):
+    """v4 block: three static token-shift mixes (one fused pass), k/v/r projections, the v4 WKV op
+    (``rwkv::wkv`` with the raw ``time_decay`` / ``time_first``), sigmoid(r) gate, output projection.
+    ``forward(x, TimeMixState) -> (out, TimeMixState)``; the wkv state is fp32 ``[B,C,3]`` and
+    carries its gradient (in the op's max-shifted convention) to the previous segment."""
+
+    def __init__(self, layer_id, n_layer, n_embd, dim_att):
+        super().__init__()
+        self.layer_id, self.n_layer, self.n_embd, self.dim_att = layer_id, n_layer, n_embd, dim_att
+        r01, r1a0 = _layer_ratios(layer_id, n_layer)
+        with torch.no_grad():
+            h = torch.arange(dim_att, dtype=torch.float32)
+            self.time_decay = nn.Parameter(-5.0 + 8.0 * (h / max(dim_att - 1, 1)).pow(0.7 + 1.3 * r01))
+            self.time_first = nn.Parameter(torch.full((dim_att,), 0.3).log() + ((h + 1) % 3 - 1) * 0.5)
+            ddd = (torch.arange(n_embd, dtype=torch.float32) / n_embd).view(1, 1, n_embd)
+            self.time_mix_k = nn.Parameter(ddd.pow(r1a0))
+            self.time_mix_v = nn.Parameter(ddd.pow(r1a0) + 0.3 * r01)
+            self.time_mix_r = nn.Parameter(ddd.pow(0.5 * r1a0))
+        self.key = nn.Linear(n_embd, dim_att, bias=False)
+        self.value = nn.Linear(n_embd, dim_att, bias=False)
+        self.receptance = nn.Linear(n_embd, dim_att, bias=False)
+        self.output = nn.Linear(dim_att, n_embd, bias=False)
+
+    def forward(self, x, last_state: TimeMixState):
+        x = x.to(BF16).contiguous()
+        C = x.shape[-1]
+        # x*mix + x_prev*(1-mix)  =  x + (x_prev - x)*(1-mix)
+        maa = 1.0 - torch.cat((self.time_mix_k, self.time_mix_v, self.time_mix_r), 0).view(3, C)
+        xk, xv, xr = ddlerp(x, last_state.shift_state.to(BF16).contiguous(), maa).unbind(0)
+        k, v = _lin(xk, self.key), _lin(xv, self.value)
+        sr = torch.sigmoid(_lin(xr, self.receptance))
+        y, new_wkv_state = wkv_op(self.time_decay, self.time_first.to(BF16), k, v, last_state.wkv_state)
+        return _lin(sr * y, self.output), TimeMixState(x[:, -1], new_wkv_state)
